@@ -1,0 +1,60 @@
+"""ctypes binding of libsrm2_b200.so (the C ABI declared in include/srm2_b200.h).
+
+There is no fallback: if the library is missing or a symbol is absent, importing the bound function
+raises, and every non-zero status from the library becomes a RuntimeError.
+"""
+import ctypes as C
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+LIB_PATH = PKG / 'libsrm2_b200.so'
+
+_vp, _i64, _i32, _u32, _f32, _f64 = C.c_void_p, C.c_int64, C.c_int, C.c_uint32, C.c_float, C.c_double
+_f8 = C.POINTER(C.c_float)
+
+# name -> (restype, argtypes); must list every symbol of include/srm2_b200.h
+SIGNATURES = {
+    'srm2_version': (C.c_int, []),
+    'srm2_status_string': (C.c_char_p, [C.c_int]),
+    'srm2_last_cuda_error': (C.c_char_p, []),
+    'srm2_adam_scalars': (C.c_int, [_f64, _f64, _f64, _f64, _i64, _f8]),
+    'srm2_adam_rows_f32': (C.c_int, [_vp, _vp, _i32, _vp, _i64, _i64, _f8, _vp]),
+    'srm2_init_rows_f32': (C.c_int, [_vp, _vp, _i64, _i64, _u32, _f32, _vp]),
+    'srm2_replay_rows_f32': (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _u32, _f32, _vp, _i64, _vp]),
+}
+
+_lib = None
+
+
+def lib():
+    """The loaded library; raises if it has not been built (python -m elara_b200.build)."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(f'{LIB_PATH} is missing: build it with `python -m elara_b200.build` '
+                               '(there is no CPU or PyTorch fallback for these kernels)')
+        L = C.CDLL(str(LIB_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            f = getattr(L, name)          # AttributeError if the symbol is not exported
+            f.restype, f.argtypes = res, args
+        _lib = L
+    return _lib
+
+
+def check(status, what):
+    if status != 0:
+        L = lib()
+        msg = L.srm2_status_string(status).decode()
+        if status == -4:
+            msg += ': ' + L.srm2_last_cuda_error().decode()
+        raise RuntimeError(f'{what}: {msg} (status {status})')
+
+
+def ptr(t):
+    """Device (or host) address of a tensor's first element; 0 for None."""
+    return 0 if t is None else t.data_ptr()
+
+
+def stream_of(device):
+    import torch
+    return torch.cuda.current_stream(device).cuda_stream

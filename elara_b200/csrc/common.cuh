@@ -1,0 +1,60 @@
+// Shared device/host helpers of the srm2_b200 kernels (sm_100a).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "srm2_b200.h"
+
+namespace srm2 {
+
+// The B200 has 148 SMs; grids of the streaming kernels are sized in multiples of this.
+constexpr int kSMs = 148;
+
+// Records a CUDA runtime error for srm2_last_cuda_error(); returns SRM2_ERR_CUDA or SRM2_OK.
+int note_cuda(cudaError_t e);
+
+inline int launch_status() { return note_cuda(cudaGetLastError()); }
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---- exact fp32 arithmetic: every operation rounded on its own, never contracted ----------------
+struct AdamSc { float lr, b1, omb1, b2, omb2, bc1, bc2, eps; };
+
+// One Adam step on one element, in the operation order of the reference
+// (srm2/ops.py:50-56 == srm2/csrc/srm2_cpu.cpp:27-32).
+__device__ __forceinline__ void adam_elem(float& w, float& m, float& v, float g, const AdamSc& s) {
+  m = __fadd_rn(__fmul_rn(s.b1, m), __fmul_rn(s.omb1, g));
+  const float t2 = __fmul_rn(s.omb2, g);
+  v = __fadd_rn(__fmul_rn(s.b2, v), __fmul_rn(t2, g));
+  const float mh = __fdiv_rn(m, s.bc1);
+  const float vh = __fdiv_rn(v, s.bc2);
+  const float den = __fadd_rn(__fsqrt_rn(vh), s.eps);
+  w = __fsub_rn(w, __fdiv_rn(__fmul_rn(s.lr, mh), den));
+}
+
+__device__ __forceinline__ void adam_vec4(float4& w, float4& m, float4& v, const float4& g, const AdamSc& s) {
+  adam_elem(w.x, m.x, v.x, g.x, s);
+  adam_elem(w.y, m.y, v.y, g.y, s);
+  adam_elem(w.z, m.z, v.z, g.z, s);
+  adam_elem(w.w, m.w, v.w, g.w, s);
+}
+
+// murmur3 fmix32 (srm2/gpu_ops.py:15-23)
+__device__ __forceinline__ uint32_t fmix32(uint32_t x) {
+  x ^= x >> 16; x *= 0x85EBCA6Bu; x ^= x >> 13; x *= 0xC2B2AE35u; x ^= x >> 16;
+  return x;
+}
+
+// Initial weight of element j of row r (srm2/gpu_ops.py:29-34).  rowkey = fmix32((uint32)(r>>32) + seed),
+// base = (uint32)(r*D).  u*2-1 is exact; the product with bound is the single rounding.
+__device__ __forceinline__ float init_elem(uint32_t base, uint32_t j, uint32_t rowkey, uint32_t seed, float bound) {
+  const uint32_t h = fmix32(((base + j) ^ rowkey) ^ seed);
+  const float u = __fmul_rn(__uint2float_rn(h >> 8), 1.0f / 16777216.0f);
+  return __fmul_rn(__fsub_rn(__fmul_rn(u, 2.0f), 1.0f), bound);
+}
+
+// streaming (read-once) 16-byte load / store
+__device__ __forceinline__ float4 ld_stream4(const float* p) { return __ldcs(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ void st_stream4(float* p, const float4& v) { __stcs(reinterpret_cast<float4*>(p), v); }
+
+}  // namespace srm2

@@ -1,0 +1,82 @@
+/*
+ * srm2_b200 — C ABI of the B200 (sm_100a) kernels for the sparse-optimizer path of ELARA's srm2 package.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless the parameter comment says "host".
+ *   - Nothing here allocates, frees or synchronises; scratch memory is passed in by the caller.
+ *   - Every call enqueues its kernels on `stream` (a cudaStream_t passed as void*; NULL = legacy default
+ *     stream) of the CURRENT device and returns immediately.
+ *   - Return value: SRM2_OK (0) or a negative SRM2_ERR_* code; srm2_status_string() names it.  Argument
+ *     errors are detected on the host before anything is enqueued.
+ *   - fp32 arithmetic is IEEE round-to-nearest, one rounding per operation, no FMA contraction, in the
+ *     operation order of the reference, so results are bit-identical to the reference's CPU and GPU paths.
+ *
+ * Each entry point names the reference interface it stands in for (paths relative to the reference project).
+ */
+#ifndef SRM2_B200_H
+#define SRM2_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SRM2_OK 0
+#define SRM2_ERR_ARG (-1)         /* null pointer, negative size, inconsistent arguments            */
+#define SRM2_ERR_UNSUPPORTED (-2) /* a size outside what the kernels are built for                  */
+#define SRM2_ERR_SCRATCH (-3)     /* scratch buffer too small (see the *_scratch_bytes functions)   */
+#define SRM2_ERR_CUDA (-4)        /* the CUDA runtime refused a launch; see srm2_last_cuda_error()  */
+
+typedef void* srm2_stream_t;
+
+/* library identification: major*10000 + minor*100 + patch */
+int srm2_version(void);
+const char* srm2_status_string(int status);
+/* text of the last CUDA runtime error seen by this thread inside the library ("" if none) */
+const char* srm2_last_cuda_error(void);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Adam scalars.  Replaces `adam_scalars` of the reference's host extension
+ * (srm2/csrc/srm2_cpu.cpp:13-20 make_scalars, :255-257 export; called at srm2/ops.py:64 and srm2/gpu_ops.py:87).
+ * out (host) = {lr, b1, 1-b1, b2, 1-b2, 1-b1^step, 1-b2^step, eps}, each evaluated in double, rounded to float once.
+ */
+int srm2_adam_scalars(double lr, double b1, double b2, double eps, int64_t step, float out[8] /* host */);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Row-sparse Adam.  Replaces `gpu_adam` / Triton `_adam_rows` (srm2/ops.py:42-67); same arithmetic as the
+ * reference's `cpu_adam` (srm2/csrc/srm2_cpu.cpp:22-56).
+ *   pool   [C,3,D] fp32, row record = w[D] m[D] v[D]; updated in place for the rows named in `slots`
+ *   slots  [n] int32 (slots_is_i64 == 0) or int64 (!= 0), DISTINCT row indices into pool
+ *   grad   [n,D] fp32 contiguous; row i belongs to slots[i]
+ *   sc     (host) the 8 scalars of srm2_adam_scalars
+ * n == 0 is a no-op.
+ */
+int srm2_adam_rows_f32(float* pool, const void* slots, int slots_is_i64, const float* grad, int64_t n, int64_t D,
+                       const float sc[8] /* host */, srm2_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Counter-hash row initialisation.  Replaces `init_rows` / Triton `_init_rows` (srm2/gpu_ops.py:15-48).
+ *   out [n,3,D] fp32: w = (u*2-1)*bound with u = (fmix32(key ^ seed) >> 8) * 2^-24,
+ *                     key = (uint32)(row*D + j) ^ fmix32((uint32)(row >> 32) + seed); m = v = 0
+ *   rows [n] int64;  seed = the reference's integer seed truncated to 32 bits.
+ */
+int srm2_init_rows_f32(float* out, const int64_t* rows, int64_t n, int64_t D, uint32_t seed, float bound,
+                       srm2_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Exact replay of up to K logged gradients into freshly initialised rows.
+ * Replaces `replay_rows` / Triton `_replay` (srm2/gpu_ops.py:51-99).
+ *   out   [n,3,D]            rows [n] int64
+ *   logs  flat [sum(cnt), D] fp32; the entries of row i start at offs[i] (int64 [n])
+ *   steps [n,K] int32 logical step of each entry;  cnt [n] int32 (0..K)
+ *   table [table_rows, 8] fp32: Adam scalars per logical step (`ScalarTable.t`, srm2/gpu_ops.py:82-88)
+ */
+int srm2_replay_rows_f32(float* out, const int64_t* rows, const float* logs, const int64_t* offs, const int32_t* steps,
+                         const int32_t* cnt, int64_t n, int64_t D, int64_t K, uint32_t seed, float bound,
+                         const float* table, int64_t table_rows, srm2_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SRM2_B200_H */

@@ -51,6 +51,7 @@ def lib():
         L.orc_unique_inverse.argtypes = [_i64p, C.c_int64, _i64p, _i64p]
         L.orc_unique_inverse.restype = C.c_int64
         L.orc_segment_reduce.argtypes = [_f32p, _i64p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, _f32p]
+        L.orc_segment_reduce_windowed.argtypes = [_f32p, _i64p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, _f32p]
         L.orc_dir_a.argtypes = [C.POINTER(_Dir), _i64p, C.c_int64, _i64p, _i32p, C.c_int64, _i64p, C.c_int64, C.c_int64,
                                 _i32p, _i32p, _i64p, _i64p, _i64p, _u8p, _i64p, _i64p, _i64p]
         L.orc_dir_admit.argtypes = [C.POINTER(_Dir), _i64p, _i64p, C.c_int64, C.c_int64, C.c_int64]
@@ -132,10 +133,23 @@ def unique_inverse(ids):
 SEGMENT_CHUNK = 10
 
 
-def segment_reduce(grad, inv, n_unique, chunk=None):
+# inputs of at most this many lookups follow the windowed order (see orc_segment_reduce_windowed)
+SEGMENT_SMALL_N = 3072
+SEGMENT_WINDOW = 32
+
+
+def segment_reduce(grad, inv, n_unique, chunk=None, window=None):
+    """chunk/window None: the order PyTorch's CUDA operator uses for an input of this size."""
     grad = np.ascontiguousarray(grad, np.float32)
     n, D = grad.shape
     out = np.empty((n_unique, D), np.float32)
+    if window is None and chunk is None and n <= SEGMENT_SMALL_N:
+        window = SEGMENT_WINDOW
+    if window:
+        lib().orc_segment_reduce_windowed(grad.reshape(-1) if n else np.zeros(1, np.float32),
+                                          np.ascontiguousarray(inv, np.int64) if n else np.zeros(1, np.int64), n, D, n_unique,
+                                          window, out.reshape(-1) if n_unique else np.zeros(1, np.float32))
+        return out
     ck = SEGMENT_CHUNK if chunk is None else chunk
     lib().orc_segment_reduce(grad.reshape(-1) if n else np.zeros(1, np.float32), np.ascontiguousarray(inv, np.int64) if n else np.zeros(1, np.int64),
                              n, D, n_unique, ck, out.reshape(-1) if n_unique else np.zeros(1, np.float32))

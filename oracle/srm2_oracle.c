@@ -183,6 +183,31 @@ void orc_segment_reduce(const float* grad, const int64_t* inv, int64_t n, int64_
   free(start); free(order); free(fill);
 }
 
+/* Small-input order of the same operator (inputs of at most a few thousand lookups take a different  */
+/* kernel inside PyTorch): the lookups are walked in windows of `window` consecutive positions; inside */
+/* a window the lookups of one unique row are summed left to right starting from the first of them,   */
+/* and that window sum is then added to the output row, which starts at +0.                           */
+void orc_segment_reduce_windowed(const float* grad, const int64_t* inv, int64_t n, int64_t D, int64_t n_unique,
+                                 int64_t window, float* out) {
+  for (int64_t t = 0; t < n_unique * D; ++t) out[t] = 0.0f;
+  uint8_t* done = ORC_NEW(uint8_t, window);
+  for (int64_t w0 = 0; w0 < n; w0 += window) {
+    const int64_t w1 = w0 + window < n ? w0 + window : n;
+    memset(done, 0, (size_t)window);
+    for (int64_t p = w0; p < w1; ++p) {
+      if (done[p - w0]) continue;
+      const int64_t j = inv[p];
+      for (int64_t d = 0; d < D; ++d) {
+        float acc = grad[p * D + d];
+        for (int64_t q = p + 1; q < w1; ++q) if (inv[q] == j) acc = acc + grad[q * D + d];
+        out[j * D + d] = out[j * D + d] + acc;
+      }
+      for (int64_t q = p + 1; q < w1; ++q) if (inv[q] == j) done[q - w0] = 1;
+    }
+  }
+  free(done);
+}
+
 /* ------------------------------------------------------------------------------------------- */
 /* State directory; state layout srm2/csrc/elara_dir.cpp:8-11, built at srm2/elara.py:117-149.   */
 typedef struct {

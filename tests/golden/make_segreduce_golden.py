@@ -1,0 +1,75 @@
+"""Known-answer vectors for the segment-reduce, produced by PyTorch's own CUDA operator on a GPU box.
+
+The reference sums per-lookup gradients with `torch.ops.aten.embedding_dense_backward` (srm2/train.py:429);
+the order of the fp32 additions is that operator's.  This script runs the operator (black box: inputs in,
+outputs out) on inputs whose sums depend on the association order, stores inputs and outputs, and reports
+which candidate order of the CPU oracle reproduces each case.
+
+    python tests/golden/make_segreduce_golden.py [--out tests/golden/segreduce_cuda.npz]
+
+Needs a CUDA device; the torch version that produced the committed file is stored inside it.
+"""
+import argparse
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent.parent
+sys.path.insert(0, str(ROOT))
+
+
+def case(rng, n, D, n_keys, zipf=False):
+    """Order-sensitive values: normal numbers over seven decades, a few zeros and negative zeros."""
+    if zipf:
+        p = np.arange(1, n_keys + 1, dtype=np.float64) ** -1.1
+        p /= p.sum()
+        keys = rng.choice(n_keys, size=n, p=p)
+    else:
+        keys = rng.integers(0, n_keys, n)
+    _, inv = np.unique(keys, return_inverse=True)            # every index in [0, n_unique) occurs
+    inv = inv.reshape(-1).astype(np.int64)
+    grad = (rng.standard_normal((n, D)) * 10.0 ** rng.integers(-3, 4, (n, 1))).astype(np.float32)
+    grad[rng.random(n) < 0.02] = 0.0
+    grad[rng.random(n) < 0.02] = -0.0
+    return grad, inv, int(inv.max()) + 1 if n else 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--out', default=str(ROOT / 'tests/golden/segreduce_cuda.npz'))
+    a = ap.parse_args()
+    from oracle import oracle as O
+    dev = torch.device('cuda:0')
+    rng = np.random.default_rng(2024)
+    save = {'torch_version': np.array(torch.__version__), 'device': np.array(torch.cuda.get_device_name(0))}
+    specs = []
+    for n in (1, 5, 31, 32, 33, 64, 100, 767, 768, 769, 1000, 3071, 3072, 3073, 4000, 5000):
+        for D, nk in ((16, 3), (16, 40), (128, 7)):
+            if D == 128 and n > 1100:
+                continue
+            specs.append((n, D, nk, False))
+    specs += [(20000, 16, 600, True), (30000, 32, 3000, True), (6000, 64, 50, True), (3500, 24, 11, False), (3500, 6, 11, False)]
+    summary = {}
+    for ci, (n, D, nk, zipf) in enumerate(specs):
+        grad, inv, nu = case(rng, n, D, nk, zipf)
+        out = torch.ops.aten.embedding_dense_backward(torch.from_numpy(grad).to(dev), torch.from_numpy(inv).to(dev), nu, -1, False)
+        out2 = torch.ops.aten.embedding_dense_backward(torch.from_numpy(grad).to(dev), torch.from_numpy(inv).to(dev), nu, -1, False)
+        out = out.cpu().numpy()
+        assert np.array_equal(out.view(np.uint32), out2.cpu().numpy().view(np.uint32)), 'operator is not run-to-run deterministic'
+        cands = {'sequential': O.segment_reduce(grad, inv, nu, chunk=0, window=0), 'chunk10': O.segment_reduce(grad, inv, nu, chunk=10, window=0),
+                 'window32': O.segment_reduce(grad, inv, nu, window=32), 'default': O.segment_reduce(grad, inv, nu)}
+        match = [k for k, v in cands.items() if np.array_equal(v.view(np.uint32), out.view(np.uint32))]
+        summary[(n, D, nk)] = match
+        print(f'n={n:6d} D={D:4d} keys={nu:5d} zipf={int(zipf)} matches={match}', flush=True)
+        save[f'c{ci}_grad'] = grad; save[f'c{ci}_inv'] = inv; save[f'c{ci}_nu'] = np.array(nu); save[f'c{ci}_out'] = out
+    save['n_cases'] = np.array(len(specs))
+    Path(a.out).parent.mkdir(parents=True, exist_ok=True)
+    np.savez_compressed(a.out, **save)
+    bad = [k for k, v in summary.items() if 'default' not in v]
+    print('cases not matched by the oracle default order:', bad)
+
+
+if __name__ == '__main__':
+    main()
