@@ -54,16 +54,26 @@ def main():
     summary = {}
     for ci, (n, D, nk, zipf) in enumerate(specs):
         grad, inv, nu = case(rng, n, D, nk, zipf)
-        out = torch.ops.aten.embedding_dense_backward(torch.from_numpy(grad).to(dev), torch.from_numpy(inv).to(dev), nu, -1, False)
-        out2 = torch.ops.aten.embedding_dense_backward(torch.from_numpy(grad).to(dev), torch.from_numpy(inv).to(dev), nu, -1, False)
-        out = out.cpu().numpy()
-        assert np.array_equal(out.view(np.uint32), out2.cpu().numpy().view(np.uint32)), 'operator is not run-to-run deterministic'
+        g_d, i_d = torch.from_numpy(grad).to(dev), torch.from_numpy(inv).to(dev)
+        # default mode, several runs: for inputs above a few thousand lookups that map to FEW unique rows the operator
+        # is not run-to-run deterministic in its default mode; such cases are stored with the output of
+        # torch.use_deterministic_algorithms(True) and flagged.
+        torch.use_deterministic_algorithms(False)
+        runs = [torch.ops.aten.embedding_dense_backward(g_d, i_d, nu, -1, False).cpu().numpy() for _ in range(5)]
+        stable = len({r.tobytes() for r in runs}) == 1
+        torch.use_deterministic_algorithms(True)
+        det = torch.ops.aten.embedding_dense_backward(g_d, i_d, nu, -1, False).cpu().numpy()
+        torch.use_deterministic_algorithms(False)
+        if stable:
+            assert np.array_equal(det.view(np.uint32), runs[0].view(np.uint32)), 'deterministic mode differs from a stable default mode'
+        out = runs[0] if stable else det
         cands = {'sequential': O.segment_reduce(grad, inv, nu, chunk=0, window=0), 'chunk10': O.segment_reduce(grad, inv, nu, chunk=10, window=0),
                  'window32': O.segment_reduce(grad, inv, nu, window=32), 'default': O.segment_reduce(grad, inv, nu)}
         match = [k for k, v in cands.items() if np.array_equal(v.view(np.uint32), out.view(np.uint32))]
         summary[(n, D, nk)] = match
-        print(f'n={n:6d} D={D:4d} keys={nu:5d} zipf={int(zipf)} matches={match}', flush=True)
+        print(f'n={n:6d} D={D:4d} keys={nu:5d} zipf={int(zipf)} default-mode-stable={int(stable)} matches={match}', flush=True)
         save[f'c{ci}_grad'] = grad; save[f'c{ci}_inv'] = inv; save[f'c{ci}_nu'] = np.array(nu); save[f'c{ci}_out'] = out
+        save[f'c{ci}_default_mode_stable'] = np.array(stable)
     save['n_cases'] = np.array(len(specs))
     Path(a.out).parent.mkdir(parents=True, exist_ok=True)
     np.savez_compressed(a.out, **save)

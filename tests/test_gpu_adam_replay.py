@@ -56,7 +56,7 @@ def test_adam_unaligned_views_and_empty(dev, oracle):
     from elara_b200.ops import gpu_adam
     rng = np.random.default_rng(3)
     R, D, n = 300, 16, 64
-    st = (rng.standard_normal((R, 3, D)) * 0.05).astype(np.float32)
+    st = (rng.standard_normal((R, 3, D)) * 0.05).astype(np.float32); st[:, 2] = np.abs(st[:, 2])
     # gradient matrix that starts 4 bytes into its storage: not 16-byte aligned
     flat = torch.zeros(n * D + 1, device=dev)
     grad = (rng.standard_normal((n, D)) * 1e-2).astype(np.float32)
