@@ -9,7 +9,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 LIB_PATH = PKG / 'libsrm2_b200.so'
 
-_vp, _i64, _i32, _u32, _f32, _f64 = C.c_void_p, C.c_int64, C.c_int, C.c_uint32, C.c_float, C.c_double
+_vp, _i64, _i32, _u32, _f32, _f64, _sz = C.c_void_p, C.c_int64, C.c_int, C.c_uint32, C.c_float, C.c_double, C.c_size_t
 _f8 = C.POINTER(C.c_float)
 
 # name -> (restype, argtypes); must list every symbol of include/srm2_b200.h
@@ -21,6 +21,11 @@ SIGNATURES = {
     'srm2_adam_rows_f32': (C.c_int, [_vp, _vp, _i32, _vp, _i64, _i64, _f8, _vp]),
     'srm2_init_rows_f32': (C.c_int, [_vp, _vp, _i64, _i64, _u32, _f32, _vp]),
     'srm2_replay_rows_f32': (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _u32, _f32, _vp, _i64, _vp]),
+    'srm2_unique_scratch_bytes': (_sz, [_i64]),
+    'srm2_unique_inverse_i64': (C.c_int, [_vp, _i64, _i64, _vp, _i64, _vp, _vp, _vp, _sz, _vp]),
+    'srm2_segment_scratch_bytes': (_sz, [_i64, _i64, _i64]),
+    'srm2_segment_reduce_f32': (C.c_int, [_vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp, _sz, _vp]),
+    'srm2_reduce_adam_f32': (C.c_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _f8, _vp, _sz, _vp]),
 }
 
 _lib = None

@@ -1,0 +1,63 @@
+// Block-level scan helpers and a single-CTA exclusive scan kernel for the small integer arrays
+// (histograms, per-segment counts) that the dedup / sort / segment kernels produce.
+#pragma once
+#include "common.cuh"
+
+namespace srm2 {
+
+constexpr int kScanThreads = 1024;
+
+// Exclusive scan of one value per thread over a block of NT threads (NT multiple of 32, <= 1024).
+// Returns the exclusive prefix of `v`; *total (optional) receives the block sum.  `ws` is 33 words of shared memory.
+template <int NT>
+__device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* ws, uint32_t* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += t;
+  }
+  if (lane == 31) ws[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    uint32_t s = lane < NT / 32 ? ws[lane] : 0u;
+    uint32_t si = s;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t t = __shfl_up_sync(0xffffffffu, si, o);
+      if (lane >= o) si += t;
+    }
+    ws[lane] = si - s;                 // exclusive prefix of the warp sums
+    if (lane == 31) ws[32] = si;       // block total
+  }
+  __syncthreads();
+  const uint32_t res = ws[warp] + inc - v;
+  if (total) *total = ws[32];
+  __syncthreads();                     // ws may be reused by the caller
+  return res;
+}
+
+// out[i] = sum_{k<i} in[i]  for i < count (count read from *count_dev when count_dev != nullptr, else count_host);
+// count is clamped to count_cap (the allocated length); optionally out[count] = total and *total_out = total.  One CTA of kScanThreads threads; in == out allowed.
+static __global__ void __launch_bounds__(kScanThreads)
+srm2_scan_exclusive_u32_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out, int64_t count_host,
+                               const int64_t* __restrict__ count_dev, int64_t count_cap, int write_tail,
+                               uint32_t* __restrict__ total_out) {
+  __shared__ uint32_t ws[33];
+  int64_t count = count_dev ? *count_dev : count_host;
+  if (count > count_cap) count = count_cap;
+  const int64_t per = (count + kScanThreads - 1) / kScanThreads;
+  const int64_t lo = (int64_t)threadIdx.x * per, hi = lo + per < count ? lo + per : count;
+  uint32_t s = 0;
+  for (int64_t i = lo; i < hi; ++i) s += in[i];
+  uint32_t total;
+  uint32_t run = block_exclusive_scan<kScanThreads>(s, ws, &total);
+  for (int64_t i = lo; i < hi; ++i) { const uint32_t x = in[i]; out[i] = run; run += x; }
+  if (threadIdx.x == 0) {
+    if (write_tail) out[count] = total;
+    if (total_out) *total_out = total;
+  }
+}
+
+}  // namespace srm2

@@ -16,6 +16,7 @@
 #ifndef SRM2_B200_H
 #define SRM2_B200_H
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -75,6 +76,48 @@ int srm2_init_rows_f32(float* out, const int64_t* rows, int64_t n, int64_t D, ui
 int srm2_replay_rows_f32(float* out, const int64_t* rows, const float* logs, const int64_t* offs, const int32_t* steps,
                          const int32_t* cnt, int64_t n, int64_t D, int64_t K, uint32_t seed, float bound,
                          const float* table, int64_t table_rows, srm2_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Dedup of row ids from a bounded universe.  Replaces the driver's `torch.unique(ids, return_inverse=True)`
+ * (srm2/train.py:352; ids are global row ids in [0, R), srm2/train.py:205-214).
+ *   ids       [n] int64 in [0, n_rows)
+ *   uniq      [uniq_cap] int64: the distinct ids in ascending order (entries past the count are untouched;
+ *             ranks >= uniq_cap are dropped, so uniq_cap = min(n, n_rows) always suffices)
+ *   inv       [n] int64: index of ids[p] in uniq (-1 for an id outside [0, n_rows))
+ *   out_count [2] int64 (device): [0] = number of distinct ids, [1] = 1 if an id was out of range
+ *   scratch   srm2_unique_scratch_bytes(n_rows) bytes, 256-byte aligned; contents need not be preserved
+ * The result is a pure function of the input: no atomically assigned positions, no run-to-run variation.
+ */
+size_t srm2_unique_scratch_bytes(int64_t n_rows);
+int srm2_unique_inverse_i64(const int64_t* ids, int64_t n, int64_t n_rows, int64_t* uniq, int64_t uniq_cap, int64_t* inv,
+                            int64_t* out_count, void* scratch, size_t scratch_bytes, srm2_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Segment-reduce of per-lookup gradients.  Replaces the driver's
+ * `torch.ops.aten.embedding_dense_backward(grad, inv, n_unique, -1, False)` (srm2/train.py:429), in that
+ * operator's CUDA summation order (torch 2.11.0): see elara_b200/csrc/segreduce.cu.
+ *   grad [n,D] fp32 (D % 4 == 0, 16-byte aligned);  inv [n] int64 in [0, n_unique)
+ *   out  [n_unique, D] fp32; rows without lookups are zero
+ *   n_unique      host value, used when n_unique_dev == NULL
+ *   n_unique_dev  optional device int64: the count is read on the device (no host sync after a dedup);
+ *                 max_unique then bounds it and sizes the scratch
+ *   scratch       srm2_segment_scratch_bytes(n, max_unique or n_unique, D) bytes, 256-byte aligned
+ */
+size_t srm2_segment_scratch_bytes(int64_t n, int64_t max_unique, int64_t D);
+int srm2_segment_reduce_f32(const float* grad, const int64_t* inv, int64_t n, int64_t D, int64_t n_unique,
+                            const int64_t* n_unique_dev, int64_t max_unique, float* out, void* scratch,
+                            size_t scratch_bytes, srm2_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Segment-reduce fused with row-sparse Adam: the two reference calls
+ * `gW = embedding_dense_backward(...)` (srm2/train.py:429) and `gpu_adam(pool, slots, gW, ...)`
+ * (srm2/ops.py:59-67) in one pass; gW is never written.  Same bits as the two calls in sequence.
+ *   pool [C,3,D]; slots [n_unique] int64 distinct pool rows (slots[j] belongs to unique row j); other
+ *   arguments as in srm2_segment_reduce_f32 and srm2_adam_rows_f32.
+ */
+int srm2_reduce_adam_f32(float* pool, const int64_t* slots, const float* grad, const int64_t* inv, int64_t n, int64_t D,
+                         int64_t n_unique, const int64_t* n_unique_dev, int64_t max_unique, const float sc[8] /* host */,
+                         void* scratch, size_t scratch_bytes, srm2_stream_t stream);
 
 #ifdef __cplusplus
 }
