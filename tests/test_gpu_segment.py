@@ -32,7 +32,8 @@ def test_unique_inverse(dev, oracle, n, n_rows):
     from elara_b200.ops import unique_inverse
     rng = np.random.default_rng(n + n_rows)
     ids = np.minimum((rng.pareto(1.1, n) * 3).astype(np.int64), n_rows - 1)
-    ids[rng.random(n) < 0.3] = rng.integers(0, n_rows, (rng.random(n) < 0.3).sum()) if n else 0
+    mask = rng.random(n) < 0.3
+    ids[mask] = rng.integers(0, n_rows, int(mask.sum()))
     ids[:3] = [0, n_rows - 1, min(n_rows - 1, 131071)][:min(3, n)]
     u, inv = unique_inverse(torch.from_numpy(ids).to(dev), n_rows)
     ur, invr = oracle.unique_inverse(ids)
@@ -123,7 +124,8 @@ def test_reduce_adam_fused_equals_two_calls_and_oracle(dev, oracle, n, D, R):
     from elara_b200.gpu_ops import init_rows
     rng = np.random.default_rng(n)
     ids = np.minimum((rng.pareto(1.1, n) * 5).astype(np.int64), R - 1)
-    ids[rng.random(n) < 0.2] = rng.integers(0, R, (rng.random(n) < 0.2).sum())
+    mask = rng.random(n) < 0.2
+    ids[mask] = rng.integers(0, R, int(mask.sum()))
     pool_a = init_rows(torch.arange(R, device=dev), D, 42, 0.01)
     pool_b = pool_a.clone(); pool_c = pool_a.clone()
     st = pool_a.cpu().numpy().copy()

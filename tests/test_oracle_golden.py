@@ -76,6 +76,19 @@ def test_segment_reduce_orders(oracle):
     assert seq[0, 0] == np.float32(1e8) and chk[0, 0] == np.float32(1e8) + np.float32(10.0)
 
 
+def test_segment_reduce_golden(oracle, golden_dir):
+    """Vectors produced on a B200 by PyTorch's CUDA aten.embedding_dense_backward (tests/golden/make_segreduce_golden.py);
+    cases where that operator's default mode is not run-to-run deterministic hold its deterministic-mode output."""
+    g = np.load(golden_dir / 'segreduce_cuda.npz')
+    assert str(g['torch_version']).startswith('2.11')
+    small = large = unstable = 0
+    for ci in range(int(g['n_cases'])):
+        grad, inv, nu = g[f'c{ci}_grad'], g[f'c{ci}_inv'], int(g[f'c{ci}_nu'])
+        assert eq_bits(oracle.segment_reduce(grad, inv, nu), g[f'c{ci}_out']), ci
+        small += len(inv) <= 3072; large += len(inv) > 3072; unstable += not bool(g[f'c{ci}_default_mode_stable'])
+    assert small > 10 and large > 5 and unstable > 0
+
+
 DIR_OUT_A = ('L_steps', 'L_ids', 'hrec_dyn', 'hrec_j', 'ev_row', 'rep', 'evl_ids', 'evf_slots', 'ev_dyn')
 
 
