@@ -1,0 +1,337 @@
+"""Benchmark of the sparse-optimizer hot path: dedup -> segment-reduce -> row-sparse Adam, one step per batch.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--rows R] [--batch B]
+
+N = 1: the DLRM-shaped sparse step (26 fp32 tables, d = 128, 33.8 M rows in total = 51.9 GB of (w, m, v); 8192 x 26
+       single-hot power-law lookups per step), seeded synthetic inputs.
+N > 1: the row-sharded variant (launched under torchrun, one rank per GPU): 25 M rows and 8192 x 26 lookups PER GPU
+       (200 M rows and 65,536 x 26 lookups at N = 8), rows owned by row_id mod N, lookups routed with an NCCL all-to-all.
+       Per-GPU work is fixed, so this is weak scaling.
+
+Prints ONE JSON line on rank 0.  `value` = unique rows updated per second over all GPUs with the inputs already in
+HBM; `e2e` = the same through host buffers (H2D of ids and gradients, D2H of the step's row count, every step).
+`--impl reference` times the reference's CPU path (torch.unique + aten.embedding_dense_backward on CPU tensors + its
+C++ cpu_adam with all host threads) on the same inputs, on a table compacted to the rows a step touches.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+HYP = (1e-3, 0.9, 0.999, 1e-8)
+D = 128
+N_TABLES = 26
+SEED = 42
+ALPHA = 1.1
+
+
+def peaks():
+    f = ROOT / 'MEASURED_PEAKS.json'
+    if f.exists():
+        return float(json.load(open(f))['hbm_gbs']), 'measured'
+    return 6650.0, 'fallback'
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled every 200 ms while the timed region runs."""
+    Q = ('clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,'
+         'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, index=0):
+        self.p = None
+        try:
+            self.p = subprocess.Popen(['nvidia-smi', f'--id={index}', f'--query-gpu={self.Q}', '--format=csv,noheader,nounits',
+                                       '-lms', '200'], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.p = None
+
+    def stop(self):
+        if self.p is None:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
+        time.sleep(0.25)
+        self.p.terminate()
+        out = self.p.communicate()[0]
+        sm, mx, reasons = [], [], set()
+        for line in out.splitlines():
+            f = [x.strip() for x in line.split(',')]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, v in zip(('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap'), f[2:6]):
+                if v.lower().startswith('active'):
+                    reasons.add(name)
+        return {'sm_mhz': float(np.median(sm)) if sm else None, 'sm_max_mhz': max(mx) if mx else None, 'reasons': sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------------ workload
+def workload(world, rows_per_gpu, batch_per_gpu):
+    from elara_b200 import synth
+    total_rows = rows_per_gpu * world
+    sizes, offs = synth.table_sizes(total_rows, N_TABLES, seed=SEED)
+    return total_rows, sizes, offs
+
+
+def step_ids(sizes, offs, batch_per_gpu, world, rank, step):
+    """This rank's slice of the global batch of `step`: samples [rank*B, (rank+1)*B) -> ids [B*26] (sample-major)."""
+    from elara_b200 import synth
+    return synth.zipf_lookups(sizes, offs, batch_per_gpu, ALPHA, SEED, step, first_sample=rank * batch_per_gpu)
+
+
+# ------------------------------------------------------------------------------------------------ reference arm
+def cpu_reference_step_fn(total_rows):
+    """One step of the reference's CPU path on a table compacted to the touched rows.  Returns (fn, kind, cores)."""
+    import torch
+    from oracle import oracle as O
+    E = O.ref_cpu()
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    kind = 'reference' if E is not None else 'port'
+
+    def fn(ids_np, grad_t, state, step):
+        ids = torch.from_numpy(ids_np)
+        u, inv = torch.unique(ids, return_inverse=True)
+        gW = torch.ops.aten.embedding_dense_backward(grad_t, inv, u.numel(), -1, False)
+        rows = torch.arange(u.numel())                      # compacted table: row j <-> unique row j
+        if E is not None:
+            E.cpu_adam(state[:u.numel()], rows, gW, *HYP, step, cores)
+        else:
+            O.adam_rows(state[:u.numel()].numpy(), rows.numpy(), gW.numpy(), *HYP, step, nthreads=cores)
+        return u.numel()
+    return fn, kind, cores
+
+
+def run_reference(a, world, rank):
+    import torch
+    if rank != 0:
+        return None
+    total_rows, sizes, offs = workload(world, a.rows, a.batch)
+    fn, kind, cores = cpu_reference_step_fn(total_rows)
+    n = a.batch * N_TABLES
+    g = torch.Generator().manual_seed(SEED)
+    grads = [torch.randn(n, D, generator=g) * 1e-3 for _ in range(2)]
+    state = torch.zeros(n, 3, D)
+    state[:, 0].uniform_(-0.01, 0.01, generator=g)
+    ids = [step_ids(sizes, offs, a.batch, world, 0, s + 1) for s in range(a.warmup + a.steps)]
+    for s in range(a.warmup):
+        fn(ids[s], grads[s % 2], state, s + 1)
+    rows = 0
+    t0 = time.perf_counter()
+    for s in range(a.warmup, a.warmup + a.steps):
+        rows += fn(ids[s], grads[s % 2], state, s + 1)
+    dt = time.perf_counter() - t0
+    val = rows / dt
+    sample = (f'{a.steps} steps of one GPU\'s share of the batch ({a.batch}x{N_TABLES} lookups, d={D}) on a table compacted to the '
+              f'rows each step touches; torch.unique + aten.embedding_dense_backward (CPU) + ' +
+              ('the reference\'s C++ cpu_adam' if kind == 'reference' else 'the C port of cpu_adam'))
+    return {'metric': 'sparse_adam_updated_rows_per_s', 'value': val, 'unit': 'rows/s', 'n_gpus': world, 'steps': a.steps,
+            'warmup': a.warmup, 'ms_per_step': dt / a.steps * 1e3, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
+            'dtype': 'f32', 'data': 'synthetic', 'impl': 'reference',
+            'config': config_dict(a, world, total_rows),
+            'cpu_baseline': {'value': val, 'unit': 'rows/s', 'cores': cores, 'kind': kind, 'sample': sample},
+            'e2e': {'value': val, 'unit': 'rows/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0}, 'gpu_launches': 0}
+
+
+def config_dict(a, world, total_rows):
+    name = ('dlrm_sparse_step: 26 fp32 tables, d=128, 33.8M rows, batch 8192x26 Zipf(1.1) lookups, dedup+segment-reduce+Adam'
+            if world == 1 and a.rows == 33_800_000 else
+            f'row-sharded sparse step: 26 fp32 tables, d=128, {total_rows / 1e6:.1f}M rows by row_id mod {world}, '
+            f'global batch {a.batch * world}x26 Zipf(1.1) lookups, NCCL all-to-all routing')
+    return {'workload': name, 'rows_total': int(total_rows), 'rows_per_gpu': int(a.rows), 'lookups_per_step': int(a.batch * N_TABLES * world),
+            'd': D, 'tables': N_TABLES, 'hyper': {'lr': HYP[0], 'b1': HYP[1], 'b2': HYP[2], 'eps': HYP[3]},
+            'parallelism': f'row-shard x{world}' if world > 1 else 'single GPU',
+            'l2_policy': 'inputs larger than L2: table of tens of GB gathered at random rows; gradient buffers rotate over 4 x 109 MB'}
+
+
+# ------------------------------------------------------------------------------------------------ our arm
+def run_ours(a, world, rank, local_rank):
+    import torch
+    import torch.distributed as dist
+    from elara_b200 import _lib, ops
+    from elara_b200.gpu_ops import init_rows
+    from elara_b200.sharded import ShardedSparseAdam
+
+    dev = torch.device('cuda', local_rank)
+    torch.cuda.set_device(dev)
+    L = _lib.lib()
+    total_rows, sizes, offs = workload(world, a.rows, a.batch)
+    n = a.batch * N_TABLES
+    bound = float(np.sqrt(1.0 / sizes.max()))
+    eng = ShardedSparseAdam(total_rows, D, world, rank, dev, seed=SEED, bound=bound, hyper=HYP,
+                            max_lookups_per_rank=n, group=dist.group.WORLD if world > 1 else None)
+    nsteps = a.warmup + a.steps
+    ids_np = [step_ids(sizes, offs, a.batch, world, rank, s + 1) for s in range(nsteps)]
+    ids_dev = [torch.from_numpy(x).to(dev) for x in ids_np]
+    gen = torch.Generator(device=dev).manual_seed(SEED + rank)
+    NBUF = 4
+    grads_dev = [torch.randn(n, D, device=dev, generator=gen) * 1e-3 for _ in range(NBUF)]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    # ---- device-resident timing (value) ----
+    for s in range(a.warmup):
+        eng.step(ids_dev[s], grads_dev[s % NBUF], s + 1)
+    ev_pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(a.steps)]
+    for e0, e1 in ev_pairs:
+        e0.record(); e1.record()              # materialise the handles
+    barrier()
+    launches0 = L.srm2_launch_count()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    t_begin = torch.cuda.Event(enable_timing=True); t_end = torch.cuda.Event(enable_timing=True)
+    counts = []
+    t_begin.record()
+    for k, s in enumerate(range(a.warmup, nsteps)):
+        L.srm2_stage_events(ev_pairs[k][0].cuda_event, ev_pairs[k][1].cuda_event)
+        counts.append(eng.step(ids_dev[s], grads_dev[s % NBUF], s + 1))
+    L.srm2_stage_events(None, None)
+    t_end.record()
+    barrier()
+    ms = t_begin.elapsed_time(t_end)
+    launches = L.srm2_launch_count() - launches0
+    clocks = sampler.stop() if sampler else None
+    rows_local = int(sum(int(c[0]) for c in counts))
+    lookups_local = eng.last_local_lookups_total
+    stage_ms = [e0.elapsed_time(e1) for e0, e1 in ev_pairs]
+
+    # ---- end-to-end timing (host buffers) ----
+    h_ids = [torch.from_numpy(x).pin_memory() for x in ids_np[a.warmup:]]
+    h_grads = [g.cpu().pin_memory() for g in grads_dev[:2]]
+    d_ids = torch.empty(n, dtype=torch.int64, device=dev); d_grad = torch.empty(n, D, device=dev)
+    h_count = torch.zeros(2, dtype=torch.int64).pin_memory()
+    e2e_steps = min(a.steps, 10)
+    for k in range(2):                         # warm-up of the copy path
+        d_ids.copy_(h_ids[k % len(h_ids)], non_blocking=True); d_grad.copy_(h_grads[k % 2], non_blocking=True)
+        eng.step(d_ids, d_grad, nsteps + 1 + k)
+    barrier()
+    e_rows = 0
+    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for k in range(e2e_steps):
+        d_ids.copy_(h_ids[k], non_blocking=True)
+        d_grad.copy_(h_grads[k % 2], non_blocking=True)
+        c = eng.step(d_ids, d_grad, nsteps + 3 + k, defer=True)
+        h_count.copy_(c, non_blocking=True)
+        torch.cuda.current_stream(dev).synchronize()          # the step's result is read on the host every step
+        e_rows += int(h_count[0])
+    t1.record()
+    barrier()
+    e_ms = t0.elapsed_time(t1)
+
+    # ---- gather over ranks: max time, sum rows ----
+    stats = torch.tensor([ms, e_ms, float(rows_local), float(e_rows), float(np.mean(stage_ms)), float(launches)], dtype=torch.float64, device=dev)
+    if world > 1:
+        mx = stats.clone(); dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stats.clone(); dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        ms, e_ms, stage = float(mx[0]), float(mx[1]), float(mx[4])
+        rows, e_rows_all, launches_all = float(sm[2]), float(sm[3]), float(sm[5])
+    else:
+        stage = float(stats[4]); rows, e_rows_all, launches_all = float(rows_local), float(e_rows), float(launches)
+    if rank != 0:
+        return None
+    value = rows / (ms * 1e-3)
+    peak, peak_kind = peaks()
+    # roofline of the dominant stage (run sums + Adam kernels of the fused reduce), per GPU, this rank's launch
+    lookups_stage = eng.last_local_lookups
+    uniq_stage = rows_local / a.steps
+    alg_bytes = lookups_stage * (D * 4 + 8) + uniq_stage * (6 * D * 4 + 8)
+    achieved = alg_bytes / (float(np.mean(stage_ms)) * 1e-3) / 1e9
+    traffic = None
+    tf = ROOT / 'profiles' / 'traffic.json'
+    if tf.exists():
+        try:
+            t = json.load(open(tf))
+            traffic = t['dram_bytes_per_lookup'] * lookups_stage + t['dram_bytes_per_unique_row'] * uniq_stage
+        except Exception:
+            traffic = None
+    out = {'metric': 'sparse_adam_updated_rows_per_s', 'value': value, 'unit': 'rows/s', 'n_gpus': world, 'steps': a.steps, 'warmup': a.warmup,
+           'ms_per_step': ms / a.steps, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+           'config': config_dict(a, world, total_rows),
+           'roofline': {'bound': 'hbm', 'achieved': achieved, 'peak': peak, 'unit': 'GB/s', 'frac': achieved / peak, 'traffic': traffic,
+                        'kernel': 'srm2_segment_runsum_kernel + srm2_segment_final_kernel (fused reduce+Adam stage)',
+                        'peak_source': f'{peak_kind} (MEASURED_PEAKS.json hbm_gbs)' if peak_kind == 'measured' else 'fallback 6650 GB/s',
+                        'stage_us': float(np.mean(stage_ms)) * 1e3, 'algorithmic_bytes_per_launch': alg_bytes},
+           'e2e': {'value': e_rows_all / (e_ms * 1e-3), 'unit': 'rows/s', 'h2d_bytes_per_step': int(n * 8 + n * D * 4) * world,
+                   'd2h_bytes_per_step': 16 * world, 'steps': e2e_steps},
+           'gpu_launches': int(launches_all), 'clocks': clocks,
+           'rows_updated_per_step': rows / a.steps, 'lookups_per_step_per_gpu': n}
+    return out
+
+
+def add_cpu_baseline(out, a):
+    """Reference CPU path timed on this box's host cores on a bounded sample (N = 1 only)."""
+    import torch
+    total_rows, sizes, offs = workload(1, a.rows, a.batch)
+    fn, kind, cores = cpu_reference_step_fn(total_rows)
+    n = a.batch * N_TABLES
+    g = torch.Generator().manual_seed(SEED)
+    grad = torch.randn(n, D, generator=g) * 1e-3
+    state = torch.zeros(n, 3, D); state[:, 0].uniform_(-0.01, 0.01, generator=g)
+    ids = [step_ids(sizes, offs, a.batch, 1, 0, s + 1) for s in range(6)]
+    fn(ids[0], grad, state, 1)
+    rows = 0; steps = 0
+    t0 = time.perf_counter()
+    while steps < 5 or (time.perf_counter() - t0 < 8.0 and steps < 400):
+        rows += fn(ids[steps % 6], grad, state, steps + 2); steps += 1
+    dt = time.perf_counter() - t0
+    out['cpu_baseline'] = {'value': rows / dt, 'unit': 'rows/s', 'cores': cores, 'kind': kind,
+                           'sample': f'{steps} steps of the same workload ({n} lookups, d={D}) on a table compacted to the touched rows: torch.unique + '
+                                     f'aten.embedding_dense_backward on CPU tensors + ' + ('the reference\'s C++ cpu_adam' if kind == 'reference' else 'C port of cpu_adam')}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=20)
+    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--rows', type=int, default=0, help='rows per GPU (default: 33.8M at 1 GPU, 25M per GPU above)')
+    ap.add_argument('--batch', type=int, default=8192, help='samples per GPU per step (x26 lookups)')
+    ap.add_argument('--no-cpu-baseline', action='store_true')
+    a = ap.parse_args()
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+    if a.gpus != world and world == 1 and a.gpus > 1:
+        # started without torchrun: re-launch under it
+        cmd = [sys.executable, '-m', 'torch.distributed.run', '--nnodes=1', f'--nproc-per-node={a.gpus}', '--master-addr', '127.0.0.1',
+               '--master-port', str(29500 + os.getpid() % 500)] + sys.argv
+        sys.exit(subprocess.call(cmd))
+    a.warmup = max(a.warmup, 3) if a.impl == 'ours' else a.warmup
+    if a.rows == 0:
+        a.rows = 33_800_000 if world == 1 else 25_000_000
+    if a.impl == 'reference':
+        out = run_reference(a, world, rank)
+        if out is not None:
+            print(json.dumps(out), flush=True)
+        return
+    import torch
+    import torch.distributed as dist
+    if world > 1:
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group('nccl', device_id=torch.device('cuda', local_rank))
+    out = run_ours(a, world, rank, local_rank)
+    if out is not None:
+        if world == 1 and not a.no_cpu_baseline:
+            add_cpu_baseline(out, a)
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == '__main__':
+    main()

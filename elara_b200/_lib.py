@@ -17,6 +17,8 @@ SIGNATURES = {
     'srm2_version': (C.c_int, []),
     'srm2_status_string': (C.c_char_p, [C.c_int]),
     'srm2_last_cuda_error': (C.c_char_p, []),
+    'srm2_launch_count': (C.c_int64, []),
+    'srm2_stage_events': (C.c_int, [_vp, _vp]),
     'srm2_adam_scalars': (C.c_int, [_f64, _f64, _f64, _f64, _i64, _f8]),
     'srm2_adam_rows_f32': (C.c_int, [_vp, _vp, _i32, _vp, _i64, _i64, _f8, _vp]),
     'srm2_init_rows_f32': (C.c_int, [_vp, _vp, _i64, _i64, _u32, _f32, _vp]),
@@ -24,8 +26,10 @@ SIGNATURES = {
     'srm2_unique_scratch_bytes': (_sz, [_i64]),
     'srm2_unique_inverse_i64': (C.c_int, [_vp, _i64, _i64, _vp, _i64, _vp, _vp, _vp, _sz, _vp]),
     'srm2_segment_scratch_bytes': (_sz, [_i64, _i64, _i64]),
-    'srm2_segment_reduce_f32': (C.c_int, [_vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp, _sz, _vp]),
-    'srm2_reduce_adam_f32': (C.c_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _f8, _vp, _sz, _vp]),
+    'srm2_segment_reduce_f32': (C.c_int, [_vp, _vp, _i64, _i64, _i64, _vp, _i64, _i32, _vp, _vp, _sz, _vp]),
+    'srm2_reduce_adam_f32': (C.c_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _i32, _f8, _vp, _sz, _vp]),
+    'srm2_route_scratch_bytes': (_sz, [_i64, _i64]),
+    'srm2_route_by_owner': (C.c_int, [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _sz, _vp]),
 }
 
 _lib = None

@@ -13,7 +13,13 @@ constexpr int kSMs = 148;
 // Records a CUDA runtime error for srm2_last_cuda_error(); returns SRM2_ERR_CUDA or SRM2_OK.
 int note_cuda(cudaError_t e);
 
-inline int launch_status() { return note_cuda(cudaGetLastError()); }
+// Kernel-launch bookkeeping for srm2_launch_count(): k kernels were just enqueued.
+void add_launches(int k);
+inline int launch_status(int k = 1) { add_launches(k); return note_cuda(cudaGetLastError()); }
+
+// Optional instrumentation (srm2_stage_events): events recorded around the gradient-streaming stage of a pipeline.
+void stage_begin(cudaStream_t st);
+void stage_end(cudaStream_t st);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

@@ -162,5 +162,5 @@ extern "C" int srm2_unique_inverse_i64(const int64_t* ids, int64_t n, int64_t n_
   srm2_unique_count_kernel<<<(unsigned)s.nblocks, kDT, 0, st>>>(s.bitmap, s.bsum, s.counter, s.nblocks, out_count);
   srm2_unique_emit_kernel<<<(unsigned)s.nblocks, kDT, 0, st>>>(s.bitmap, s.bsum, s.wprefix, uniq, uniq_cap);
   if (n > 0) srm2_unique_inverse_kernel<<<grid_n, kDT, 0, st>>>(ids, n, n_rows, s.bitmap, s.wprefix, inv);
-  return launch_status();
+  return launch_status(n > 0 ? 4 : 2);
 }

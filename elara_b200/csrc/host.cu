@@ -1,4 +1,5 @@
 // Host-side entry points: library identification, status text, Adam scalars.
+#include <atomic>
 #include <cmath>
 #include <cstring>
 
@@ -15,9 +16,24 @@ int note_cuda(cudaError_t e) {
   return SRM2_ERR_CUDA;
 }
 
+static std::atomic<int64_t> g_launches{0};
+void add_launches(int k) { g_launches.fetch_add(k, std::memory_order_relaxed); }
+
+static thread_local cudaEvent_t g_ev_begin = nullptr, g_ev_end = nullptr;
+void stage_begin(cudaStream_t st) { if (g_ev_begin) note_cuda(cudaEventRecord(g_ev_begin, st)); }
+void stage_end(cudaStream_t st) { if (g_ev_end) note_cuda(cudaEventRecord(g_ev_end, st)); }
+
 }  // namespace srm2
 
 extern "C" int srm2_version(void) { return 100; }
+
+extern "C" int64_t srm2_launch_count(void) { return srm2::g_launches.load(std::memory_order_relaxed); }
+
+extern "C" int srm2_stage_events(void* begin, void* end) {
+  srm2::g_ev_begin = static_cast<cudaEvent_t>(begin);
+  srm2::g_ev_end = static_cast<cudaEvent_t>(end);
+  return SRM2_OK;
+}
 
 extern "C" const char* srm2_status_string(int status) {
   switch (status) {

@@ -1,0 +1,92 @@
+// Owner routing for row-sharded tables: lookups are grouped by owner rank (row_id mod world), keeping their order
+// inside each group, and their gradient rows are gathered into one contiguous send buffer per owner.
+//
+// Stability matters: every owner later sums the lookups of a row in ascending GLOBAL lookup position; ranks hold
+// consecutive slices of the batch, so a stable grouping on every rank plus concatenation in rank order on the owner
+// reproduces the single-process order without shipping positions.
+// Kernels: one stable counting pass of the radix sort (histogram, scan, scatter; world <= 2048 owners) and a row gather
+// that streams each gradient row once (D*4 bytes read + written per lookup, HBM bound).
+#include "common.cuh"
+#include "scan.cuh"
+#include "sort.cuh"
+
+namespace srm2 {
+
+// out_lid[i] = ids[perm[i]] / world, out_grad[i,:] = grad[perm[i],:]; one thread per 16-byte lane.
+__global__ void __launch_bounds__(256)
+srm2_route_gather_kernel(const int64_t* __restrict__ ids, const float* __restrict__ grad, const uint32_t* __restrict__ perm,
+                         int64_t n, int lpr, int shift, int D, int world, int64_t* __restrict__ out_lid,
+                         float* __restrict__ out_grad) {
+  const int64_t items = n * lpr;
+  for (int64_t t = (int64_t)blockIdx.x * 256 + threadIdx.x; t < items; t += (int64_t)gridDim.x * 256) {
+    int64_t i; int j4;
+    if (shift >= 0) { i = t >> shift; j4 = (int)(t & (lpr - 1)); } else { i = t / lpr; j4 = (int)(t - i * lpr); }
+    const uint32_t p = perm[i];
+    const float4 g = ld_stream4(grad + (int64_t)p * D + j4 * 4);
+    st_stream4(out_grad + t * 4, g);
+    if (j4 == 0) { const int64_t id = ids[p]; out_lid[i] = id < 0 ? -1 : id / world; }
+  }
+}
+
+// counts[o] = number of lookups owned by rank o, from the scanned digit-major histogram of the single sort pass.
+__global__ void srm2_route_counts_kernel(const uint32_t* __restrict__ hist_scanned, int tiles, int world, int64_t n,
+                                         int64_t* __restrict__ counts) {
+  const int o = blockIdx.x * blockDim.x + threadIdx.x;
+  if (o >= world) return;
+  const uint32_t lo = hist_scanned[(int64_t)o * tiles];
+  const int64_t hi = (o + 1 < world) ? (int64_t)hist_scanned[(int64_t)(o + 1) * tiles] : n;
+  counts[o] = hi - (int64_t)lo;
+}
+
+static size_t align_up_r(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+static int route_bits(int64_t world) { int b = 1; while (((int64_t)1 << b) < world) ++b; return b; }
+
+static size_t route_layout(int64_t n, int64_t world, char* base, SortBuffers* sb) {
+  const int tiles = sort_tiles(n > 0 ? n : 1);
+  const int bits = route_bits(world);
+  size_t off = 0;
+  auto take = [&](size_t bytes) { size_t o = off; off = align_up_r(off + bytes, 256); return o; };
+  const size_t nn = (size_t)(n > 0 ? n : 1);
+  const size_t o_ka = take(nn * 4), o_va = take(nn * 4), o_h = take(((size_t)tiles * ((size_t)1 << bits) + 1) * 4);
+  if (sb) {
+    auto u = [&](size_t o) { return reinterpret_cast<uint32_t*>(base + o); };
+    sb->keyA = u(o_ka); sb->valA = u(o_va); sb->keyB = nullptr; sb->valB = nullptr; sb->hist = u(o_h); sb->tiles = tiles;
+  }
+  return off;
+}
+
+}  // namespace srm2
+
+extern "C" size_t srm2_route_scratch_bytes(int64_t n, int64_t world) {
+  if (n < 0 || world < 1) return 0;
+  return srm2::route_layout(n, world, nullptr, nullptr);
+}
+
+extern "C" int srm2_route_by_owner(const int64_t* ids, const float* grad, int64_t n, int64_t D, int64_t world,
+                                   int64_t* out_lid, float* out_grad, int64_t* out_counts, void* scratch,
+                                   size_t scratch_bytes, srm2_stream_t stream) {
+  using namespace srm2;
+  if (n < 0 || D <= 0 || world < 1 || out_counts == nullptr) return SRM2_ERR_ARG;
+  if (n > 0 && (ids == nullptr || grad == nullptr || out_lid == nullptr || out_grad == nullptr)) return SRM2_ERR_ARG;
+  if ((D & 3) != 0 || world > (1 << kMaxRadixBits) || n >= ((int64_t)1 << 31)) return SRM2_ERR_UNSUPPORTED;
+  if (n > 0 && (!aligned16(grad) || !aligned16(out_grad))) return SRM2_ERR_UNSUPPORTED;
+  if (scratch == nullptr || !aligned16(scratch) || scratch_bytes < route_layout(n, world, nullptr, nullptr)) return SRM2_ERR_SCRATCH;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (n == 0) {
+    if (note_cuda(cudaMemsetAsync(out_counts, 0, (size_t)world * 8, st))) return SRM2_ERR_CUDA;
+    return SRM2_OK;
+  }
+  SortBuffers sb;
+  route_layout(n, world, static_cast<char*>(scratch), &sb);
+  const uint32_t *skey = nullptr, *perm = nullptr;
+  const int rc = radix_sort_by_key(ids, n, (int)world, 0, route_bits(world), 1, sb, &skey, &perm, st);
+  if (rc != SRM2_OK) return rc;
+  srm2_route_counts_kernel<<<(unsigned)((world + 255) / 256), 256, 0, st>>>(sb.hist, sb.tiles, (int)world, n, out_counts);
+  const int lpr = (int)(D / 4);
+  const int shift = (lpr & (lpr - 1)) == 0 ? __builtin_ctz(lpr) : -1;
+  const int64_t items = n * lpr;
+  const int grid = (int)((items + 255) / 256 < (int64_t)kSMs * 16 ? (items + 255) / 256 : (int64_t)kSMs * 16);
+  srm2_route_gather_kernel<<<grid, 256, 0, st>>>(ids, grad, perm, n, lpr, shift, (int)D, (int)world, out_lid, out_grad);
+  return launch_status(5);
+}

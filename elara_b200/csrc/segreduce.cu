@@ -18,97 +18,13 @@
 // Gradient rows are read exactly once (D*4 bytes per lookup); everything else is small integer traffic.
 #include "common.cuh"
 #include "scan.cuh"
+#include "sort.cuh"
 
 namespace srm2 {
 
 constexpr int kRun = 10;            // lookups per run (large inputs)
 constexpr int kSmallN = 3072;       // inputs up to this many lookups use the windowed order
 constexpr int kWindow = 32;
-
-// ------------------------------------------------------------------------------------------ radix sort
-constexpr int kSortThreads = 256;
-constexpr int kSortWarps = kSortThreads / 32;
-constexpr int kSortRounds = 16;                              // elements per thread
-constexpr int kSortTile = kSortThreads * kSortRounds;        // 4096 elements per CTA
-constexpr int kMaxRadixBits = 11;
-
-// An inverse index outside [0, cap) sorts as `cap`, behind every real row.
-__device__ __forceinline__ uint32_t clamp_key(int64_t k, int64_t cap) { return (k < 0 || k >= cap) ? (uint32_t)cap : (uint32_t)k; }
-
-// Histogram of one digit per tile; hist is digit-major: hist[d * tiles + tile].
-// Pass 0 reads the keys from the int64 inverse array (key_lo == nullptr), later passes from the u32 ping-pong buffer.
-__global__ void __launch_bounds__(kSortThreads)
-srm2_sort_hist_kernel(const int64_t* __restrict__ key64, const uint32_t* __restrict__ key32, int64_t n, int shift, int bits,
-                      uint32_t* __restrict__ hist, int tiles, int64_t cap) {
-  extern __shared__ uint32_t sh[];
-  const int bins = 1 << bits;
-  for (int b = threadIdx.x; b < bins; b += kSortThreads) sh[b] = 0;
-  __syncthreads();
-  const int64_t base = (int64_t)blockIdx.x * kSortTile;
-#pragma unroll 4
-  for (int r = 0; r < kSortRounds; ++r) {
-    const int64_t i = base + r * kSortThreads + threadIdx.x;
-    if (i < n) {
-      const uint32_t k = key64 ? clamp_key(key64[i], cap) : key32[i];
-      atomicAdd(&sh[(k >> shift) & (bins - 1)], 1u);
-    }
-  }
-  __syncthreads();
-  for (int b = threadIdx.x; b < bins; b += kSortThreads) hist[(int64_t)b * tiles + blockIdx.x] = sh[b];
-}
-
-// Stable scatter of one tile.  Warp w owns elements [w*512, (w+1)*512) of the tile and walks them in rounds of 32
-// consecutive elements; __match_any_sync groups equal digits of a round, so the rank of an element among the equal
-// digits of its warp's sub-range is (count so far) + (equal digits in lower lanes).  Warp counts are then scanned
-// across the warps of the tile and added to the tile's global digit offset.
-__global__ void __launch_bounds__(kSortThreads)
-srm2_sort_scatter_kernel(const int64_t* __restrict__ key64, const uint32_t* __restrict__ key32,
-                         const uint32_t* __restrict__ val32, int64_t n, int shift, int bits,
-                         const uint32_t* __restrict__ hist_scanned, int tiles, uint32_t* __restrict__ out_key,
-                         uint32_t* __restrict__ out_val, int64_t cap) {
-  extern __shared__ uint32_t sh[];                 // [kSortWarps][bins]
-  const int bins = 1 << bits;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int b = threadIdx.x; b < bins * kSortWarps; b += kSortThreads) sh[b] = 0;
-  __syncthreads();
-  uint32_t* cnt = sh + warp * bins;
-  const int64_t base = (int64_t)blockIdx.x * kSortTile + (int64_t)warp * (32 * kSortRounds);
-  uint32_t key[kSortRounds], val[kSortRounds], rnk[kSortRounds];
-#pragma unroll
-  for (int r = 0; r < kSortRounds; ++r) {
-    const int64_t i = base + r * 32 + lane;
-    const bool ok = i < n;
-    const unsigned act = __ballot_sync(0xffffffffu, ok);
-    if (ok) {
-      key[r] = key64 ? clamp_key(key64[i], cap) : key32[i];
-      val[r] = val32 ? val32[i] : (uint32_t)i;
-      const uint32_t d = (key[r] >> shift) & (bins - 1);
-      const unsigned m = __match_any_sync(act, d);
-      const int leader = __ffs(m) - 1;
-      uint32_t old = 0;
-      if (lane == leader) { old = cnt[d]; cnt[d] = old + __popc(m); }
-      old = __shfl_sync(m, old, leader);
-      rnk[r] = old + __popc(m & ((1u << lane) - 1u));
-    }
-  }
-  __syncthreads();
-  // exclusive scan of the warp counts across warps, per digit, plus the tile's global offset
-  for (int b = threadIdx.x; b < bins; b += kSortThreads) {
-    uint32_t run = hist_scanned[(int64_t)b * tiles + blockIdx.x];
-#pragma unroll
-    for (int w = 0; w < kSortWarps; ++w) { const uint32_t c = sh[w * bins + b]; sh[w * bins + b] = run; run += c; }
-  }
-  __syncthreads();
-#pragma unroll
-  for (int r = 0; r < kSortRounds; ++r) {
-    const int64_t i = base + r * 32 + lane;
-    if (i < n) {
-      const uint32_t d = (key[r] >> shift) & (bins - 1);
-      const uint32_t dst = cnt[d] + rnk[r];
-      out_key[dst] = key[r]; out_val[dst] = val[r];
-    }
-  }
-}
 
 // ------------------------------------------------------------------------------------------ segments
 // seg_start[j] = number of sorted keys below j (lower bound), for j in [0, nu]; a row without lookups gets an empty
@@ -299,10 +215,10 @@ static size_t seg_layout(int64_t n, int64_t cap, int64_t D, char* base, SegScrat
   return off;
 }
 
-static int segment_pipeline(bool fused, const float* grad, const int64_t* inv, int64_t n, int64_t D, int64_t nu_host,
+static int segment_pipeline(bool fused, int order, const float* grad, const int64_t* inv, int64_t n, int64_t D, int64_t nu_host,
                             const int64_t* nu_dev, int64_t cap, float* out, float* pool, const int64_t* slots,
                             const float* sc, void* scratch, size_t scratch_bytes, cudaStream_t st) {
-  if (n < 0 || D <= 0 || cap < 0 || (nu_host < 0 && nu_dev == nullptr)) return SRM2_ERR_ARG;
+  if (n < 0 || D <= 0 || cap < 0 || (nu_host < 0 && nu_dev == nullptr) || order < 0 || order > 2) return SRM2_ERR_ARG;
   if (nu_dev == nullptr) cap = nu_host;
   if (cap == 0) return SRM2_OK;
   if (n > 0 && (grad == nullptr || inv == nullptr)) return SRM2_ERR_ARG;
@@ -318,22 +234,9 @@ static int segment_pipeline(bool fused, const float* grad, const int64_t* inv, i
   // 1. sort (key = inv, value = position)
   const uint32_t *skey = nullptr, *spos = nullptr;
   if (n > 0) {
-    const size_t sm_hist = ((size_t)1 << s.bits) * 4, sm_scat = sm_hist * kSortWarps;
-    if (sm_scat > 48 * 1024 &&
-        note_cuda(cudaFuncSetAttribute(srm2_sort_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm_scat)))
-      return SRM2_ERR_CUDA;
-    uint32_t *ko = s.keyA, *vo = s.valA, *ki = nullptr, *vi = nullptr;
-    for (int p = 0; p < s.passes; ++p) {
-      const int shiftp = p * s.bits;
-      srm2_sort_hist_kernel<<<s.tiles, kSortThreads, sm_hist, st>>>(p == 0 ? inv : nullptr, ki, n, shiftp, s.bits, s.hist, s.tiles, cap);
-      srm2_scan_exclusive_u32_kernel<<<1, kScanThreads, 0, st>>>(s.hist, s.hist, (int64_t)s.tiles << s.bits, nullptr,
-                                                                 (int64_t)s.tiles << s.bits, 0, nullptr);
-      srm2_sort_scatter_kernel<<<s.tiles, kSortThreads, sm_scat, st>>>(p == 0 ? inv : nullptr, ki, vi, n, shiftp, s.bits, s.hist,
-                                                                      s.tiles, ko, vo, cap);
-      ki = ko; vi = vo;
-      ko = (ko == s.keyA) ? s.keyB : s.keyA; vo = (vo == s.valA) ? s.valB : s.valA;
-    }
-    skey = ki; spos = vi;
+    SortBuffers sb{s.keyA, s.valA, s.keyB, s.valB, s.hist, s.tiles};
+    const int rc = radix_sort_by_key(inv, n, /*mod=*/0, cap, s.bits, s.passes, sb, &skey, &spos, st);
+    if (rc != SRM2_OK) return rc;
   }
   // 2. segment starts
   const int grid_n = (int)((n + 255) / 256 > 0 ? (n + 255) / 256 : 1);
@@ -347,10 +250,13 @@ static int segment_pipeline(bool fused, const float* grad, const int64_t* inv, i
   a.nu_host = nu_host; a.nu_dev = nu_dev; a.cap = cap; a.n = n;
   const int64_t row_items = cap * lpr;
   const int grid_rows = (int)((row_items + 255) / 256 < (int64_t)kSMs * 16 ? (row_items + 255) / 256 : (int64_t)kSMs * 16);
-  if (n <= kSmallN) {
+  int launches = n > 0 ? 3 * s.passes + 1 : 1;
+  if (order == SRM2_ORDER_WINDOWS || (order == SRM2_ORDER_AUTO && n <= kSmallN)) {
+    stage_begin(st);
     if (fused) srm2_segment_windowed_kernel<true><<<grid_rows, 256, 0, st>>>(a);
     else srm2_segment_windowed_kernel<false><<<grid_rows, 256, 0, st>>>(a);
-    return launch_status();
+    stage_end(st);
+    return launch_status(launches + 1);
   }
   // 3. runs per segment, their exclusive scans, run descriptors
   srm2_segment_runs_kernel<<<grid_u, 256, 0, st>>>(s.seg_start, s.runs, s.mruns, nu_host, nu_dev, cap);
@@ -360,6 +266,7 @@ static int segment_pipeline(bool fused, const float* grad, const int64_t* inv, i
   // 4. run sums, then multi-run rows
   const int64_t run_items_max = n * lpr;
   const int grid_runs = (int)((run_items_max + 255) / 256 < (int64_t)kSMs * 16 ? (run_items_max + 255) / 256 : (int64_t)kSMs * 16);
+  stage_begin(st);
   if (fused) {
     srm2_segment_runsum_kernel<true><<<grid_runs, 256, 0, st>>>(a);
     srm2_segment_final_kernel<true><<<grid_rows, 256, 0, st>>>(a);
@@ -367,7 +274,8 @@ static int segment_pipeline(bool fused, const float* grad, const int64_t* inv, i
     srm2_segment_runsum_kernel<false><<<grid_runs, 256, 0, st>>>(a);
     srm2_segment_final_kernel<false><<<grid_rows, 256, 0, st>>>(a);
   }
-  return launch_status();
+  stage_end(st);
+  return launch_status(launches + 6);
 }
 
 }  // namespace srm2
@@ -378,15 +286,15 @@ extern "C" size_t srm2_segment_scratch_bytes(int64_t n, int64_t max_unique, int6
 }
 
 extern "C" int srm2_segment_reduce_f32(const float* grad, const int64_t* inv, int64_t n, int64_t D, int64_t n_unique,
-                                       const int64_t* n_unique_dev, int64_t max_unique, float* out, void* scratch,
+                                       const int64_t* n_unique_dev, int64_t max_unique, int order, float* out, void* scratch,
                                        size_t scratch_bytes, srm2_stream_t stream) {
-  return srm2::segment_pipeline(false, grad, inv, n, D, n_unique, n_unique_dev, max_unique, out, nullptr, nullptr, nullptr,
+  return srm2::segment_pipeline(false, order, grad, inv, n, D, n_unique, n_unique_dev, max_unique, out, nullptr, nullptr, nullptr,
                                 scratch, scratch_bytes, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int srm2_reduce_adam_f32(float* pool, const int64_t* slots, const float* grad, const int64_t* inv, int64_t n,
                                     int64_t D, int64_t n_unique, const int64_t* n_unique_dev, int64_t max_unique,
-                                    const float sc[8], void* scratch, size_t scratch_bytes, srm2_stream_t stream) {
-  return srm2::segment_pipeline(true, grad, inv, n, D, n_unique, n_unique_dev, max_unique, nullptr, pool, slots, sc, scratch,
+                                    int order, const float sc[8], void* scratch, size_t scratch_bytes, srm2_stream_t stream) {
+  return srm2::segment_pipeline(true, order, grad, inv, n, D, n_unique, n_unique_dev, max_unique, nullptr, pool, slots, sc, scratch,
                                 scratch_bytes, static_cast<cudaStream_t>(stream));
 }

@@ -139,7 +139,10 @@ def _check_grad_inv(grad, inv):
         raise RuntimeError('grad and inv must be on the same device')
 
 
-def segment_reduce(grad, inv, n_unique):
+ORDER_AUTO, ORDER_RUNS, ORDER_WINDOWS = 0, 1, 2
+
+
+def segment_reduce(grad, inv, n_unique, order=ORDER_AUTO):
     """gW[j] = sum of grad[p] over lookups p with inv[p] == j, fp32, in the summation order of PyTorch's CUDA
     `aten.embedding_dense_backward(grad, inv, n_unique, -1, False)` (srm2/train.py:429) -> [n_unique, D]."""
     _check_grad_inv(grad, inv)
@@ -152,13 +155,13 @@ def segment_reduce(grad, inv, n_unique):
     nb = L.srm2_segment_scratch_bytes(n, int(n_unique), D)
     scr = _scratch(dev, nb, 'segment')
     with torch.cuda.device(dev):
-        st = L.srm2_segment_reduce_f32(_lib.ptr(grad), _lib.ptr(inv), n, D, int(n_unique), 0, int(n_unique), out.data_ptr(),
+        st = L.srm2_segment_reduce_f32(_lib.ptr(grad), _lib.ptr(inv), n, D, int(n_unique), 0, int(n_unique), order, out.data_ptr(),
                                        scr.data_ptr(), scr.numel(), _lib.stream_of(dev))
     _lib.check(st, 'segment_reduce')
     return out
 
 
-def reduce_adam(pool, slots, grad, inv, lr, b1, b2, eps, step, n_unique=None, count=None):
+def reduce_adam(pool, slots, grad, inv, lr, b1, b2, eps, step, n_unique=None, count=None, order=ORDER_AUTO):
     """segment_reduce followed by gpu_adam(pool, slots, gW, ...) in one pass over the gradients: same bits, gW never
     materialised.  slots int64 [>= n_unique]: pool row of each unique row.  Give either n_unique (host int) or count
     (the cuda tensor returned by unique_inverse(sync=False)); with count nothing waits on the GPU."""
@@ -184,5 +187,5 @@ def reduce_adam(pool, slots, grad, inv, lr, b1, b2, eps, step, n_unique=None, co
     with torch.cuda.device(dev):
         st = L.srm2_reduce_adam_f32(pool.data_ptr(), slots.data_ptr(), _lib.ptr(grad), _lib.ptr(inv), n, D,
                                     -1 if n_unique is None else cap, 0 if count is None or n_unique is not None else count.data_ptr(),
-                                    cap, sc, scr.data_ptr(), scr.numel(), _lib.stream_of(dev))
+                                    cap, order, sc, scr.data_ptr(), scr.numel(), _lib.stream_of(dev))
     _lib.check(st, 'reduce_adam')

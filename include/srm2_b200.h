@@ -36,6 +36,12 @@ int srm2_version(void);
 const char* srm2_status_string(int status);
 /* text of the last CUDA runtime error seen by this thread inside the library ("" if none) */
 const char* srm2_last_cuda_error(void);
+/* number of kernels this library has enqueued in this process so far (all threads) */
+int64_t srm2_launch_count(void);
+/* Instrumentation for benchmarks: while set (per calling thread), srm2_segment_reduce_f32 / srm2_reduce_adam_f32 record
+ * the cudaEvent_t `begin` before and `end` after their gradient-streaming kernels, on the call's stream.  Pass NULL, NULL
+ * to clear.  No counterpart in the reference. */
+int srm2_stage_events(void* begin /* cudaEvent_t */, void* end /* cudaEvent_t */);
 
 /* ---------------------------------------------------------------------------------------------------------
  * Adam scalars.  Replaces `adam_scalars` of the reference's host extension
@@ -101,11 +107,17 @@ int srm2_unique_inverse_i64(const int64_t* ids, int64_t n, int64_t n_rows, int64
  *   n_unique      host value, used when n_unique_dev == NULL
  *   n_unique_dev  optional device int64: the count is read on the device (no host sync after a dedup);
  *                 max_unique then bounds it and sizes the scratch
+ *   order         SRM2_ORDER_AUTO: the operator's rule (windows of 32 positions for n <= 3072, runs of 10 above);
+ *                 SRM2_ORDER_RUNS / SRM2_ORDER_WINDOWS force one (a shard of a larger batch must use the order of the
+ *                 whole batch)
  *   scratch       srm2_segment_scratch_bytes(n, max_unique or n_unique, D) bytes, 256-byte aligned
  */
+#define SRM2_ORDER_AUTO 0
+#define SRM2_ORDER_RUNS 1
+#define SRM2_ORDER_WINDOWS 2
 size_t srm2_segment_scratch_bytes(int64_t n, int64_t max_unique, int64_t D);
 int srm2_segment_reduce_f32(const float* grad, const int64_t* inv, int64_t n, int64_t D, int64_t n_unique,
-                            const int64_t* n_unique_dev, int64_t max_unique, float* out, void* scratch,
+                            const int64_t* n_unique_dev, int64_t max_unique, int order, float* out, void* scratch,
                             size_t scratch_bytes, srm2_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------------
@@ -116,8 +128,21 @@ int srm2_segment_reduce_f32(const float* grad, const int64_t* inv, int64_t n, in
  *   arguments as in srm2_segment_reduce_f32 and srm2_adam_rows_f32.
  */
 int srm2_reduce_adam_f32(float* pool, const int64_t* slots, const float* grad, const int64_t* inv, int64_t n, int64_t D,
-                         int64_t n_unique, const int64_t* n_unique_dev, int64_t max_unique, const float sc[8] /* host */,
-                         void* scratch, size_t scratch_bytes, srm2_stream_t stream);
+                         int64_t n_unique, const int64_t* n_unique_dev, int64_t max_unique, int order,
+                         const float sc[8] /* host */, void* scratch, size_t scratch_bytes, srm2_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Owner routing for row-sharded tables (rows owned by row_id mod world, local row = row_id div world).
+ * No counterpart in the reference, which is single-GPU; it serves the row-sharded benchmark configuration.
+ *   ids [n] int64 global row ids, grad [n,D] fp32
+ *   out_lid  [n] int64: local row ids (row_id div world) grouped by owner rank 0..world-1, original order kept
+ *            inside each group;  out_grad [n,D]: the gradient rows in the same order
+ *   out_counts [world] int64 (device): lookups per owner
+ *   scratch  srm2_route_scratch_bytes(n, world) bytes, 256-byte aligned
+ */
+size_t srm2_route_scratch_bytes(int64_t n, int64_t world);
+int srm2_route_by_owner(const int64_t* ids, const float* grad, int64_t n, int64_t D, int64_t world, int64_t* out_lid,
+                        float* out_grad, int64_t* out_counts, void* scratch, size_t scratch_bytes, srm2_stream_t stream);
 
 #ifdef __cplusplus
 }
