@@ -43,17 +43,40 @@ static size_t dedup_layout(int64_t n_rows, char* base, DedupScratch* s) {
   return off;
 }
 
-// flags[1] bit 0: an id outside [0, n_rows) was seen (it is ignored; its inverse is -1)
+// Marks the ids of one chunk of lookups.  Hot rows are looked up thousands of times per batch and the hottest ids of a
+// table share a bitmap word, so naive atomics serialise on a few words in L2.  Each CTA therefore first ORs its bits
+// into a direct-mapped shared-memory cache keyed by word index (collisions fall through to a global atomic) and then
+// flushes every cached word with a single global atomicOr.
+// out_count[1] = 1 if an id outside [0, n_rows) was seen (it is ignored; its inverse is -1).
+constexpr int kMarkPerThread = 8;
+constexpr int kMarkSlots = 2048;
 __global__ void __launch_bounds__(kDT)
 srm2_unique_mark_kernel(const int64_t* __restrict__ ids, int64_t n, int64_t n_rows, uint32_t* __restrict__ bitmap,
                         int64_t* __restrict__ out_count) {
-  for (int64_t p = (int64_t)blockIdx.x * kDT + threadIdx.x; p < n; p += (int64_t)gridDim.x * kDT) {
-    const int64_t id = ids[p];
-    if (id < 0 || id >= n_rows) { out_count[1] = 1; continue; }
-    const uint32_t bit = 1u << (id & 31);
-    uint32_t* w = bitmap + (id >> 5);
-    if (!(*reinterpret_cast<volatile uint32_t*>(w) & bit)) atomicOr(w, bit);
+  __shared__ uint32_t tag[kMarkSlots];
+  __shared__ uint32_t val[kMarkSlots];
+  for (int i = threadIdx.x; i < kMarkSlots; i += kDT) { tag[i] = 0xffffffffu; val[i] = 0u; }
+  __syncthreads();
+  const int64_t base = (int64_t)blockIdx.x * (kDT * kMarkPerThread);
+  int64_t id[kMarkPerThread];
+#pragma unroll
+  for (int k = 0; k < kMarkPerThread; ++k) {
+    const int64_t p = base + k * kDT + threadIdx.x;
+    id[k] = p < n ? ids[p] : -2;
   }
+#pragma unroll
+  for (int k = 0; k < kMarkPerThread; ++k) {
+    if (id[k] == -2) continue;
+    if (id[k] < 0 || id[k] >= n_rows) { out_count[1] = 1; continue; }
+    const uint32_t w = (uint32_t)(id[k] >> 5), bit = 1u << (id[k] & 31);
+    const uint32_t slot = (w * 2654435761u) >> (32 - 11);
+    const uint32_t prev = atomicCAS(&tag[slot], 0xffffffffu, w);
+    if (prev == 0xffffffffu || prev == w) atomicOr(&val[slot], bit);
+    else atomicOr(bitmap + w, bit);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < kMarkSlots; i += kDT)
+    if (tag[i] != 0xffffffffu) atomicOr(bitmap + tag[i], val[i]);
 }
 
 // Per block of 4096 words: number of set bits.  The last block to finish turns bsum into its exclusive scan and
@@ -91,13 +114,20 @@ srm2_unique_count_kernel(const uint32_t* __restrict__ bitmap, uint32_t* __restri
 }
 
 // Per word: exclusive prefix of distinct ids; every set bit writes its id at its rank.
+// The prefixes are computed with each thread owning 16 consecutive words; the ids are then written with the words
+// dealt round-robin to the threads, because set bits cluster (the frequent ids of a table are its smallest) and a run
+// of dense words must not end up in a single thread.
 __global__ void __launch_bounds__(kDT)
 srm2_unique_emit_kernel(const uint32_t* __restrict__ bitmap, const uint32_t* __restrict__ bsum, uint32_t* __restrict__ wprefix,
                         int64_t* __restrict__ uniq, int64_t uniq_cap) {
   __shared__ uint32_t ws[33];
-  const int64_t w0 = (int64_t)blockIdx.x * kWordsPerBlock + (int64_t)threadIdx.x * kWordsPerThread;
+  __shared__ uint32_t s_w[kWordsPerBlock];
+  __shared__ uint32_t s_p[kWordsPerBlock];
+  const int64_t wb = (int64_t)blockIdx.x * kWordsPerBlock;
+  const int t0 = threadIdx.x * kWordsPerThread;
   uint32_t wv[kWordsPerThread];
-  const uint4* src = reinterpret_cast<const uint4*>(bitmap + w0);
+  const uint4* src = reinterpret_cast<const uint4*>(bitmap + wb + t0);
+  const uint32_t bbase = bsum[blockIdx.x];
   uint32_t c = 0;
 #pragma unroll
   for (int k = 0; k < kWordsPerThread / 4; ++k) {
@@ -105,19 +135,21 @@ srm2_unique_emit_kernel(const uint32_t* __restrict__ bitmap, const uint32_t* __r
     wv[4 * k] = v.x; wv[4 * k + 1] = v.y; wv[4 * k + 2] = v.z; wv[4 * k + 3] = v.w;
     c += __popc(v.x) + __popc(v.y) + __popc(v.z) + __popc(v.w);
   }
-  uint32_t run = bsum[blockIdx.x] + block_exclusive_scan<kDT>(c, ws, nullptr);
+  uint32_t total;
+  uint32_t run = bbase + block_exclusive_scan<kDT>(c, ws, &total);
   uint32_t pf[kWordsPerThread];
 #pragma unroll
-  for (int k = 0; k < kWordsPerThread; ++k) { pf[k] = run; run += __popc(wv[k]); }
-  uint4* dst = reinterpret_cast<uint4*>(wprefix + w0);
+  for (int k = 0; k < kWordsPerThread; ++k) { pf[k] = run; run += __popc(wv[k]); s_w[t0 + k] = wv[k]; s_p[t0 + k] = pf[k]; }
+  uint4* dst = reinterpret_cast<uint4*>(wprefix + wb + t0);
 #pragma unroll
   for (int k = 0; k < kWordsPerThread / 4; ++k) dst[k] = make_uint4(pf[4 * k], pf[4 * k + 1], pf[4 * k + 2], pf[4 * k + 3]);
-#pragma unroll
-  for (int k = 0; k < kWordsPerThread; ++k) {
-    uint32_t bits = wv[k]; uint32_t r = pf[k];
+  if (total == 0) return;                            // uniform: nothing to emit in this block of words
+  __syncthreads();
+  for (int i = threadIdx.x; i < kWordsPerBlock; i += kDT) {
+    uint32_t bits = s_w[i]; uint32_t r = s_p[i];
     while (bits) {
       const int b = __ffs(bits) - 1; bits &= bits - 1;
-      if ((int64_t)r < uniq_cap) uniq[r] = ((w0 + k) << 5) + b;
+      if ((int64_t)r < uniq_cap) uniq[r] = ((wb + i) << 5) + b;
       ++r;
     }
   }
@@ -158,7 +190,8 @@ extern "C" int srm2_unique_inverse_i64(const int64_t* ids, int64_t n, int64_t n_
   if (note_cuda(cudaMemsetAsync(s.counter, 0, 4, st))) return SRM2_ERR_CUDA;
   if (note_cuda(cudaMemsetAsync(out_count, 0, 16, st))) return SRM2_ERR_CUDA;
   const int grid_n = (int)((n + kDT - 1) / kDT < kSMs * 8 ? (n + kDT - 1) / kDT : kSMs * 8);
-  if (n > 0) srm2_unique_mark_kernel<<<grid_n, kDT, 0, st>>>(ids, n, n_rows, s.bitmap, out_count);
+  const int64_t mark_blocks = (n + kDT * kMarkPerThread - 1) / (kDT * kMarkPerThread);
+  if (n > 0) srm2_unique_mark_kernel<<<(unsigned)mark_blocks, kDT, 0, st>>>(ids, n, n_rows, s.bitmap, out_count);
   srm2_unique_count_kernel<<<(unsigned)s.nblocks, kDT, 0, st>>>(s.bitmap, s.bsum, s.counter, s.nblocks, out_count);
   srm2_unique_emit_kernel<<<(unsigned)s.nblocks, kDT, 0, st>>>(s.bitmap, s.bsum, s.wprefix, uniq, uniq_cap);
   if (n > 0) srm2_unique_inverse_kernel<<<grid_n, kDT, 0, st>>>(ids, n, n_rows, s.bitmap, s.wprefix, inv);

@@ -4,7 +4,7 @@
 // Stability matters: every owner later sums the lookups of a row in ascending GLOBAL lookup position; ranks hold
 // consecutive slices of the batch, so a stable grouping on every rank plus concatenation in rank order on the owner
 // reproduces the single-process order without shipping positions.
-// Kernels: one stable counting pass of the radix sort (histogram, scan, scatter; world <= 2048 owners) and a row gather
+// Kernels: one stable counting pass of the radix sort (histogram, scatter; world <= 2048 owners) and a row gather
 // that streams each gradient row once (D*4 bytes read + written per lookup, HBM bound).
 #include "common.cuh"
 #include "scan.cuh"
@@ -28,14 +28,16 @@ srm2_route_gather_kernel(const int64_t* __restrict__ ids, const float* __restric
   }
 }
 
-// counts[o] = number of lookups owned by rank o, from the scanned digit-major histogram of the single sort pass.
-__global__ void srm2_route_counts_kernel(const uint32_t* __restrict__ hist_scanned, int tiles, int world, int64_t n,
-                                         int64_t* __restrict__ counts) {
+// counts[o] = number of lookups owned by rank o: the digit totals of the single sort pass, or, when the histogram was
+// scanned by the separate kernel, the difference of consecutive digit starts.
+__global__ void srm2_route_counts_kernel(const uint32_t* __restrict__ hist, const uint32_t* __restrict__ dtot, int tiles, int world,
+                                         int64_t n, int64_t* __restrict__ counts) {
   const int o = blockIdx.x * blockDim.x + threadIdx.x;
   if (o >= world) return;
-  const uint32_t lo = hist_scanned[(int64_t)o * tiles];
-  const int64_t hi = (o + 1 < world) ? (int64_t)hist_scanned[(int64_t)(o + 1) * tiles] : n;
-  counts[o] = hi - (int64_t)lo;
+  if (dtot) { counts[o] = dtot[o]; return; }
+  const int64_t lo = hist[(int64_t)o * tiles];
+  const int64_t hi = (o + 1 < world) ? (int64_t)hist[(int64_t)(o + 1) * tiles] : n;
+  counts[o] = hi - lo;
 }
 
 static size_t align_up_r(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -48,10 +50,10 @@ static size_t route_layout(int64_t n, int64_t world, char* base, SortBuffers* sb
   size_t off = 0;
   auto take = [&](size_t bytes) { size_t o = off; off = align_up_r(off + bytes, 256); return o; };
   const size_t nn = (size_t)(n > 0 ? n : 1);
-  const size_t o_ka = take(nn * 4), o_va = take(nn * 4), o_h = take(((size_t)tiles * ((size_t)1 << bits) + 1) * 4);
+  const size_t o_ka = take(nn * 4), o_va = take(nn * 4), o_h = take(sort_hist_words(tiles, bits) * 4), o_dt = take(sort_dtot_words(bits, 1) * 4);
   if (sb) {
     auto u = [&](size_t o) { return reinterpret_cast<uint32_t*>(base + o); };
-    sb->keyA = u(o_ka); sb->valA = u(o_va); sb->keyB = nullptr; sb->valB = nullptr; sb->hist = u(o_h); sb->tiles = tiles;
+    sb->keyA = u(o_ka); sb->valA = u(o_va); sb->keyB = nullptr; sb->valB = nullptr; sb->hist = u(o_h); sb->dtot = u(o_dt); sb->tiles = tiles;
   }
   return off;
 }
@@ -80,13 +82,16 @@ extern "C" int srm2_route_by_owner(const int64_t* ids, const float* grad, int64_
   SortBuffers sb;
   route_layout(n, world, static_cast<char*>(scratch), &sb);
   const uint32_t *skey = nullptr, *perm = nullptr;
-  const int rc = radix_sort_by_key(ids, n, (int)world, 0, route_bits(world), 1, sb, &skey, &perm, st);
+  int launches = 0;
+  const uint32_t* hb = nullptr;
+  if (note_cuda(cudaMemsetAsync(sb.dtot, 0, sort_dtot_words(route_bits(world), 1) * 4, st))) return SRM2_ERR_CUDA;
+  const int rc = radix_sort_by_key(ids, n, (int)world, 0, route_bits(world), 1, sb, &skey, &perm, &hb, &launches, st);
   if (rc != SRM2_OK) return rc;
-  srm2_route_counts_kernel<<<(unsigned)((world + 255) / 256), 256, 0, st>>>(sb.hist, sb.tiles, (int)world, n, out_counts);
+  srm2_route_counts_kernel<<<(unsigned)((world + 255) / 256), 256, 0, st>>>(sb.hist, hb, sb.tiles, (int)world, n, out_counts);
   const int lpr = (int)(D / 4);
   const int shift = (lpr & (lpr - 1)) == 0 ? __builtin_ctz(lpr) : -1;
   const int64_t items = n * lpr;
   const int grid = (int)((items + 255) / 256 < (int64_t)kSMs * 16 ? (items + 255) / 256 : (int64_t)kSMs * 16);
   srm2_route_gather_kernel<<<grid, 256, 0, st>>>(ids, grad, perm, n, lpr, shift, (int)D, (int)world, out_lid, out_grad);
-  return launch_status(5);
+  return launch_status(launches + 2);
 }

@@ -47,13 +47,20 @@ srm2_scan_exclusive_u32_kernel(const uint32_t* __restrict__ in, uint32_t* __rest
   __shared__ uint32_t ws[33];
   int64_t count = count_dev ? *count_dev : count_host;
   if (count > count_cap) count = count_cap;
-  const int64_t per = (count + kScanThreads - 1) / kScanThreads;
-  const int64_t lo = (int64_t)threadIdx.x * per, hi = lo + per < count ? lo + per : count;
-  uint32_t s = 0;
-  for (int64_t i = lo; i < hi; ++i) s += in[i];
-  uint32_t total;
-  uint32_t run = block_exclusive_scan<kScanThreads>(s, ws, &total);
-  for (int64_t i = lo; i < hi; ++i) { const uint32_t x = in[i]; out[i] = run; run += x; }
+  // rounds of 4 * kScanThreads consecutive entries; thread t owns entries [4t, 4t+4) of the round (coalesced)
+  uint32_t carry = 0;
+  for (int64_t base = 0; base < count; base += 4 * kScanThreads) {
+    const int64_t i0 = base + 4 * (int64_t)threadIdx.x;
+    uint32_t x[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) x[e] = (i0 + e < count) ? in[i0 + e] : 0u;
+    uint32_t tot;
+    uint32_t run = carry + block_exclusive_scan<kScanThreads>(x[0] + x[1] + x[2] + x[3], ws, &tot);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { if (i0 + e < count) out[i0 + e] = run; run += x[e]; }
+    carry += tot;
+  }
+  const uint32_t total = carry;
   if (threadIdx.x == 0) {
     if (write_tail) out[count] = total;
     if (total_out) *total_out = total;

@@ -9,12 +9,17 @@
 //                      are summed left to right starting from the first; window sums are added to a row that starts +0.
 //
 // Pipeline (all on the caller's stream, nothing synchronises, scratch supplied by the caller):
-//   1. stable LSD radix sort of (key = inverse index, value = lookup position), 32-bit keys, up to 11 bits per pass;
-//      the number of passes follows from the bound on the number of unique rows, so typical inputs take two.
-//   2. segment starts from the sorted keys; per-segment run counts; exclusive scans of those (single CTA).
-//   3. run descriptors; one thread group per run sums its <= 10 gradient rows (all loads issued up front) — work is
-//      balanced over the whole GPU however long the longest segment is; rows with a single run are finished here.
-//   4. rows with several runs: run sums added in order (partials are L2 resident), then written / Adam applied.
+//   1. stable LSD radix sort of (key = inverse index, value = lookup position); the number of passes follows from the
+//      bound on the number of unique rows (two 9-bit passes for ~200 k lookups).
+//   2. segment boundaries from the sorted keys.
+//   3. plan: runs per segment and three block-local exclusive scans (runs, runs of multi-run rows, multi-run rows);
+//      the last CTA to finish scans the per-CTA totals.  A global prefix is (CTA prefix + in-CTA offset): no separate
+//      scan launch.
+//   4. run descriptors {first sorted index, row, length, partial slot} and the list of multi-run rows.
+//   5. run sums: one thread group per run sums its <= 10 gradient rows, all loads issued up front.  Work is spread over
+//      the whole GPU however long the longest segment is.  Rows with one run are finished here (written, or Adam applied).
+//   6. multi-run rows: the run sums are staged through shared memory with cp.async (a warp per short row, the whole CTA
+//      per long row) and added in order; the only serial part is the fp32 add chain itself.
 // Gradient rows are read exactly once (D*4 bytes per lookup); everything else is small integer traffic.
 #include "common.cuh"
 #include "scan.cuh"
@@ -25,56 +30,26 @@ namespace srm2 {
 constexpr int kRun = 10;            // lookups per run (large inputs)
 constexpr int kSmallN = 3072;       // inputs up to this many lookups use the windowed order
 constexpr int kWindow = 32;
+constexpr int kPlanThreads = 256;
+constexpr uint32_t kNoSlot = 0xffffffffu;
 
-// ------------------------------------------------------------------------------------------ segments
-// seg_start[j] = number of sorted keys below j (lower bound), for j in [0, nu]; a row without lookups gets an empty
-// segment.  Keys are clamped to `cap` by the sort, so lookups with an invalid index land behind every segment.
-__global__ void __launch_bounds__(256)
-srm2_segment_bounds_kernel(const uint32_t* __restrict__ skey, int64_t n, uint32_t* __restrict__ seg_start,
-                           int64_t nu_host, const int64_t* __restrict__ nu_dev, int64_t cap) {
-  int64_t nu = nu_dev ? *nu_dev : nu_host; if (nu > cap) nu = cap;
-  for (int64_t j = (int64_t)blockIdx.x * 256 + threadIdx.x; j <= nu; j += (int64_t)gridDim.x * 256) {
-    int64_t lo = 0, hi = n;
-    while (lo < hi) { const int64_t mid = (lo + hi) >> 1; if ((int64_t)skey[mid] < j) lo = mid + 1; else hi = mid; }
-    seg_start[j] = (uint32_t)lo;
-  }
-}
-
-// runs[j] = number of runs of segment j; mruns[j] = the same if the segment has more than one run, else 0.
-__global__ void __launch_bounds__(256)
-srm2_segment_runs_kernel(const uint32_t* __restrict__ seg_start, uint32_t* __restrict__ runs, uint32_t* __restrict__ mruns,
-                         int64_t nu_host, const int64_t* __restrict__ nu_dev, int64_t cap) {
-  int64_t nu = nu_dev ? *nu_dev : nu_host; if (nu > cap) nu = cap;
-  for (int64_t j = (int64_t)blockIdx.x * 256 + threadIdx.x; j < nu; j += (int64_t)gridDim.x * 256) {
-    const uint32_t len = seg_start[j + 1] - seg_start[j];
-    const uint32_t r = (len + kRun - 1) / kRun;
-    runs[j] = r; mruns[j] = r > 1 ? r : 0u;
-  }
-}
-
-// run_first[c] = sorted index of the first lookup of run c.
-__global__ void __launch_bounds__(256)
-srm2_segment_descr_kernel(const uint32_t* __restrict__ skey, int64_t n, const uint32_t* __restrict__ seg_start,
-                          const uint32_t* __restrict__ run_base, uint32_t* __restrict__ run_first, int64_t nu_host,
-                          const int64_t* __restrict__ nu_dev, int64_t cap) {
-  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
-  if (i >= n) return;
-  int64_t nu = nu_dev ? *nu_dev : nu_host; if (nu > cap) nu = cap;
-  const uint32_t j = skey[i];
-  if ((int64_t)j >= nu) return;
-  const uint32_t off = (uint32_t)i - seg_start[j];
-  if (off % kRun == 0) run_first[run_base[j] + off / kRun] = (uint32_t)i;
-}
+struct SegCounters { uint32_t n_runs, n_mrows, n_mruns, done; };
 
 struct ReduceArgs {
   const float* grad; int D; int lpr; int shift;
-  const uint32_t* skey; const uint32_t* spos; const uint32_t* seg_start;
-  const uint32_t* run_base; const uint32_t* mrun_base; const uint32_t* run_first; const uint32_t* n_runs;
+  const uint32_t* skey; const uint32_t* spos; const uint32_t* seg_start; const uint32_t* seg_end;
+  const uint4* run_desc; const uint32_t* mrows; const SegCounters* counters;
+  const uint32_t* mrun_off; const uint32_t* bpre_m;
   float* partial;
-  float* out;               // [nu, D] (unfused) or nullptr
+  float* out;                                     // [nu, D] (unfused) or nullptr
   float* pool; const int64_t* slots; AdamSc sc;   // fused Adam: pool [C,3,D], slots[j] = pool row of unique row j
   int64_t nu_host; const int64_t* nu_dev; int64_t cap; int64_t n;
 };
+
+__device__ __forceinline__ int64_t load_nu(int64_t nu_host, const int64_t* nu_dev, int64_t cap) {
+  int64_t nu = nu_dev ? *nu_dev : nu_host;
+  return nu > cap ? cap : (nu < 0 ? 0 : nu);
+}
 
 __device__ __forceinline__ float4 add4(const float4& a, const float4& b) {
   return make_float4(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y), __fadd_rn(a.z, b.z), __fadd_rn(a.w, b.w));
@@ -94,75 +69,227 @@ __device__ __forceinline__ void finish_row(const ReduceArgs& a, uint32_t j, int 
   }
 }
 
+// ------------------------------------------------------------------------------------------ boundaries
+// seg_start[j] / seg_end[j] = sorted index range of unique row j.  Both arrays are zeroed first, so a row that no
+// lookup names has an empty range.  Lookups with an invalid index carry key == cap and belong to no row.
+__global__ void __launch_bounds__(256)
+srm2_segment_bounds_kernel(const uint32_t* __restrict__ skey, int64_t n, uint32_t* __restrict__ seg_start,
+                           uint32_t* __restrict__ seg_end, int64_t cap) {
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= n) return;
+  const uint32_t k = skey[i];
+  if ((int64_t)k >= cap) return;
+  if (i == 0 || skey[i - 1] != k) seg_start[k] = (uint32_t)i;
+  if (i == n - 1 || skey[i + 1] != k) seg_end[k] = (uint32_t)(i + 1);
+}
+
+// ------------------------------------------------------------------------------------------ plan
+// Per unique row: runs, block-local exclusive offsets of (runs, runs of multi-run rows, multi-run rows); per CTA the
+// totals; the last CTA to finish turns the totals into exclusive prefixes and writes the grand totals.
+// Rows without lookups are finished here (zero gradient).
+template <bool FUSED>
+__global__ void __launch_bounds__(kPlanThreads)
+srm2_segment_plan_kernel(ReduceArgs a, uint32_t* __restrict__ run_off, uint32_t* __restrict__ mrun_off,
+                         uint32_t* __restrict__ mrow_off, uint32_t* __restrict__ bsum_r, uint32_t* __restrict__ bsum_m,
+                         uint32_t* __restrict__ bsum_f, SegCounters* __restrict__ counters, int nblocks, int small) {
+  __shared__ uint32_t ws[33];
+  __shared__ bool last;
+  const int64_t nu = load_nu(a.nu_host, a.nu_dev, a.cap);
+  const int64_t j = (int64_t)blockIdx.x * kPlanThreads + threadIdx.x;
+  uint32_t r = 0, m = 0, f = 0;
+  if (j < nu) {
+    const uint32_t len = a.seg_end[j] - a.seg_start[j];
+    r = (len + kRun - 1) / kRun; f = r > 1; m = f ? r : 0u;
+    if (len == 0 && !small)
+      for (int j4 = 0; j4 < a.lpr; ++j4) finish_row<FUSED>(a, (uint32_t)j, j4, make_float4(0.f, 0.f, 0.f, 0.f));
+  }
+  if (small) return;                               // the windowed order needs no runs
+  uint32_t tr, tm, tf;
+  const uint32_t er = block_exclusive_scan<kPlanThreads>(r, ws, &tr);
+  const uint32_t em = block_exclusive_scan<kPlanThreads>(m, ws, &tm);
+  const uint32_t ef = block_exclusive_scan<kPlanThreads>(f, ws, &tf);
+  if (j < a.cap) { run_off[j] = er; mrun_off[j] = em; mrow_off[j] = ef; }
+  if (threadIdx.x == 0) {
+    bsum_r[blockIdx.x] = tr; bsum_m[blockIdx.x] = tm; bsum_f[blockIdx.x] = tf;
+    __threadfence();
+    last = atomicAdd(&counters->done, 1u) == (uint32_t)(nblocks - 1);
+  }
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  uint32_t cr = 0, cm = 0, cf = 0;
+  for (int base = 0; base < nblocks; base += kPlanThreads) {
+    const int i = base + threadIdx.x;
+    const uint32_t vr = i < nblocks ? reinterpret_cast<volatile uint32_t*>(bsum_r)[i] : 0u;
+    const uint32_t vm = i < nblocks ? reinterpret_cast<volatile uint32_t*>(bsum_m)[i] : 0u;
+    const uint32_t vf = i < nblocks ? reinterpret_cast<volatile uint32_t*>(bsum_f)[i] : 0u;
+    uint32_t t0, t1, t2;
+    const uint32_t xr = block_exclusive_scan<kPlanThreads>(vr, ws, &t0);
+    const uint32_t xm = block_exclusive_scan<kPlanThreads>(vm, ws, &t1);
+    const uint32_t xf = block_exclusive_scan<kPlanThreads>(vf, ws, &t2);
+    if (i < nblocks) { bsum_r[i] = cr + xr; bsum_m[i] = cm + xm; bsum_f[i] = cf + xf; }
+    cr += t0; cm += t1; cf += t2;
+  }
+  if (threadIdx.x == 0) { counters->n_runs = cr; counters->n_mruns = cm; counters->n_mrows = cf; counters->done = 0u; }
+}
+
+// Run descriptors and the list of multi-run rows; one thread per sorted lookup.
+__global__ void __launch_bounds__(256)
+srm2_segment_descr_kernel(const uint32_t* __restrict__ skey, int64_t n, const uint32_t* __restrict__ seg_start,
+                          const uint32_t* __restrict__ seg_end, const uint32_t* __restrict__ run_off,
+                          const uint32_t* __restrict__ mrun_off, const uint32_t* __restrict__ mrow_off,
+                          const uint32_t* __restrict__ bpre_r, const uint32_t* __restrict__ bpre_m,
+                          const uint32_t* __restrict__ bpre_f, uint4* __restrict__ run_desc, uint32_t* __restrict__ mrows,
+                          int64_t nu_host, const int64_t* __restrict__ nu_dev, int64_t cap) {
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= n) return;
+  const uint32_t j = skey[i];
+  if ((int64_t)j >= load_nu(nu_host, nu_dev, cap)) return;
+  const uint32_t s = seg_start[j];
+  const uint32_t off = (uint32_t)i - s;
+  if (off % kRun != 0) return;
+  const uint32_t e = seg_end[j];
+  const bool multi = e - s > (uint32_t)kRun;
+  const uint32_t blk = j / kPlanThreads, ri = off / kRun;
+  const uint32_t c = bpre_r[blk] + run_off[j] + ri;
+  const uint32_t len = min((uint32_t)kRun, e - (uint32_t)i);
+  const uint32_t pslot = multi ? bpre_m[blk] + mrun_off[j] + ri : kNoSlot;
+  run_desc[c] = make_uint4((uint32_t)i, j, len, pslot);
+  if (off == 0 && multi) mrows[bpre_f[blk] + mrow_off[j]] = j;
+}
+
+// ------------------------------------------------------------------------------------------ run sums
 // One thread per (run, 16-byte lane).  Sums the <= 10 gradient rows of the run from +0; a row with a single run is
 // finished here ((+0) + run sum), otherwise the run sum goes to the partial buffer.
 template <bool FUSED>
 __global__ void __launch_bounds__(256)
 srm2_segment_runsum_kernel(ReduceArgs a) {
-  const int64_t items = (int64_t)(*a.n_runs) * a.lpr;
+  const int64_t items = (int64_t)a.counters->n_runs * a.lpr;
   for (int64_t t = (int64_t)blockIdx.x * 256 + threadIdx.x; t < items; t += (int64_t)gridDim.x * 256) {
     int64_t c; int j4;
     if (a.shift >= 0) { c = t >> a.shift; j4 = (int)(t & (a.lpr - 1)); } else { c = t / a.lpr; j4 = (int)(t - c * a.lpr); }
-    const uint32_t first = a.run_first[c];
-    const uint32_t j = a.skey[first];
-    const uint32_t s0 = a.seg_start[j], s1 = a.seg_start[j + 1];
-    const uint32_t len = min((uint32_t)kRun, s1 - first);
+    const uint4 d = __ldg(a.run_desc + c);          // {first, row, len, partial slot}
     float4 g[kRun];
 #pragma unroll
     for (int q = 0; q < kRun; ++q)
-      if (q < (int)len) g[q] = ld_stream4(a.grad + (int64_t)a.spos[first + q] * a.D + j4 * 4);
+      if (q < (int)d.z) g[q] = ld_stream4(a.grad + (int64_t)__ldg(a.spos + d.x + q) * a.D + j4 * 4);
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int q = 0; q < kRun; ++q)
-      if (q < (int)len) acc = add4(acc, g[q]);
-    if (s1 - s0 <= (uint32_t)kRun) {
-      finish_row<FUSED>(a, j, j4, add4(make_float4(0.f, 0.f, 0.f, 0.f), acc));
-    } else {
-      const uint32_t slot = a.mrun_base[j] + (first - s0) / kRun;
-      *reinterpret_cast<float4*>(a.partial + (int64_t)slot * a.D + j4 * 4) = acc;
+      if (q < (int)d.z) acc = add4(acc, g[q]);
+    if (d.w == kNoSlot) finish_row<FUSED>(a, d.y, j4, add4(make_float4(0.f, 0.f, 0.f, 0.f), acc));
+    else *reinterpret_cast<float4*>(a.partial + (int64_t)d.w * a.D + j4 * 4) = acc;
+  }
+}
+
+// ------------------------------------------------------------------------------------------ multi-run rows
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+constexpr int kFinalWarps = 4;
+constexpr int kFinalThreads = kFinalWarps * 32;
+constexpr int kMaxColsPerLane = 4;                 // D <= 512
+constexpr int kFinalSmemBytes = 64 * 1024;         // staging buffer of one CTA
+
+// Adds `cnt` staged run sums (rows of lpr float4 in shared memory) to the running totals of this lane's columns.
+__device__ __forceinline__ void add_staged(float4 (&tot)[kMaxColsPerLane], const float4* __restrict__ buf, int cnt, int lpr, int lane) {
+#pragma unroll
+  for (int q = 0; q < kMaxColsPerLane; ++q) {
+    const int col = lane + 32 * q;
+    if (col < lpr) {
+      float4 t = tot[q];
+      const float4* src = buf + col;
+      int r = 0;
+      for (; r + 8 <= cnt; r += 8) {
+        float4 x[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[e] = src[(r + e) * lpr];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) t = add4(t, x[e]);
+      }
+      for (; r < cnt; ++r) t = add4(t, src[r * lpr]);
+      tot[q] = t;
     }
   }
 }
 
-// One thread per (unique row, lane): rows with several runs add their run sums in order, from +0.
+// Multi-run rows: run sums added in order from +0.  A CTA takes four rows at a time.
+//  - a row with at most `short_rows` run sums is handled by one warp: each lane copies its own 16-byte columns of all
+//    run sums into shared memory with cp.async in one go (every load in flight at once) and adds them up;
+//  - longer rows are then handled by the whole CTA, one after another: the run sums of a row are contiguous in the
+//    partial buffer, so all threads copy a chunk of `chunk_rows` of them as one linear block, then warp 0 adds the
+//    chunk (the fp32 add chain is the only serial part; a chunk of 128 rows is ~1 us of copy and ~0.3 us of adds).
 template <bool FUSED>
-__global__ void __launch_bounds__(256)
-srm2_segment_final_kernel(ReduceArgs a) {
-  int64_t nu = a.nu_dev ? *a.nu_dev : a.nu_host; if (nu > a.cap) nu = a.cap;
-  const int64_t items = nu * a.lpr;
-  for (int64_t t = (int64_t)blockIdx.x * 256 + threadIdx.x; t < items; t += (int64_t)gridDim.x * 256) {
-    int64_t j; int j4;
-    if (a.shift >= 0) { j = t >> a.shift; j4 = (int)(t & (a.lpr - 1)); } else { j = t / a.lpr; j4 = (int)(t - j * a.lpr); }
-    const uint32_t len = a.seg_start[j + 1] - a.seg_start[j];
-    if (len == 0) { finish_row<FUSED>(a, (uint32_t)j, j4, make_float4(0.f, 0.f, 0.f, 0.f)); continue; }   // no lookups: zero gradient
-    if (len <= (uint32_t)kRun) continue;
-    const uint32_t nr = (len + kRun - 1) / kRun;
-    const float* p = a.partial + (int64_t)a.mrun_base[j] * a.D + j4 * 4;
-    float4 tot = make_float4(0.f, 0.f, 0.f, 0.f);
-    uint32_t c = 0;
-    for (; c + 8 <= nr; c += 8) {
-      float4 x[8];
-#pragma unroll
-      for (int q = 0; q < 8; ++q) x[q] = *reinterpret_cast<const float4*>(p + (int64_t)(c + q) * a.D);
-#pragma unroll
-      for (int q = 0; q < 8; ++q) tot = add4(tot, x[q]);
+__global__ void __launch_bounds__(kFinalThreads)
+srm2_segment_final_kernel(ReduceArgs a, int short_rows, int chunk_rows) {
+  extern __shared__ float4 smf[];                  // kFinalSmemBytes
+  __shared__ uint32_t s_j[kFinalWarps], s_nr[kFinalWarps], s_pb[kFinalWarps];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float4* mine = smf + (size_t)warp * short_rows * a.lpr;
+  const uint32_t n_mrows = a.counters->n_mrows;
+  for (uint32_t g = blockIdx.x; g * kFinalWarps < n_mrows; g += gridDim.x) {
+    const uint32_t mi = g * kFinalWarps + warp;
+    uint32_t j = 0, nr = 0, pb = 0;
+    if (mi < n_mrows) {
+      j = a.mrows[mi];
+      nr = (a.seg_end[j] - a.seg_start[j] + kRun - 1) / kRun;
+      pb = a.bpre_m[j / kPlanThreads] + a.mrun_off[j];
     }
-    for (; c < nr; ++c) tot = add4(tot, *reinterpret_cast<const float4*>(p + (int64_t)c * a.D));
-    finish_row<FUSED>(a, (uint32_t)j, j4, tot);
+    if (lane == 0) { s_j[warp] = j; s_nr[warp] = nr; s_pb[warp] = pb; }
+    if (nr > 0 && nr <= (uint32_t)short_rows) {
+      const float* p = a.partial + (int64_t)pb * a.D;
+      for (uint32_t r = 0; r < nr; ++r)
+        for (int col = lane; col < a.lpr; col += 32) cp_async16(mine + (size_t)r * a.lpr + col, p + (int64_t)r * a.D + col * 4);
+      cp_async_commit(); cp_async_wait<0>();
+      float4 tot[kMaxColsPerLane];
+#pragma unroll
+      for (int q = 0; q < kMaxColsPerLane; ++q) tot[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+      add_staged(tot, mine, (int)nr, a.lpr, lane);
+#pragma unroll
+      for (int q = 0; q < kMaxColsPerLane; ++q) { const int col = lane + 32 * q; if (col < a.lpr) finish_row<FUSED>(a, j, col, tot[q]); }
+    }
+    __syncthreads();
+    for (int w = 0; w < kFinalWarps; ++w) {
+      const uint32_t lnr = s_nr[w];
+      if (lnr <= (uint32_t)short_rows) continue;       // uniform over the CTA
+      const float* p = a.partial + (int64_t)s_pb[w] * a.D;
+      float4 tot[kMaxColsPerLane];
+#pragma unroll
+      for (int q = 0; q < kMaxColsPerLane; ++q) tot[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (uint32_t c0 = 0; c0 < lnr; c0 += chunk_rows) {
+        const int cnt = (int)min((uint32_t)chunk_rows, lnr - c0);
+        const float* src = p + (int64_t)c0 * a.D;
+        for (int idx = threadIdx.x; idx < cnt * a.lpr; idx += kFinalThreads) cp_async16(smf + idx, src + (int64_t)idx * 4);
+        cp_async_commit(); cp_async_wait<0>();
+        __syncthreads();
+        if (warp == 0) add_staged(tot, smf, cnt, a.lpr, lane);
+        __syncthreads();
+      }
+      if (warp == 0) {
+#pragma unroll
+        for (int q = 0; q < kMaxColsPerLane; ++q) { const int col = lane + 32 * q; if (col < a.lpr) finish_row<FUSED>(a, s_j[w], col, tot[q]); }
+      }
+    }
+    __syncthreads();
   }
 }
 
-// Small inputs: one thread per (unique row, lane) walks the row's lookups in ascending position; lookups of the same
-// 32-position window are summed from the first one, each window sum is then added to the row total (from +0).
+// ------------------------------------------------------------------------------------------ small inputs
+// One thread per (unique row, lane) walks the row's lookups in ascending position; lookups of the same 32-position
+// window are summed from the first one, each window sum is then added to the row total (from +0).
 template <bool FUSED>
 __global__ void __launch_bounds__(256)
 srm2_segment_windowed_kernel(ReduceArgs a) {
-  int64_t nu = a.nu_dev ? *a.nu_dev : a.nu_host; if (nu > a.cap) nu = a.cap;
+  const int64_t nu = load_nu(a.nu_host, a.nu_dev, a.cap);
   const int64_t items = nu * a.lpr;
   for (int64_t t = (int64_t)blockIdx.x * 256 + threadIdx.x; t < items; t += (int64_t)gridDim.x * 256) {
     int64_t j; int j4;
     if (a.shift >= 0) { j = t >> a.shift; j4 = (int)(t & (a.lpr - 1)); } else { j = t / a.lpr; j4 = (int)(t - j * a.lpr); }
-    const uint32_t s0 = a.seg_start[j], s1 = a.seg_start[j + 1];
+    const uint32_t s0 = a.seg_start[j], s1 = a.seg_end[j];
     float4 tot = make_float4(0.f, 0.f, 0.f, 0.f), win = tot;
     uint32_t cur = 0xffffffffu;
     for (uint32_t i = s0; i < s1; ++i) {
@@ -182,9 +309,9 @@ srm2_segment_windowed_kernel(ReduceArgs a) {
 
 // ------------------------------------------------------------------------------------------ host side
 struct SegScratch {
-  uint32_t *keyA, *valA, *keyB, *valB, *hist, *seg_start, *runs, *mruns, *run_first, *n_runs;
-  float* partial;
-  int tiles, bits, passes;
+  uint32_t *keyA, *valA, *keyB, *valB, *hist, *dtot, *seg_start, *seg_end, *run_off, *mrun_off, *mrow_off, *bsum_r, *bsum_m, *bsum_f, *mrows;
+  uint4* run_desc; SegCounters* counters; float* partial;
+  int tiles, bits, passes, nblocks;
 };
 
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -192,25 +319,30 @@ static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 static int ceil_log2(int64_t x) { int b = 0; while (((int64_t)1 << b) < x) ++b; return b; }
 
 static size_t seg_layout(int64_t n, int64_t cap, int64_t D, char* base, SegScratch* s) {
-  const int tiles = (int)((n + kSortTile - 1) / kSortTile);
+  const int tiles = sort_tiles(n > 0 ? n : 1);
   const int keybits = ceil_log2(cap + 1 < 2 ? 2 : cap + 1);     // keys 0..cap (cap = invalid index)
   const int passes = (keybits + kMaxRadixBits - 1) / kMaxRadixBits;
   const int bits = (keybits + passes - 1) / passes;
+  const int nblocks = (int)((cap + kPlanThreads - 1) / kPlanThreads);
   size_t off = 0;
   auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return o; };
-  const size_t nn = (size_t)(n > 0 ? n : 1);
+  const size_t nn = (size_t)(n > 0 ? n : 1), cc = (size_t)(cap + 1), nb = (size_t)(nblocks + 1);
   const size_t o_ka = take(nn * 4), o_va = take(nn * 4), o_kb = take(nn * 4), o_vb = take(nn * 4);
-  const size_t o_h = take(((size_t)tiles * ((size_t)1 << bits) + 1) * 4);
-  const size_t o_ss = take((size_t)(cap + 2) * 4), o_r = take((size_t)(cap + 2) * 4), o_mr = take((size_t)(cap + 2) * 4);
-  const size_t o_rf = take(nn * 4), o_nr = take(16);
+  const size_t o_h = take(sort_hist_words(tiles, bits) * 4), o_dt = take(sort_dtot_words(bits, passes) * 4);
+  const size_t o_ss = take(cc * 4 * 2);                          // seg_start and seg_end, contiguous (one memset)
+  const size_t o_ro = take(cc * 4), o_mo = take(cc * 4), o_fo = take(cc * 4);
+  const size_t o_br = take(nb * 4), o_bm = take(nb * 4), o_bf = take(nb * 4);
+  const size_t o_mr = take(cc * 4), o_rd = take(nn * 16), o_ct = take(sizeof(SegCounters));
   const size_t max_partial = (size_t)(n / kRun + n / (kRun + 1) + 2);
   const size_t o_p = take(max_partial * (size_t)D * 4);
   if (s) {
     auto u = [&](size_t o) { return reinterpret_cast<uint32_t*>(base + o); };
-    s->keyA = u(o_ka); s->valA = u(o_va); s->keyB = u(o_kb); s->valB = u(o_vb); s->hist = u(o_h); s->seg_start = u(o_ss);
-    s->runs = u(o_r); s->mruns = u(o_mr); s->run_first = u(o_rf); s->n_runs = u(o_nr);
+    s->keyA = u(o_ka); s->valA = u(o_va); s->keyB = u(o_kb); s->valB = u(o_vb); s->hist = u(o_h); s->dtot = u(o_dt);
+    s->seg_start = u(o_ss); s->seg_end = u(o_ss) + cc;
+    s->run_off = u(o_ro); s->mrun_off = u(o_mo); s->mrow_off = u(o_fo); s->bsum_r = u(o_br); s->bsum_m = u(o_bm); s->bsum_f = u(o_bf);
+    s->mrows = u(o_mr); s->run_desc = reinterpret_cast<uint4*>(base + o_rd); s->counters = reinterpret_cast<SegCounters*>(base + o_ct);
     s->partial = reinterpret_cast<float*>(base + o_p);
-    s->tiles = tiles; s->bits = bits; s->passes = passes;
+    s->tiles = tiles; s->bits = bits; s->passes = passes; s->nblocks = nblocks;
   }
   return off;
 }
@@ -223,59 +355,79 @@ static int segment_pipeline(bool fused, int order, const float* grad, const int6
   if (cap == 0) return SRM2_OK;
   if (n > 0 && (grad == nullptr || inv == nullptr)) return SRM2_ERR_ARG;
   if (fused ? (pool == nullptr || slots == nullptr || sc == nullptr) : out == nullptr) return SRM2_ERR_ARG;
-  if ((D & 3) != 0 || D > (1 << 16) || n >= ((int64_t)1 << 31) || cap >= ((int64_t)1 << 31)) return SRM2_ERR_UNSUPPORTED;
-  if (!aligned16(grad) || (fused ? !aligned16(pool) : !aligned16(out))) return SRM2_ERR_UNSUPPORTED;
+  if ((D & 3) != 0 || D > 128 * kMaxColsPerLane || n >= ((int64_t)1 << 31) || cap >= ((int64_t)1 << 31)) return SRM2_ERR_UNSUPPORTED;
+  if ((n > 0 && !aligned16(grad)) || (fused ? !aligned16(pool) : !aligned16(out))) return SRM2_ERR_UNSUPPORTED;
   if (scratch == nullptr || !aligned16(scratch) || scratch_bytes < seg_layout(n, cap, D, nullptr, nullptr)) return SRM2_ERR_SCRATCH;
   SegScratch s;
   seg_layout(n, cap, D, static_cast<char*>(scratch), &s);
   const int lpr = (int)(D / 4);
   const int shift = (lpr & (lpr - 1)) == 0 ? __builtin_ctz(lpr) : -1;
+  const bool small = order == SRM2_ORDER_WINDOWS || (order == SRM2_ORDER_AUTO && n <= kSmallN);
+  int launches = 0;
 
-  // 1. sort (key = inv, value = position)
+  // empty ranges for rows that no lookup names; counters (incl. the finished-CTA count) start at zero
+  if (note_cuda(cudaMemsetAsync(s.seg_start, 0, (size_t)(cap + 1) * 8, st))) return SRM2_ERR_CUDA;
+  if (note_cuda(cudaMemsetAsync(s.counters, 0, sizeof(SegCounters), st))) return SRM2_ERR_CUDA;
+  // 1. sort (key = inv, value = position), 2. boundaries
   const uint32_t *skey = nullptr, *spos = nullptr;
   if (n > 0) {
-    SortBuffers sb{s.keyA, s.valA, s.keyB, s.valB, s.hist, s.tiles};
-    const int rc = radix_sort_by_key(inv, n, /*mod=*/0, cap, s.bits, s.passes, sb, &skey, &spos, st);
+    SortBuffers sb{s.keyA, s.valA, s.keyB, s.valB, s.hist, s.dtot, s.tiles};
+    const uint32_t* hb = nullptr;
+    if (note_cuda(cudaMemsetAsync(s.dtot, 0, sort_dtot_words(s.bits, s.passes) * 4, st))) return SRM2_ERR_CUDA;
+    const int rc = radix_sort_by_key(inv, n, /*mod=*/0, cap, s.bits, s.passes, sb, &skey, &spos, &hb, &launches, st);
     if (rc != SRM2_OK) return rc;
+    srm2_segment_bounds_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(skey, n, s.seg_start, s.seg_end, cap);
+    ++launches;
   }
-  // 2. segment starts
-  const int grid_n = (int)((n + 255) / 256 > 0 ? (n + 255) / 256 : 1);
-  const int grid_u = (int)((cap + 256) / 256 < (int64_t)kSMs * 8 ? (cap + 256) / 256 : (int64_t)kSMs * 8);
-  srm2_segment_bounds_kernel<<<grid_u, 256, 0, st>>>(skey, n, s.seg_start, nu_host, nu_dev, cap);
   ReduceArgs a{};
-  a.grad = grad; a.D = (int)D; a.lpr = lpr; a.shift = shift; a.skey = skey; a.spos = spos; a.seg_start = s.seg_start;
-  a.run_base = s.runs; a.mrun_base = s.mruns; a.run_first = s.run_first; a.n_runs = s.n_runs; a.partial = s.partial;
+  a.grad = grad; a.D = (int)D; a.lpr = lpr; a.shift = shift; a.skey = skey; a.spos = spos; a.seg_start = s.seg_start; a.seg_end = s.seg_end;
+  a.run_desc = s.run_desc; a.mrows = s.mrows; a.counters = s.counters; a.mrun_off = s.mrun_off; a.bpre_m = s.bsum_m; a.partial = s.partial;
   a.out = out; a.pool = pool; a.slots = slots;
   if (fused) a.sc = AdamSc{sc[0], sc[1], sc[2], sc[3], sc[4], sc[5], sc[6], sc[7]};
   a.nu_host = nu_host; a.nu_dev = nu_dev; a.cap = cap; a.n = n;
-  const int64_t row_items = cap * lpr;
-  const int grid_rows = (int)((row_items + 255) / 256 < (int64_t)kSMs * 16 ? (row_items + 255) / 256 : (int64_t)kSMs * 16);
-  int launches = n > 0 ? 3 * s.passes + 1 : 1;
-  if (order == SRM2_ORDER_WINDOWS || (order == SRM2_ORDER_AUTO && n <= kSmallN)) {
+  if (small) {
+    const int64_t row_items = cap * lpr;
+    const int grid_rows = (int)((row_items + 255) / 256 < (int64_t)kSMs * 16 ? (row_items + 255) / 256 : (int64_t)kSMs * 16);
     stage_begin(st);
     if (fused) srm2_segment_windowed_kernel<true><<<grid_rows, 256, 0, st>>>(a);
     else srm2_segment_windowed_kernel<false><<<grid_rows, 256, 0, st>>>(a);
     stage_end(st);
     return launch_status(launches + 1);
   }
-  // 3. runs per segment, their exclusive scans, run descriptors
-  srm2_segment_runs_kernel<<<grid_u, 256, 0, st>>>(s.seg_start, s.runs, s.mruns, nu_host, nu_dev, cap);
-  srm2_scan_exclusive_u32_kernel<<<1, kScanThreads, 0, st>>>(s.runs, s.runs, nu_host, nu_dev, cap, 0, s.n_runs);
-  srm2_scan_exclusive_u32_kernel<<<1, kScanThreads, 0, st>>>(s.mruns, s.mruns, nu_host, nu_dev, cap, 0, nullptr);
-  srm2_segment_descr_kernel<<<grid_n, 256, 0, st>>>(skey, n, s.seg_start, s.runs, s.run_first, nu_host, nu_dev, cap);
-  // 4. run sums, then multi-run rows
+  // 3. plan, 4. descriptors
+  if (fused)
+    srm2_segment_plan_kernel<true><<<s.nblocks, kPlanThreads, 0, st>>>(a, s.run_off, s.mrun_off, s.mrow_off, s.bsum_r, s.bsum_m, s.bsum_f,
+                                                                      s.counters, s.nblocks, 0);
+  else
+    srm2_segment_plan_kernel<false><<<s.nblocks, kPlanThreads, 0, st>>>(a, s.run_off, s.mrun_off, s.mrow_off, s.bsum_r, s.bsum_m, s.bsum_f,
+                                                                       s.counters, s.nblocks, 0);
+  if (n > 0)
+    srm2_segment_descr_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(skey, n, s.seg_start, s.seg_end, s.run_off, s.mrun_off, s.mrow_off,
+                                                                          s.bsum_r, s.bsum_m, s.bsum_f, s.run_desc, s.mrows, nu_host, nu_dev, cap);
+  // 5. run sums, 6. multi-run rows
   const int64_t run_items_max = n * lpr;
-  const int grid_runs = (int)((run_items_max + 255) / 256 < (int64_t)kSMs * 16 ? (run_items_max + 255) / 256 : (int64_t)kSMs * 16);
+  const int grid_runs = (int)((run_items_max + 255) / 256 < (int64_t)kSMs * 8 ? (run_items_max + 255) / 256 : (int64_t)kSMs * 8);
+  const int rows_fit = (int)(kFinalSmemBytes / (D * 4));                 // run sums that fit the CTA's staging buffer
+  const int short_rows = rows_fit / kFinalWarps, chunk_rows = rows_fit;
+  const size_t sm_final = kFinalSmemBytes;
+  const int64_t groups_max = (n / (kRun + 1) + kFinalWarps) / kFinalWarps;
+  const int grid_final = (int)(groups_max < (int64_t)kSMs * 3 ? groups_max : (int64_t)kSMs * 3);
   stage_begin(st);
-  if (fused) {
-    srm2_segment_runsum_kernel<true><<<grid_runs, 256, 0, st>>>(a);
-    srm2_segment_final_kernel<true><<<grid_rows, 256, 0, st>>>(a);
-  } else {
-    srm2_segment_runsum_kernel<false><<<grid_runs, 256, 0, st>>>(a);
-    srm2_segment_final_kernel<false><<<grid_rows, 256, 0, st>>>(a);
+  if (n > 0) {
+    if (fused) {
+      if (sm_final > 48 * 1024 && note_cuda(cudaFuncSetAttribute(srm2_segment_final_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm_final)))
+        return SRM2_ERR_CUDA;
+      srm2_segment_runsum_kernel<true><<<grid_runs, 256, 0, st>>>(a);
+      srm2_segment_final_kernel<true><<<grid_final, kFinalThreads, sm_final, st>>>(a, short_rows, chunk_rows);
+    } else {
+      if (sm_final > 48 * 1024 && note_cuda(cudaFuncSetAttribute(srm2_segment_final_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm_final)))
+        return SRM2_ERR_CUDA;
+      srm2_segment_runsum_kernel<false><<<grid_runs, 256, 0, st>>>(a);
+      srm2_segment_final_kernel<false><<<grid_final, kFinalThreads, sm_final, st>>>(a, short_rows, chunk_rows);
+    }
   }
   stage_end(st);
-  return launch_status(launches + 6);
+  return launch_status(launches + (n > 0 ? 4 : 1));
 }
 
 }  // namespace srm2
