@@ -30,6 +30,11 @@ SIGNATURES = {
     'srm2_reduce_adam_f32': (C.c_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _i32, _f8, _vp, _sz, _vp]),
     'srm2_route_scratch_bytes': (_sz, [_i64, _i64]),
     'srm2_route_by_owner': (C.c_int, [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _sz, _vp]),
+    'srm2_dir_scratch_bytes': (_sz, [_i64]),
+    'srm2_dir_a': (C.c_int, [_vp, _vp, _i64, _vp, _vp, _i64, _vp, _i64, _i64] + [_vp] * 9 + [_vp, _sz, _vp]),
+    'srm2_dir_admit': (C.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _sz, _vp]),
+    'srm2_dir_b': (C.c_int, [_vp, _vp, _vp, _i64, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _sz, _vp]),
+    'srm2_dir_status': (C.c_int, [_vp, _vp, _vp]),
 }
 
 _lib = None

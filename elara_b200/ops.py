@@ -189,3 +189,9 @@ def reduce_adam(pool, slots, grad, inv, lr, b1, b2, eps, step, n_unique=None, co
                                     -1 if n_unique is None else cap, 0 if count is None or n_unique is not None else count.data_ptr(),
                                     cap, order, sc, scr.data_ptr(), scr.numel(), _lib.stream_of(dev))
     _lib.check(st, 'reduce_adam')
+
+
+def dir_ext():
+    """ELARA state-directory operations (reference: srm2/ops.py:32-39): object with elara_dir_a / elara_dir_b."""
+    from .directory import dir_ext as _d
+    return _d()

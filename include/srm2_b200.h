@@ -144,6 +144,63 @@ size_t srm2_route_scratch_bytes(int64_t n, int64_t world);
 int srm2_route_by_owner(const int64_t* ids, const float* grad, int64_t n, int64_t D, int64_t world, int64_t* out_lid,
                         float* out_grad, int64_t* out_counts, void* scratch, size_t scratch_bytes, srm2_stream_t stream);
 
+/* ---------------------------------------------------------------------------------------------------------
+ * ELARA state directory (device-resident).  Field for field the reference's state vector
+ * (srm2/csrc/elara_dir.cpp:8-11, built at srm2/elara.py:117-149, 275-277).  The struct itself lives on the host and
+ * is passed by pointer; all array members are device pointers.
+ */
+typedef struct srm2_dir_state {
+  int8_t* code;          /* [R]          row code: 0 = I, 1..K = L_c, MAT = M                              */
+  int32_t* loc;          /* [R+1]        MAT slot of a row (-1 none); last element unused ("trash")        */
+  int32_t* ent;          /* [(R+1)*K]    log-entry ids, row-major [R+1, K] (-1 empty); last row unused      */
+  int32_t* lstep;        /* [Lcap+1]     logical step of each log entry                                     */
+  int32_t* lfree;        /* [Lcap+1]     free stack of log ids                                              */
+  int64_t* n_lfree;      /* [1]          entries on the free stack                                          */
+  int64_t* log_top;      /* [1]          bump pointer of the log arena                                      */
+  int64_t* mat_top;      /* [1]          bump pointer of the MAT arena                                      */
+  int64_t* live;         /* [1]          live log entries                                                   */
+  int8_t* adm_c0;        /* [C]          host log entries of the resident row at admission (-1: came from M) */
+  int8_t* rj;            /* [C]          gradients recorded while resident                                  */
+  int32_t* pstep;        /* [Cdyn+1, K]  steps of the resident history of each dynamic slot                 */
+  const int8_t* kthr;    /* [T]          per-table materialisation threshold                                */
+  const int64_t* toff;   /* [T]          first row of each table, ascending                                 */
+  int32_t* slot_of;      /* [R]          pool slot of a row (-1 not resident)                               */
+  int64_t* slot_row;     /* [C]          row held by a pool slot (-1 free)                                  */
+  int8_t* rok;           /* [C]          resident history is complete (representable as log entries)        */
+  int64_t R, K, Lcap, n0, Cdyn, MAT, trash, evl, T;   /* C = n0 + Cdyn; evl: evictions may return rows to L */
+} srm2_dir_state;
+
+/* scratch for the directory calls of one plan step; max_items >= max(nev, na, nc); 256-byte aligned; the SAME buffer
+ * must be passed to srm2_dir_a, srm2_dir_admit, srm2_dir_b and srm2_dir_status of a step */
+size_t srm2_dir_scratch_bytes(int64_t max_items);
+
+/* Call A.  Replaces `elara_dir_a` (srm2/csrc/elara_dir.cpp:50-96; torch twin srm2/elara.py:285-343): replay inputs of
+ * the L rows, resident-history recording of the pool hits, representation of the evicted slots (back to L with newly
+ * allocated log ids, or to M with a MAT slot and release of their host log entries).
+ *   in : hs [nh] int64 hit slots (distinct), L_row [nL] int64, L_cnt [nL] int32, ev_slot [nev] int64 (distinct), step
+ *   out: L_steps [nL,K] int32, L_ids [nL,K] int32, hrec_dyn [nh] int64, hrec_j [nh] int64, ev_row [nev] int64,
+ *        rep [nev] uint8/bool, evl_ids [nev,K] int64, evf_slots [nev] int64, ev_dyn [nev] int64 */
+int srm2_dir_a(const srm2_dir_state* st /* host */, const int64_t* hs, int64_t nh, const int64_t* L_row, const int32_t* L_cnt,
+               int64_t nL, const int64_t* ev_slot, int64_t nev, int64_t step, int32_t* L_steps, int32_t* L_ids,
+               int64_t* hrec_dyn, int64_t* hrec_j, int64_t* ev_row, uint8_t* rep, int64_t* evl_ids, int64_t* evf_slots,
+               int64_t* ev_dyn, void* scratch, size_t scratch_bytes, srm2_stream_t stream);
+
+/* Pool-slot admissions between the two calls.  Replaces the torch statements at srm2/elara.py:358-366:
+ * adm_rows [n_adm] take adm_slots [n_adm]; the first lazy_n rows come from states I / L. */
+int srm2_dir_admit(const srm2_dir_state* st /* host */, const int64_t* adm_rows, const int64_t* adm_slots, int64_t n_adm,
+                   int64_t lazy_n, int64_t step, void* scratch, size_t scratch_bytes, srm2_stream_t stream);
+
+/* Call B.  Replaces `elara_dir_b` (srm2/csrc/elara_dir.cpp:98-110; torch twin srm2/elara.py:380-386): appends
+ * (a_rows [na], entry index a_k [na] -> a_ids [na] int64) and compactions (c_rows [nc], c_cnt [nc] -> c_slots [nc]). */
+int srm2_dir_b(const srm2_dir_state* st /* host */, const int64_t* a_rows, const int64_t* a_k, int64_t na, const int64_t* c_rows,
+               const int64_t* c_cnt, int64_t nc, int64_t step, int64_t* a_ids, int64_t* c_slots, void* scratch,
+               size_t scratch_bytes, srm2_stream_t stream);
+
+/* Copies the step's sticky error word (bit 0: row index out of range, bit 1: pool slot out of range, bit 2: log id out
+ * of range / arena overflow) to status_out (device or pinned host memory) on the stream.  The offending access was
+ * skipped, never performed.  The reference has no counterpart: it indexes unchecked. */
+int srm2_dir_status(const void* scratch, uint32_t* status_out, srm2_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
