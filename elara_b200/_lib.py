@@ -35,6 +35,8 @@ SIGNATURES = {
     'srm2_dir_admit': (C.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _sz, _vp]),
     'srm2_dir_b': (C.c_int, [_vp, _vp, _vp, _i64, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _sz, _vp]),
     'srm2_dir_status': (C.c_int, [_vp, _vp, _vp]),
+    'srm2_unique_noalloc_max_rows': (C.c_int64, []),
+    'srm2_unique_inverse_noalloc_i64': (C.c_int, [_vp, _i64, _i64, _vp, _i64, _vp, _vp, _vp]),
 }
 
 _lib = None

@@ -7,6 +7,8 @@
 // inside its word.  Kernels: mark -> per-block popcount sums (+ scan of the block sums by the last block
 // to finish) -> per-word prefixes and emission of the unique ids -> inverse.  Integer work on an
 // L2-resident table: latency-bound, a few microseconds each.
+#include <atomic>
+
 #include "common.cuh"
 #include "scan.cuh"
 
@@ -196,4 +198,58 @@ extern "C" int srm2_unique_inverse_i64(const int64_t* ids, int64_t n, int64_t n_
   srm2_unique_emit_kernel<<<(unsigned)s.nblocks, kDT, 0, st>>>(s.bitmap, s.bsum, s.wprefix, uniq, uniq_cap);
   if (n > 0) srm2_unique_inverse_kernel<<<grid_n, kDT, 0, st>>>(ids, n, n_rows, s.bitmap, s.wprefix, inv);
   return launch_status(n > 0 ? 4 : 2);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Dedup without caller-supplied scratch.
+//
+// Some hosts of this library are not in a position to hand over a scratch buffer, because they must not allocate
+// device memory at the point where they need a dedup: a process whose device memory is capped and already fully
+// committed to its tables (the reference driver can cap itself that way), a latency-critical loop that cannot afford
+// the implicit device synchronisation an allocation or a free may bring, or an embedding host in which another
+// component owns every byte of device memory.  For them the same kernels run on a fixed scratch area that is part of
+// the library image: a file-scope __device__ array.  Each GPU that loads the library carries it (about 1 MiB) until
+// the process exits.  Its size bounds the universe: at most kNoAllocMaxRows row ids.
+//
+// The array's name is only a host-side handle; the kernels need its device address, which the runtime reports per
+// device.  The first call on a device looks the address up (cudaGetSymbolAddress, with that device current) and keeps
+// it; later calls on that device reuse it.
+namespace srm2 {
+
+constexpr int64_t kNoAllocMaxRows = 4194304;                                   // 2^22 rows
+constexpr size_t kNoAllocScratchBytes = 2 * (size_t)(kNoAllocMaxRows / 32) * 4 + 1024;   // bitmap + word prefixes + counters
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+constexpr int kNoAllocMaxDevices = 64;
+static std::atomic<void*> g_noalloc_addr[kNoAllocMaxDevices];                  // device address of the array, per device
+
+// Device address of g_noalloc_scratch on the current device (looked up once per device), or nullptr with *rc set.
+static void* noalloc_scratch_address(int* rc) {
+  int dev = -1;
+  if ((*rc = note_cuda(cudaGetDevice(&dev))) != SRM2_OK) return nullptr;
+  if (dev < 0 || dev >= kNoAllocMaxDevices) { *rc = SRM2_ERR_UNSUPPORTED; return nullptr; }
+  void* p = g_noalloc_addr[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
+    if ((*rc = note_cuda(cudaGetSymbolAddress(&p, g_noalloc_scratch))) != SRM2_OK) return nullptr;
+    g_noalloc_addr[dev].store(p, std::memory_order_release);                   // every thread finds the same address
+  }
+  return p;
+}
+
+}  // namespace srm2
+
+extern "C" int64_t srm2_unique_noalloc_max_rows(void) { return srm2::kNoAllocMaxRows; }
+
+extern "C" int srm2_unique_inverse_noalloc_i64(const int64_t* ids, int64_t n, int64_t n_rows, int64_t* uniq, int64_t uniq_cap,
+                                               int64_t* inv, int64_t* out_count, srm2_stream_t stream) {
+  using namespace srm2;
+  if (n_rows <= 0) return SRM2_ERR_ARG;
+  if (n_rows > kNoAllocMaxRows || dedup_layout(n_rows, nullptr, nullptr) > kNoAllocScratchBytes) return SRM2_ERR_LIMIT;
+  int rc = SRM2_OK;
+  void* scratch = noalloc_scratch_address(&rc);
+  if (scratch == nullptr) return rc;
+  // The shared array still holds whatever the previous call left there.  The dedup entry point clears everything that
+  // has to start at zero (bitmap, block counter, result counts) on the caller's stream before its kernels run.
+  return srm2_unique_inverse_i64(ids, n, n_rows, uniq, uniq_cap, inv, out_count, scratch, kNoAllocScratchBytes, stream);
 }

@@ -42,6 +42,7 @@ extern "C" const char* srm2_status_string(int status) {
     case SRM2_ERR_UNSUPPORTED: return "size not supported";
     case SRM2_ERR_SCRATCH: return "scratch buffer too small";
     case SRM2_ERR_CUDA: return "CUDA runtime error";
+    case SRM2_ERR_LIMIT: return "size exceeds the built-in scratch of the no-allocation entry point";
     default: return "unknown status";
   }
 }

@@ -28,6 +28,7 @@ extern "C" {
 #define SRM2_ERR_UNSUPPORTED (-2) /* a size outside what the kernels are built for                  */
 #define SRM2_ERR_SCRATCH (-3)     /* scratch buffer too small (see the *_scratch_bytes functions)   */
 #define SRM2_ERR_CUDA (-4)        /* the CUDA runtime refused a launch; see srm2_last_cuda_error()  */
+#define SRM2_ERR_LIMIT (-5)       /* larger than the fixed scratch of srm2_unique_inverse_noalloc_i64 */
 
 typedef void* srm2_stream_t;
 
@@ -200,6 +201,28 @@ int srm2_dir_b(const srm2_dir_state* st /* host */, const int64_t* a_rows, const
  * of range / arena overflow) to status_out (device or pinned host memory) on the stream.  The offending access was
  * skipped, never performed.  The reference has no counterpart: it indexes unchecked. */
 int srm2_dir_status(const void* scratch, uint32_t* status_out, srm2_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Dedup for callers that cannot provide scratch memory.  No counterpart in the reference.
+ *
+ * Same inputs, outputs and results as srm2_unique_inverse_i64, but no scratch argument: the kernels work on a fixed
+ * area inside the library image (a __device__ array of about 1 MiB that every GPU loading the library holds until the
+ * process ends).  Meant for hosts that must not allocate device memory where they need the dedup — a process whose
+ * memory cap is already spent on its tables, a loop that cannot take the device-wide synchronisation an allocation
+ * may cause, a host whose device memory belongs to another allocator.  The entry point itself allocates and frees
+ * nothing, on the device or through any library.
+ *   - Limit: n_rows <= srm2_unique_noalloc_max_rows() (4,194,304); beyond it the call returns SRM2_ERR_LIMIT and
+ *     enqueues nothing.
+ *   - First use on a device: the first call made while a given device is current asks the CUDA runtime for the device
+ *     address of the area (cudaGetSymbolAddress) and remembers it for that device.  Make that first call outside any
+ *     stream capture.
+ *   - The area is shared by every call in the process and keeps the previous call's contents; each call clears what it
+ *     needs zeroed, on its own stream.  Two calls whose kernels may overlap on one GPU (different streams without an
+ *     ordering between them, or different host threads) race on the area and give undefined results: order them.
+ */
+int64_t srm2_unique_noalloc_max_rows(void);
+int srm2_unique_inverse_noalloc_i64(const int64_t* ids, int64_t n, int64_t n_rows, int64_t* uniq, int64_t uniq_cap,
+                                    int64_t* inv, int64_t* out_count, srm2_stream_t stream);
 
 #ifdef __cplusplus
 }
