@@ -1,0 +1,52 @@
+"""Worker of tests/test_gpu_multi.py, started by torchrun with one rank per GPU: runs the row-sharded step on the GPUs
+(routing kernel, NCCL all-to-all, dedup + fused reduce + Adam on every shard) and compares every shard bit for bit with
+the single-process CPU oracle on the whole batch."""
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+HYP = (1e-3, 0.9, 0.999, 1e-8)
+
+
+def main():
+    rank, world, local = int(os.environ['RANK']), int(os.environ['WORLD_SIZE']), int(os.environ['LOCAL_RANK'])
+    torch.cuda.set_device(local)
+    dev = torch.device('cuda', local)
+    dist.init_process_group('nccl', device_id=dev)
+    from elara_b200 import synth
+    from elara_b200.sharded import ShardedSparseAdam
+    from oracle import oracle as O
+    total_rows, D, batch = 200_000, 64, 512
+    sizes, offs = synth.table_sizes(total_rows, 26, lo=4, hi=60_000, seed=3)
+    eng = ShardedSparseAdam(total_rows, D, world, rank, dev, seed=42, bound=0.01, hyper=HYP, max_lookups_per_rank=batch * 26,
+                            group=dist.group.WORLD)
+    st = O.init_rows(np.arange(total_rows), D, 42, 0.01)
+    rows_updated = 0
+    for step in (1, 2, 3):
+        ids = synth.zipf_lookups(sizes, offs, batch, 1.1, 7, step, first_sample=rank * batch)
+        grad = synth.normal_f32((len(ids), D), 1e-3, 7, step, stream=10 + rank)
+        c = eng.step(torch.from_numpy(ids).to(dev), torch.from_numpy(grad).to(dev), step)
+        rows_updated += int(c[0])
+        gids = np.concatenate([synth.zipf_lookups(sizes, offs, batch, 1.1, 7, step, first_sample=r * batch) for r in range(world)])
+        ggrad = np.concatenate([synth.normal_f32((batch * 26, D), 1e-3, 7, step, stream=10 + r) for r in range(world)])
+        u, inv = O.unique_inverse(gids)
+        O.adam_rows(st, u, O.segment_reduce(ggrad, inv, len(u)), *HYP, step)
+    shard = eng.pool.cpu().numpy()
+    ok = np.array_equal(shard.view(np.uint32), st[rank::world].view(np.uint32))
+    flag = torch.tensor([int(ok), rows_updated], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print(f'MULTI_GPU_RESULT ok={int(flag[0])} world={world} rows_updated_min={int(flag[1])}', flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(0 if ok else 1)
+
+
+if __name__ == '__main__':
+    main()
