@@ -31,14 +31,13 @@ constexpr int kRun = 10;            // lookups per run (large inputs)
 constexpr int kSmallN = 3072;       // inputs up to this many lookups use the windowed order
 constexpr int kWindow = 32;
 constexpr int kPlanThreads = 256;
-constexpr uint32_t kNoSlot = 0xffffffffu;
 
 struct SegCounters { uint32_t n_runs, n_mrows, n_mruns, done; };
 
 struct ReduceArgs {
   const float* grad; int D; int lpr; int shift;
   const uint32_t* skey; const uint32_t* spos; const uint32_t* seg_start; const uint32_t* seg_end;
-  const uint4* run_desc; const uint32_t* mrows; const SegCounters* counters;
+  const uint4* run_desc; const uint32_t* run_pos; const uint32_t* mrows; uint4* mrow_info; const SegCounters* counters; int inplace;
   const uint32_t* mrun_off; const uint32_t* bpre_m;
   float* partial;
   float* out;                                     // [nu, D] (unfused) or nullptr
@@ -133,62 +132,184 @@ srm2_segment_plan_kernel(ReduceArgs a, uint32_t* __restrict__ run_off, uint32_t*
   if (threadIdx.x == 0) { counters->n_runs = cr; counters->n_mruns = cm; counters->n_mrows = cf; counters->done = 0u; }
 }
 
-// Run descriptors and the list of multi-run rows; one thread per sorted lookup.
+// Run descriptors and the multi-run rows; one thread per sorted lookup, the first lookup of a run writes.
+//   run_desc[c] = {first sorted index, length | kMultiBit, z, w}
+//     run of a multi-run row: c = its partial slot (these runs come first), z = partial slot, w = index of the row in
+//                             mrow_info;  single-run row: c = n_mruns + rank among single-run rows, (z, w) = 64-bit
+//                             target: the pool row (fused) or the unique row index.
+//   mrow_info[mi] = {unique row, number of runs, first partial slot, finished-run counter = 0}
+constexpr uint32_t kMultiBit = 0x80000000u;
 __global__ void __launch_bounds__(256)
-srm2_segment_descr_kernel(const uint32_t* __restrict__ skey, int64_t n, const uint32_t* __restrict__ seg_start,
+srm2_segment_descr_kernel(const uint32_t* __restrict__ skey, const uint32_t* __restrict__ spos, int64_t n,
+                          const uint32_t* __restrict__ seg_start,
                           const uint32_t* __restrict__ seg_end, const uint32_t* __restrict__ run_off,
                           const uint32_t* __restrict__ mrun_off, const uint32_t* __restrict__ mrow_off,
                           const uint32_t* __restrict__ bpre_r, const uint32_t* __restrict__ bpre_m,
-                          const uint32_t* __restrict__ bpre_f, uint4* __restrict__ run_desc, uint32_t* __restrict__ mrows,
-                          int64_t nu_host, const int64_t* __restrict__ nu_dev, int64_t cap) {
+                          const uint32_t* __restrict__ bpre_f, const SegCounters* __restrict__ counters,
+                          const int64_t* __restrict__ slots, uint4* __restrict__ run_desc, uint32_t* __restrict__ run_pos,
+                          uint32_t* __restrict__ mrows, uint4* __restrict__ mrow_info, int64_t nu_host,
+                          const int64_t* __restrict__ nu_dev, int64_t cap) {
   const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
   if (i >= n) return;
   const uint32_t j = skey[i];
   if ((int64_t)j >= load_nu(nu_host, nu_dev, cap)) return;
-  const uint32_t s = seg_start[j];
+  const uint32_t s = seg_start[j], e = seg_end[j];
   const uint32_t off = (uint32_t)i - s;
-  if (off % kRun != 0) return;
-  const uint32_t e = seg_end[j];
   const bool multi = e - s > (uint32_t)kRun;
-  const uint32_t blk = j / kPlanThreads, ri = off / kRun;
-  const uint32_t c = bpre_r[blk] + run_off[j] + ri;
+  const uint32_t blk = j / kPlanThreads, ri = off / kRun, rq = off - ri * kRun;
+  const uint32_t rbase = bpre_r[blk] + run_off[j], mbase = bpre_m[blk] + mrun_off[j];
+  const uint32_t c = multi ? mbase + ri : counters->n_mruns + (rbase - mbase);
+  run_pos[(int64_t)c * kRun + rq] = spos[i];             // positions of run c, padded to kRun per run
+  if (rq != 0) return;
   const uint32_t len = min((uint32_t)kRun, e - (uint32_t)i);
-  const uint32_t pslot = multi ? bpre_m[blk] + mrun_off[j] + ri : kNoSlot;
-  run_desc[c] = make_uint4((uint32_t)i, j, len, pslot);
-  if (off == 0 && multi) mrows[bpre_f[blk] + mrow_off[j]] = j;
-}
-
-// ------------------------------------------------------------------------------------------ run sums
-// One thread per (run, 16-byte lane).  Sums the <= 10 gradient rows of the run from +0; a row with a single run is
-// finished here ((+0) + run sum), otherwise the run sum goes to the partial buffer.
-template <bool FUSED>
-__global__ void __launch_bounds__(256)
-srm2_segment_runsum_kernel(ReduceArgs a) {
-  const int64_t items = (int64_t)a.counters->n_runs * a.lpr;
-  for (int64_t t = (int64_t)blockIdx.x * 256 + threadIdx.x; t < items; t += (int64_t)gridDim.x * 256) {
-    int64_t c; int j4;
-    if (a.shift >= 0) { c = t >> a.shift; j4 = (int)(t & (a.lpr - 1)); } else { c = t / a.lpr; j4 = (int)(t - c * a.lpr); }
-    const uint4 d = __ldg(a.run_desc + c);          // {first, row, len, partial slot}
-    float4 g[kRun];
-#pragma unroll
-    for (int q = 0; q < kRun; ++q)
-      if (q < (int)d.z) g[q] = ld_stream4(a.grad + (int64_t)__ldg(a.spos + d.x + q) * a.D + j4 * 4);
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-    for (int q = 0; q < kRun; ++q)
-      if (q < (int)d.z) acc = add4(acc, g[q]);
-    if (d.w == kNoSlot) finish_row<FUSED>(a, d.y, j4, add4(make_float4(0.f, 0.f, 0.f, 0.f), acc));
-    else *reinterpret_cast<float4*>(a.partial + (int64_t)d.w * a.D + j4 * 4) = acc;
+  if (multi) {
+    const uint32_t mi = bpre_f[blk] + mrow_off[j];
+    run_desc[c] = make_uint4((uint32_t)i, len | kMultiBit, c, mi);
+    if (off == 0) { mrows[mi] = j; mrow_info[mi] = make_uint4(j, (e - s + kRun - 1) / kRun, mbase, 0u); }
+  } else {
+    const uint64_t target = slots ? (uint64_t)slots[j] : (uint64_t)j;
+    run_desc[c] = make_uint4((uint32_t)i, len, (uint32_t)target, (uint32_t)(target >> 32));
   }
 }
 
-// ------------------------------------------------------------------------------------------ multi-run rows
+// ------------------------------------------------------------------------------------------ run sums
+// Finishes a row whose state (fused) was loaded ahead of time.
+template <bool FUSED>
+__device__ __forceinline__ void finish_loaded(const ReduceArgs& a, float* b, float4 w, float4 m, float4 v, const float4& g) {
+  if (FUSED) {
+    adam_vec4(w, m, v, g, a.sc);
+    *reinterpret_cast<float4*>(b) = w; *reinterpret_cast<float4*>(b + a.D) = m; *reinterpret_cast<float4*>(b + 2 * a.D) = v;
+  } else {
+    *reinterpret_cast<float4*>(b) = g;
+  }
+}
+
+// One thread per (run, 16-byte lane).  Sums the <= 10 gradient rows of the run from +0.
+//  - single-run row: finished here ((+0) + run sum); its (w, m, v) loads are issued together with the gradient loads;
+//  - run of a multi-run row: the run sum goes to the partial buffer.  With a.inplace (the D/4 lanes of a run are an
+//    aligned part of one warp) the group then counts itself finished on the row; the group that completes the row adds
+//    the row's run sums in order and finishes the row — nobody waits, and the long rows (whose runs come first in the
+//    descriptor order) are finished while the bulk of the single-run rows is still streaming.  Without a.inplace a
+//    separate kernel adds the run sums.
+struct RunItem { uint4 d; uint2 p[kRun / 2]; };
+
+__device__ __forceinline__ void load_item(const ReduceArgs& a, int64_t c, RunItem& it) {
+  it.d = __ldg(a.run_desc + c);
+  const uint2* pp = reinterpret_cast<const uint2*>(a.run_pos + c * kRun);
+#pragma unroll
+  for (int q = 0; q < kRun / 2; ++q) it.p[q] = __ldg(pp + q);
+}
+
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
   const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+#ifndef SRM2_RUN_PREFETCH
+#define SRM2_RUN_PREFETCH 1
+#endif
+constexpr bool kRunPrefetch = SRM2_RUN_PREFETCH != 0;
+constexpr int kRunThreads = 256;
+constexpr int kRunStageVecs = kRun + 3;                                  // gradient rows + w, m, v
+constexpr int kRunSmemBytes = kRunStageVecs * kRunThreads * 16;         // 53,248 B per CTA
+
+// Every thread stages its own 16-byte pieces — up to 10 gradient rows and, for a single-run row, w, m, v — in shared
+// memory with cp.async: the bytes in flight no longer occupy registers, so four CTAs fit an SM and each thread keeps
+// up to 208 B outstanding.  A thread only reads back what it copied itself: cp.async.wait_group is the only wait.
+template <bool FUSED, bool PREFETCH>
+__global__ void __launch_bounds__(kRunThreads)
+srm2_segment_runsum_kernel(ReduceArgs a) {
+  extern __shared__ float4 stage[];                 // [kRunStageVecs][kRunThreads]
+  float4* mine = stage + threadIdx.x;
+  const int64_t items = (int64_t)a.counters->n_runs * a.lpr;
+  const int lane = threadIdx.x & 31;
+  const unsigned gmask = a.lpr >= 32 ? 0xffffffffu : (((1u << a.lpr) - 1u) << (lane & ~(a.lpr - 1)));
+  const int gleader = a.lpr >= 32 ? 0 : (lane & ~(a.lpr - 1));
+  const int64_t stride = (int64_t)gridDim.x * kRunThreads;
+  int64_t t = (int64_t)blockIdx.x * kRunThreads + threadIdx.x;
+  auto split = [&](int64_t tt, int64_t& c, int& j4) {
+    if (a.shift >= 0) { c = tt >> a.shift; j4 = (int)(tt & (a.lpr - 1)); } else { c = tt / a.lpr; j4 = (int)(tt - c * a.lpr); }
+  };
+  RunItem cur, nxt;
+  int64_t c; int j4;
+  if (PREFETCH && t < items) { split(t, c, j4); load_item(a, c, cur); }
+  for (; t < items; t += stride) {
+    split(t, c, j4);
+    if (!PREFETCH) load_item(a, c, cur);
+    const uint4 d = cur.d;
+    const int len = (int)(d.y & 0xffu);
+    const bool multi = (d.y & kMultiBit) != 0;
+    // ---- all copies of this item ----
+    float* b = nullptr;
+    if (!multi) {
+      const int64_t target = (int64_t)((uint64_t)d.z | ((uint64_t)d.w << 32));
+      if (FUSED) {
+        b = a.pool + target * (3 * (int64_t)a.D) + j4 * 4;
+        cp_async16(mine + kRun * kRunThreads, b); cp_async16(mine + (kRun + 1) * kRunThreads, b + a.D);
+        cp_async16(mine + (kRun + 2) * kRunThreads, b + 2 * a.D);
+      } else {
+        b = a.out + target * (int64_t)a.D + j4 * 4;
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < kRun; ++q) {
+      const uint32_t pos = (q & 1) ? cur.p[q / 2].y : cur.p[q / 2].x;
+      if (q < len) cp_async16(mine + q * kRunThreads, a.grad + (int64_t)pos * a.D + j4 * 4);
+    }
+    cp_async_commit();
+    if (PREFETCH && t + stride < items) { int64_t cn; int jn; split(t + stride, cn, jn); load_item(a, cn, nxt); }
+    cp_async_wait<0>();
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int q = 0; q < kRun; ++q)
+      if (q < len) acc = add4(acc, mine[q * kRunThreads]);
+    if (PREFETCH) cur = nxt;
+    if (!multi) {
+      const float4 g = add4(make_float4(0.f, 0.f, 0.f, 0.f), acc);
+      if (FUSED) {
+        float4 w = mine[kRun * kRunThreads], m = mine[(kRun + 1) * kRunThreads], v = mine[(kRun + 2) * kRunThreads];
+        adam_vec4(w, m, v, g, a.sc);
+        *reinterpret_cast<float4*>(b) = w; *reinterpret_cast<float4*>(b + a.D) = m; *reinterpret_cast<float4*>(b + 2 * a.D) = v;
+      } else {
+        *reinterpret_cast<float4*>(b) = g;
+      }
+      continue;
+    }
+    float* pp = a.partial + (int64_t)d.z * a.D + j4 * 4;
+    if (!a.inplace) { *reinterpret_cast<float4*>(pp) = acc; continue; }
+    __stcg(reinterpret_cast<float4*>(pp), acc);
+    __threadfence();
+    __syncwarp(gmask);
+    uint4 info = make_uint4(0u, 0u, 0u, 0u);
+    if (lane == gleader) {
+      info = __ldcg(reinterpret_cast<const uint4*>(a.mrow_info + d.w));
+      const uint32_t old = atomicAdd(&a.mrow_info[d.w].w, 1u);
+      info.w = old;
+    }
+    info.x = __shfl_sync(gmask, info.x, gleader); info.y = __shfl_sync(gmask, info.y, gleader);
+    info.z = __shfl_sync(gmask, info.z, gleader); info.w = __shfl_sync(gmask, info.w, gleader);
+    if (info.w != info.y - 1u) continue;               // not the last run of the row to finish
+    __threadfence();
+    // the group that completes a row adds its run sums in order, staging kRun of them at a time the same way
+    const float* p = a.partial + (int64_t)info.z * a.D + j4 * 4;
+    float4 tot = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (uint32_t r0 = 0; r0 < info.y; r0 += kRun) {
+      const int cnt = (int)min((uint32_t)kRun, info.y - r0);
+#pragma unroll
+      for (int e = 0; e < kRun; ++e)
+        if (e < cnt) cp_async16(mine + e * kRunThreads, p + (int64_t)(r0 + e) * a.D);
+      cp_async_commit(); cp_async_wait<0>();
+#pragma unroll
+      for (int e = 0; e < kRun; ++e)
+        if (e < cnt) tot = add4(tot, mine[e * kRunThreads]);
+    }
+    finish_row<FUSED>(a, info.x, j4, tot);
+  }
+}
+
+// ------------------------------------------------------------------------------------------ multi-run rows
 
 constexpr int kFinalWarps = 4;
 constexpr int kFinalThreads = kFinalWarps * 32;
@@ -310,7 +431,7 @@ srm2_segment_windowed_kernel(ReduceArgs a) {
 // ------------------------------------------------------------------------------------------ host side
 struct SegScratch {
   uint32_t *keyA, *valA, *keyB, *valB, *hist, *dtot, *seg_start, *seg_end, *run_off, *mrun_off, *mrow_off, *bsum_r, *bsum_m, *bsum_f, *mrows;
-  uint4* run_desc; SegCounters* counters; float* partial;
+  uint4* run_desc; uint32_t* run_pos; uint4* mrow_info; SegCounters* counters; float* partial;
   int tiles, bits, passes, nblocks;
 };
 
@@ -332,7 +453,7 @@ static size_t seg_layout(int64_t n, int64_t cap, int64_t D, char* base, SegScrat
   const size_t o_ss = take(cc * 4 * 2);                          // seg_start and seg_end, contiguous (one memset)
   const size_t o_ro = take(cc * 4), o_mo = take(cc * 4), o_fo = take(cc * 4);
   const size_t o_br = take(nb * 4), o_bm = take(nb * 4), o_bf = take(nb * 4);
-  const size_t o_mr = take(cc * 4), o_rd = take(nn * 16), o_ct = take(sizeof(SegCounters));
+  const size_t o_mr = take(cc * 4), o_rd = take(nn * 16), o_rp = take((nn * kRun + 16) * 4), o_mi = take((nn / (kRun + 1) + 2) * 16), o_ct = take(sizeof(SegCounters));
   const size_t max_partial = (size_t)(n / kRun + n / (kRun + 1) + 2);
   const size_t o_p = take(max_partial * (size_t)D * 4);
   if (s) {
@@ -340,7 +461,7 @@ static size_t seg_layout(int64_t n, int64_t cap, int64_t D, char* base, SegScrat
     s->keyA = u(o_ka); s->valA = u(o_va); s->keyB = u(o_kb); s->valB = u(o_vb); s->hist = u(o_h); s->dtot = u(o_dt);
     s->seg_start = u(o_ss); s->seg_end = u(o_ss) + cc;
     s->run_off = u(o_ro); s->mrun_off = u(o_mo); s->mrow_off = u(o_fo); s->bsum_r = u(o_br); s->bsum_m = u(o_bm); s->bsum_f = u(o_bf);
-    s->mrows = u(o_mr); s->run_desc = reinterpret_cast<uint4*>(base + o_rd); s->counters = reinterpret_cast<SegCounters*>(base + o_ct);
+    s->mrows = u(o_mr); s->run_desc = reinterpret_cast<uint4*>(base + o_rd); s->run_pos = u(o_rp); s->mrow_info = reinterpret_cast<uint4*>(base + o_mi); s->counters = reinterpret_cast<SegCounters*>(base + o_ct);
     s->partial = reinterpret_cast<float*>(base + o_p);
     s->tiles = tiles; s->bits = bits; s->passes = passes; s->nblocks = nblocks;
   }
@@ -381,7 +502,8 @@ static int segment_pipeline(bool fused, int order, const float* grad, const int6
   }
   ReduceArgs a{};
   a.grad = grad; a.D = (int)D; a.lpr = lpr; a.shift = shift; a.skey = skey; a.spos = spos; a.seg_start = s.seg_start; a.seg_end = s.seg_end;
-  a.run_desc = s.run_desc; a.mrows = s.mrows; a.counters = s.counters; a.mrun_off = s.mrun_off; a.bpre_m = s.bsum_m; a.partial = s.partial;
+  a.run_desc = s.run_desc; a.run_pos = s.run_pos; a.mrows = s.mrows; a.mrow_info = s.mrow_info; a.counters = s.counters;
+  a.inplace = (lpr <= 32 && (lpr & (lpr - 1)) == 0) ? 1 : 0; a.mrun_off = s.mrun_off; a.bpre_m = s.bsum_m; a.partial = s.partial;
   a.out = out; a.pool = pool; a.slots = slots;
   if (fused) a.sc = AdamSc{sc[0], sc[1], sc[2], sc[3], sc[4], sc[5], sc[6], sc[7]};
   a.nu_host = nu_host; a.nu_dev = nu_dev; a.cap = cap; a.n = n;
@@ -402,8 +524,9 @@ static int segment_pipeline(bool fused, int order, const float* grad, const int6
     srm2_segment_plan_kernel<false><<<s.nblocks, kPlanThreads, 0, st>>>(a, s.run_off, s.mrun_off, s.mrow_off, s.bsum_r, s.bsum_m, s.bsum_f,
                                                                        s.counters, s.nblocks, 0);
   if (n > 0)
-    srm2_segment_descr_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(skey, n, s.seg_start, s.seg_end, s.run_off, s.mrun_off, s.mrow_off,
-                                                                          s.bsum_r, s.bsum_m, s.bsum_f, s.run_desc, s.mrows, nu_host, nu_dev, cap);
+    srm2_segment_descr_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(skey, spos, n, s.seg_start, s.seg_end, s.run_off, s.mrun_off, s.mrow_off,
+                                                                          s.bsum_r, s.bsum_m, s.bsum_f, s.counters, fused ? slots : nullptr, s.run_desc, s.run_pos, s.mrows, s.mrow_info,
+                                                                          nu_host, nu_dev, cap);
   // 5. run sums, 6. multi-run rows
   const int64_t run_items_max = n * lpr;
   const int grid_runs = (int)((run_items_max + 255) / 256 < (int64_t)kSMs * 8 ? (run_items_max + 255) / 256 : (int64_t)kSMs * 8);
@@ -417,17 +540,19 @@ static int segment_pipeline(bool fused, int order, const float* grad, const int6
     if (fused) {
       if (sm_final > 48 * 1024 && note_cuda(cudaFuncSetAttribute(srm2_segment_final_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm_final)))
         return SRM2_ERR_CUDA;
-      srm2_segment_runsum_kernel<true><<<grid_runs, 256, 0, st>>>(a);
-      srm2_segment_final_kernel<true><<<grid_final, kFinalThreads, sm_final, st>>>(a, short_rows, chunk_rows);
+      if (note_cuda(cudaFuncSetAttribute(srm2_segment_runsum_kernel<true, kRunPrefetch>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRunSmemBytes))) return SRM2_ERR_CUDA;
+      srm2_segment_runsum_kernel<true, kRunPrefetch><<<grid_runs, kRunThreads, kRunSmemBytes, st>>>(a);
+      if (!a.inplace) srm2_segment_final_kernel<true><<<grid_final, kFinalThreads, sm_final, st>>>(a, short_rows, chunk_rows);
     } else {
       if (sm_final > 48 * 1024 && note_cuda(cudaFuncSetAttribute(srm2_segment_final_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm_final)))
         return SRM2_ERR_CUDA;
-      srm2_segment_runsum_kernel<false><<<grid_runs, 256, 0, st>>>(a);
-      srm2_segment_final_kernel<false><<<grid_final, kFinalThreads, sm_final, st>>>(a, short_rows, chunk_rows);
+      if (note_cuda(cudaFuncSetAttribute(srm2_segment_runsum_kernel<false, kRunPrefetch>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRunSmemBytes))) return SRM2_ERR_CUDA;
+      srm2_segment_runsum_kernel<false, kRunPrefetch><<<grid_runs, kRunThreads, kRunSmemBytes, st>>>(a);
+      if (!a.inplace) srm2_segment_final_kernel<false><<<grid_final, kFinalThreads, sm_final, st>>>(a, short_rows, chunk_rows);
     }
   }
   stage_end(st);
-  return launch_status(launches + (n > 0 ? 4 : 1));
+  return launch_status(launches + (n > 0 ? (a.inplace ? 3 : 4) : 1));
 }
 
 }  // namespace srm2

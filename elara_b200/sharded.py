@@ -62,6 +62,7 @@ class ShardedSparseAdam:
             self._lid = torch.empty(n, dtype=torch.int64, device=device)
             self._grad = torch.empty(n, D, device=device)
             self._counts = torch.empty(world, dtype=torch.int64, device=device)
+            self._pipe = None
 
     def route(self, ids, grads):
         """-> (lids grouped by owner, gradient rows in the same order, per-owner counts on the device)."""
@@ -96,3 +97,86 @@ class ShardedSparseAdam:
         self.last_local_lookups = recv_lids.numel()
         self.last_local_lookups_total += recv_lids.numel()
         return count
+
+    # ------------------------------------------------------------------------------------------------------------
+    # Software-pipelined form for a sequence of steps whose inputs are known ahead (a training loop reads its batches
+    # ahead of the optimizer): routing and the all-to-all of step s+1 run on a second stream while the shard update of
+    # step s runs on the caller's stream; the host reads the split sizes of step s+1 while the GPU is busy with step s,
+    # so the read never leaves the GPU idle.  Results are identical to calling step() in order.
+    def _pipe_buffers(self, n_max):
+        if self._pipe is None or self._pipe['n'] < n_max:
+            cap = 2 * n_max + 1024                                  # room for an unbalanced owner
+            mk = lambda *shape, dt=torch.float32: torch.empty(*shape, dtype=dt, device=self.dev)
+            self._pipe = dict(n=n_max, cap=cap, comm=torch.cuda.Stream(self.dev),
+                              lid=[mk(n_max, dt=torch.int64) for _ in range(2)], grad=[mk(n_max, self.D) for _ in range(2)],
+                              counts=[mk(self.world, dt=torch.int64) for _ in range(2)], rcounts=[mk(self.world, dt=torch.int64) for _ in range(2)],
+                              hcounts=[torch.empty(2, self.world, dtype=torch.int64).pin_memory() for _ in range(2)],
+                              rlid=[mk(cap, dt=torch.int64) for _ in range(2)], rgrad=[mk(cap, self.D) for _ in range(2)])
+        return self._pipe
+
+    def run_steps(self, batches, first_step):
+        """batches: list of (ids, grads) of this rank, one per step; step numbers first_step, first_step+1, ...
+        Returns the list of per-step count tensors (see step())."""
+        import torch.distributed as dist
+        if self.world == 1:
+            return [self.step(i, g, first_step + k) for k, (i, g) in enumerate(batches)]
+        K = len(batches)
+        P = self._pipe_buffers(max(i.numel() for i, _ in batches))
+        comm, comp = P['comm'], torch.cuda.current_stream(self.dev)
+        L = _lib.lib()
+        ev_counts = [torch.cuda.Event() for _ in range(K)]
+        ev_payload = [torch.cuda.Event() for _ in range(K)]
+        ev_done = [torch.cuda.Event() for _ in range(K)]
+        ev_start = torch.cuda.Event(); ev_start.record(comp)
+        recv_n = [0] * K
+
+        def prepare(k):                       # route + exchange of the counts, on the side stream
+            ids, grads = batches[k]
+            b = k & 1
+            n = ids.numel()
+            with torch.cuda.stream(comm):
+                if k >= 2:
+                    comm.wait_event(ev_done[k - 2])           # the buffers of this parity are free again
+                nb = L.srm2_route_scratch_bytes(n, self.world)
+                scr = ops._scratch(self.dev, nb, 'route')
+                st = L.srm2_route_by_owner(_lib.ptr(ids), _lib.ptr(grads), n, self.D, self.world, P['lid'][b].data_ptr(),
+                                           P['grad'][b].data_ptr(), P['counts'][b].data_ptr(), scr.data_ptr(), scr.numel(),
+                                           comm.cuda_stream)
+                _lib.check(st, 'route_by_owner')
+                dist.all_to_all_single(P['rcounts'][b], P['counts'][b], group=self.group)
+                P['hcounts'][b][0].copy_(P['counts'][b], non_blocking=True)
+                P['hcounts'][b][1].copy_(P['rcounts'][b], non_blocking=True)
+                ev_counts[k].record(comm)
+
+        def payload(k):                       # needs the split sizes on the host
+            b = k & 1
+            n = batches[k][0].numel()
+            ev_counts[k].synchronize()
+            send = P['hcounts'][b][0].tolist(); recv = P['hcounts'][b][1].tolist()
+            nr = int(sum(recv))
+            if nr > P['cap']:
+                raise RuntimeError('receive buffer too small for this batch')
+            recv_n[k] = nr
+            with torch.cuda.stream(comm):
+                dist.all_to_all_single(P['rlid'][b][:nr], P['lid'][b][:n], output_split_sizes=recv, input_split_sizes=send, group=self.group)
+                dist.all_to_all_single(P['rgrad'][b][:nr], P['grad'][b][:n], output_split_sizes=recv, input_split_sizes=send, group=self.group)
+                ev_payload[k].record(comm)
+
+        comm.wait_event(ev_start)
+        prepare(0); payload(0)
+        out = []
+        for k in range(K):
+            b = k & 1
+            if k + 1 < K:
+                prepare(k + 1)
+            comp.wait_event(ev_payload[k])
+            nr = recv_n[k]
+            u, inv, count = ops.unique_inverse(P['rlid'][b][:nr], max(self.n_local, 1), sync=False)
+            ops.reduce_adam(self.pool, u, P['rgrad'][b][:nr], inv, *self.hyper, first_step + k, count=count, order=ops.ORDER_RUNS)
+            ev_done[k].record(comp)
+            self.last_local_lookups = nr
+            self.last_local_lookups_total += nr
+            out.append(count)
+            if k + 1 < K:
+                payload(k + 1)
+        return out

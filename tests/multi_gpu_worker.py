@@ -26,19 +26,26 @@ def main():
     sizes, offs = synth.table_sizes(total_rows, 26, lo=4, hi=60_000, seed=3)
     eng = ShardedSparseAdam(total_rows, D, world, rank, dev, seed=42, bound=0.01, hyper=HYP, max_lookups_per_rank=batch * 26,
                             group=dist.group.WORLD)
+    eng2 = ShardedSparseAdam(total_rows, D, world, rank, dev, seed=42, bound=0.01, hyper=HYP, max_lookups_per_rank=batch * 26,
+                             group=dist.group.WORLD)
     st = O.init_rows(np.arange(total_rows), D, 42, 0.01)
     rows_updated = 0
+    batches = []
     for step in (1, 2, 3):
         ids = synth.zipf_lookups(sizes, offs, batch, 1.1, 7, step, first_sample=rank * batch)
         grad = synth.normal_f32((len(ids), D), 1e-3, 7, step, stream=10 + rank)
-        c = eng.step(torch.from_numpy(ids).to(dev), torch.from_numpy(grad).to(dev), step)
+        batches.append((torch.from_numpy(ids).to(dev), torch.from_numpy(grad).to(dev)))
+        c = eng.step(batches[-1][0], batches[-1][1], step)
         rows_updated += int(c[0])
         gids = np.concatenate([synth.zipf_lookups(sizes, offs, batch, 1.1, 7, step, first_sample=r * batch) for r in range(world)])
         ggrad = np.concatenate([synth.normal_f32((batch * 26, D), 1e-3, 7, step, stream=10 + r) for r in range(world)])
         u, inv = O.unique_inverse(gids)
         O.adam_rows(st, u, O.segment_reduce(ggrad, inv, len(u)), *HYP, step)
+    counts = eng2.run_steps(batches, 1)                  # the software-pipelined form must give the same shard
+    torch.cuda.synchronize(dev)
     shard = eng.pool.cpu().numpy()
     ok = np.array_equal(shard.view(np.uint32), st[rank::world].view(np.uint32))
+    ok = ok and torch.equal(eng.pool.view(torch.int32), eng2.pool.view(torch.int32)) and sum(int(c[0]) for c in counts) == rows_updated
     flag = torch.tensor([int(ok), rows_updated], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
