@@ -170,6 +170,7 @@ def run_ours(a, world, rank, local_rank):
     bound = float(np.sqrt(1.0 / sizes.max()))
     eng = ShardedSparseAdam(total_rows, D, world, rank, dev, seed=SEED, bound=bound, hyper=HYP,
                             max_lookups_per_rank=n, group=dist.group.WORLD if world > 1 else None)
+    p2p = eng.enable_p2p(n) if world > 1 else False
     nsteps = a.warmup + a.steps
     ids_np = [step_ids(sizes, offs, a.batch, world, rank, s + 1) for s in range(nsteps)]
     ids_dev = [torch.from_numpy(x).to(dev) for x in ids_np]
@@ -282,6 +283,8 @@ def run_ours(a, world, rank, local_rank):
                    'd2h_bytes_per_step': 16 * world, 'steps': e2e_steps},
            'gpu_launches': int(launches_all), 'clocks': clocks,
            'rows_updated_per_step': rows / a.steps, 'lookups_per_step_per_gpu': n}
+    if world > 1:
+        out['config']['exchange'] = 'fused routing kernel: peer stores over NVLink' if p2p else 'NCCL all-to-all'
     return out
 
 

@@ -37,6 +37,9 @@ SIGNATURES = {
     'srm2_dir_status': (C.c_int, [_vp, _vp, _vp]),
     'srm2_unique_noalloc_max_rows': (C.c_int64, []),
     'srm2_unique_inverse_noalloc_i64': (C.c_int, [_vp, _i64, _i64, _vp, _i64, _vp, _vp, _vp]),
+    'srm2_route_plan': (C.c_int, [_vp, _i64, _i64, _vp, _vp, _sz, _vp]),
+    'srm2_route_publish': (C.c_int, [_vp, _vp, _i64, _i64, _vp]),
+    'srm2_route_dispatch': (C.c_int, [_vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _sz, _vp]),
 }
 
 _lib = None

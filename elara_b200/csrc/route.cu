@@ -95,3 +95,117 @@ extern "C" int srm2_route_by_owner(const int64_t* ids, const float* grad, int64_
   srm2_route_gather_kernel<<<grid, 256, 0, st>>>(ids, grad, perm, n, lpr, shift, (int)D, (int)world, out_lid, out_grad);
   return launch_status(launches + 2);
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// Routing fused with the exchange: instead of gathering into a local send buffer and handing that to a collective,
+// the gather kernel stores every routed lookup straight into its owner's receive buffer over NVLink (peer pointers;
+// plain stores, no multicast).  The only other traffic is the W x W matrix of lookup counts, which every rank
+// publishes into every rank's copy the same way.  Two stream-ordered barriers of the caller's choice (any collective on
+// the same stream) separate: counts published | rows dispatched | receive buffers read.
+//   plan     : stable grouping by owner (sort pass) -> permutation + per-owner counts           (this rank only)
+//   publish  : counts -> row `rank` of every rank's count matrix
+//   dispatch : row offset in owner d's buffer = sum of counts[s][d] over ranks s < rank, plus the lookup's index in
+//              this rank's group for d; rows and local ids are written there.  Receivers see their lookups in rank
+//              order, each rank's part in its original order: the global lookup order.
+namespace srm2 {
+
+constexpr int kMaxPeers = 16;
+struct PeerPtrs { void* p[kMaxPeers]; };
+
+__global__ void srm2_route_publish_kernel(const int64_t* __restrict__ counts, PeerPtrs cmat, int rank, int world) {
+  const int d = threadIdx.x;
+  if (d >= world) return;
+  const int64_t c = counts[d];
+  for (int r = 0; r < world; ++r) static_cast<int64_t*>(cmat.p[r])[rank * world + d] = c;
+}
+
+__global__ void __launch_bounds__(256)
+srm2_route_dispatch_kernel(const int64_t* __restrict__ ids, const float* __restrict__ grad, const uint32_t* __restrict__ perm,
+                           const uint32_t* __restrict__ owner_sorted, int64_t n, int lpr, int shift, int D, int world, int rank,
+                           const int64_t* __restrict__ cmat, PeerPtrs lid_peers, PeerPtrs grad_peers, int64_t cap,
+                           int64_t* __restrict__ n_recv, uint32_t* __restrict__ err) {
+  __shared__ int64_t s_start[kMaxPeers], s_base[kMaxPeers];
+  if (threadIdx.x < world) {
+    const int d = threadIdx.x;
+    int64_t start = 0, base = 0;
+    for (int e = 0; e < d; ++e) start += cmat[rank * world + e];      // first index of owner d in this rank's grouping
+    for (int s = 0; s < rank; ++s) base += cmat[s * world + d];       // rows that lower ranks send to owner d
+    s_start[d] = start; s_base[d] = base;
+    if (blockIdx.x == 0 && d == rank) {
+      int64_t tot = 0;
+      for (int s = 0; s < world; ++s) tot += cmat[s * world + rank];
+      *n_recv = tot;
+      if (tot > cap) atomicOr(err, 1u);
+    }
+  }
+  __syncthreads();
+  const int64_t items = n * lpr;
+  for (int64_t t = (int64_t)blockIdx.x * 256 + threadIdx.x; t < items; t += (int64_t)gridDim.x * 256) {
+    int64_t i; int j4;
+    if (shift >= 0) { i = t >> shift; j4 = (int)(t & (lpr - 1)); } else { i = t / lpr; j4 = (int)(t - i * lpr); }
+    const uint32_t d = owner_sorted[i];
+    if (d >= (uint32_t)world) continue;
+    const int64_t r = s_base[d] + (i - s_start[d]);
+    if (r >= cap) { atomicOr(err, 1u); continue; }
+    const uint32_t p = perm[i];
+    const float4 g = ld_stream4(grad + (int64_t)p * D + j4 * 4);
+    *reinterpret_cast<float4*>(static_cast<float*>(grad_peers.p[d]) + r * D + j4 * 4) = g;
+    if (j4 == 0) { const int64_t id = ids[p]; static_cast<int64_t*>(lid_peers.p[d])[r] = id < 0 ? -1 : id / world; }
+  }
+}
+
+}  // namespace srm2
+
+extern "C" int srm2_route_plan(const int64_t* ids, int64_t n, int64_t world, int64_t* out_counts, void* scratch,
+                               size_t scratch_bytes, srm2_stream_t stream) {
+  using namespace srm2;
+  if (n < 0 || world < 1 || out_counts == nullptr || (n > 0 && ids == nullptr)) return SRM2_ERR_ARG;
+  if (world > kMaxPeers || n >= ((int64_t)1 << 31)) return SRM2_ERR_UNSUPPORTED;
+  if (scratch == nullptr || !aligned16(scratch) || scratch_bytes < route_layout(n, world, nullptr, nullptr)) return SRM2_ERR_SCRATCH;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (n == 0) return note_cuda(cudaMemsetAsync(out_counts, 0, (size_t)world * 8, st));
+  SortBuffers sb;
+  route_layout(n, world, static_cast<char*>(scratch), &sb);
+  int launches = 0;
+  const uint32_t *skey = nullptr, *perm = nullptr, *dt = nullptr;
+  if (note_cuda(cudaMemsetAsync(sb.dtot, 0, sort_dtot_words(route_bits(world), 1) * 4, st))) return SRM2_ERR_CUDA;
+  const int rc = radix_sort_by_key(ids, n, (int)world, 0, route_bits(world), 1, sb, &skey, &perm, &dt, &launches, st);
+  if (rc != SRM2_OK) return rc;
+  srm2_route_counts_kernel<<<(unsigned)((world + 255) / 256), 256, 0, st>>>(sb.hist, dt, sb.tiles, (int)world, n, out_counts);
+  return launch_status(launches + 1);
+}
+
+extern "C" int srm2_route_publish(const int64_t* counts, void* const* peer_cmat, int64_t rank, int64_t world, srm2_stream_t stream) {
+  using namespace srm2;
+  if (counts == nullptr || peer_cmat == nullptr || world < 1 || world > kMaxPeers || rank < 0 || rank >= world) return SRM2_ERR_ARG;
+  PeerPtrs pp{};
+  for (int r = 0; r < world; ++r) { if (peer_cmat[r] == nullptr) return SRM2_ERR_ARG; pp.p[r] = peer_cmat[r]; }
+  srm2_route_publish_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(counts, pp, (int)rank, (int)world);
+  return launch_status(1);
+}
+
+extern "C" int srm2_route_dispatch(const int64_t* ids, const float* grad, int64_t n, int64_t D, int64_t world, int64_t rank,
+                                   const int64_t* cmat, void* const* peer_lid, void* const* peer_grad, int64_t cap,
+                                   int64_t* n_recv, uint32_t* err, void* scratch, size_t scratch_bytes, srm2_stream_t stream) {
+  using namespace srm2;
+  if (n < 0 || D <= 0 || world < 1 || world > kMaxPeers || rank < 0 || rank >= world || cap < 0) return SRM2_ERR_ARG;
+  if (cmat == nullptr || peer_lid == nullptr || peer_grad == nullptr || n_recv == nullptr || err == nullptr) return SRM2_ERR_ARG;
+  if (n > 0 && (ids == nullptr || grad == nullptr)) return SRM2_ERR_ARG;
+  if ((D & 3) != 0 || (n > 0 && !aligned16(grad))) return SRM2_ERR_UNSUPPORTED;
+  if (scratch == nullptr || !aligned16(scratch) || scratch_bytes < route_layout(n, world, nullptr, nullptr)) return SRM2_ERR_SCRATCH;
+  PeerPtrs pl{}, pg{};
+  for (int r = 0; r < world; ++r) {
+    if (peer_lid[r] == nullptr || peer_grad[r] == nullptr || !aligned16(peer_grad[r])) return SRM2_ERR_ARG;
+    pl.p[r] = peer_lid[r]; pg.p[r] = peer_grad[r];
+  }
+  SortBuffers sb;
+  route_layout(n, world, static_cast<char*>(scratch), &sb);     // keyA / valA hold the owners and the permutation of srm2_route_plan
+  const int lpr = (int)(D / 4);
+  const int shift = (lpr & (lpr - 1)) == 0 ? __builtin_ctz(lpr) : -1;
+  const int64_t items = n * lpr;
+  int grid = (int)((items + 255) / 256 < (int64_t)kSMs * 16 ? (items + 255) / 256 : (int64_t)kSMs * 16);
+  if (grid < 1) grid = 1;
+  srm2_route_dispatch_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(ids, grad, sb.valA, sb.keyA, n, lpr, shift, (int)D,
+                                                                                 (int)world, (int)rank, cmat, pl, pg, cap, n_recv, err);
+  return launch_status(1);
+}

@@ -120,6 +120,8 @@ class ShardedSparseAdam:
         import torch.distributed as dist
         if self.world == 1:
             return [self.step(i, g, first_step + k) for k, (i, g) in enumerate(batches)]
+        if getattr(self, '_peer', None) is not None:
+            return self._run_steps_p2p(batches, first_step)
         K = len(batches)
         P = self._pipe_buffers(max(i.numel() for i, _ in batches))
         comm, comp = P['comm'], torch.cuda.current_stream(self.dev)
@@ -179,4 +181,94 @@ class ShardedSparseAdam:
             out.append(count)
             if k + 1 < K:
                 payload(k + 1)
+        return out
+
+    # ------------------------------------------------------------------------------------------------------------
+    # Exchange fused into the routing kernel: routed lookups are stored straight into the owners' receive buffers through
+    # peer pointers (NVLink), see srm2_route_plan / publish / dispatch.  Nothing is read on the host: the receive buffers
+    # have a fixed capacity, unused rows carry id -1 and are ignored by the shard update.
+    def enable_p2p(self, max_lookups_per_rank, slack=1.5):
+        """Allocates the symmetric receive buffers and exchanges their addresses.  Collective over the group.
+        Returns True when peer access is available; otherwise the NCCL all-to-all path stays in use."""
+        import ctypes as C
+        import torch.distributed as dist
+        if self.world == 1 or self.world > 16:
+            return False
+        try:
+            import torch.distributed._symmetric_memory as symm
+            W, D = self.world, self.D
+            cap = int(max_lookups_per_rank * slack) + 4096
+            rlid = symm.empty(2 * cap, dtype=torch.int64, device=self.dev)
+            rgrad = symm.empty(2 * cap * D, dtype=torch.float32, device=self.dev)
+            cmat = symm.empty(2 * W * W, dtype=torch.int64, device=self.dev)
+            h = [symm.rendezvous(t, self.group) for t in (rlid, rgrad, cmat)]
+            arr = lambda ptrs: (C.c_void_p * W)(*[int(x) for x in ptrs])
+            peer = dict(cap=cap, rlid=rlid, rgrad=rgrad, cmat=cmat, handles=h,
+                        p_lid=[arr([h[0].buffer_ptrs[r] + b * cap * 8 for r in range(W)]) for b in range(2)],
+                        p_grad=[arr([h[1].buffer_ptrs[r] + b * cap * D * 4 for r in range(W)]) for b in range(2)],
+                        p_cmat=[arr([h[2].buffer_ptrs[r] + b * W * W * 8 for r in range(W)]) for b in range(2)],
+                        counts=torch.zeros(W, dtype=torch.int64, device=self.dev), n_recv=torch.zeros(2, dtype=torch.int64, device=self.dev),
+                        err=torch.zeros(1, dtype=torch.int32, device=self.dev), bar=torch.zeros(1, device=self.dev),
+                        comm=torch.cuda.Stream(self.dev))
+            rlid.fill_(-1); cmat.zero_()
+            torch.cuda.synchronize(self.dev)
+            dist.barrier(group=self.group)
+            self._peer = peer
+            return True
+        except Exception as e:                                   # no peer access on this system: keep the NCCL path
+            self._peer = None
+            self._peer_error = repr(e)
+            return False
+
+    def _run_steps_p2p(self, batches, first_step):
+        import torch.distributed as dist
+        P, W, D = self._peer, self.world, self.D
+        cap, comm, comp = P['cap'], P['comm'], torch.cuda.current_stream(self.dev)
+        L = _lib.lib()
+        K = len(batches)
+        ev_payload = [torch.cuda.Event() for _ in range(K)]
+        ev_done = [torch.cuda.Event() for _ in range(K)]
+        ev_start = torch.cuda.Event(); ev_start.record(comp)
+        comm.wait_event(ev_start)
+
+        def prepare(k):
+            ids, grads = batches[k]
+            b, n = k & 1, ids.numel()
+            rlid_b = P['rlid'][b * cap:(b + 1) * cap]
+            cmat_b = P['cmat'][b * W * W:(b + 1) * W * W]
+            with torch.cuda.stream(comm):
+                if k >= 2:
+                    comm.wait_event(ev_done[k - 2])               # this parity's receive buffer has been consumed
+                rlid_b.fill_(-1)
+                nb = L.srm2_route_scratch_bytes(n, W)
+                scr = ops._scratch(self.dev, nb, 'route')
+                s = comm.cuda_stream
+                _lib.check(L.srm2_route_plan(_lib.ptr(ids), n, W, P['counts'].data_ptr(), scr.data_ptr(), scr.numel(), s), 'route_plan')
+                _lib.check(L.srm2_route_publish(P['counts'].data_ptr(), P['p_cmat'][b], self.rank, W, s), 'route_publish')
+                dist.all_reduce(P['bar'], group=self.group)       # barrier: count matrices complete, receive buffers reset
+                _lib.check(L.srm2_route_dispatch(_lib.ptr(ids), _lib.ptr(grads), n, D, W, self.rank, cmat_b.data_ptr(), P['p_lid'][b],
+                                                 P['p_grad'][b], cap, P['n_recv'][b:b + 1].data_ptr(), P['err'].data_ptr(),
+                                                 scr.data_ptr(), scr.numel(), s), 'route_dispatch')
+                dist.all_reduce(P['bar'], group=self.group)       # barrier: every row has arrived
+                ev_payload[k].record(comm)
+
+        prepare(0)
+        out = []
+        for k in range(K):
+            b = k & 1
+            if k + 1 < K:
+                prepare(k + 1)
+            comp.wait_event(ev_payload[k])
+            rl = P['rlid'][b * cap:(b + 1) * cap]
+            rg = P['rgrad'][b * cap * D:(b + 1) * cap * D].view(cap, D)
+            u, inv, count = ops.unique_inverse(rl, max(self.n_local, 1), sync=False)
+            ops.reduce_adam(self.pool, u, rg, inv, *self.hyper, first_step + k, count=count, order=ops.ORDER_RUNS)
+            ev_done[k].record(comp)
+            out.append(count)
+        comp.wait_stream(comm)
+        if int(P['err'].item()) != 0:
+            raise RuntimeError('a receive buffer overflowed: raise the slack of enable_p2p')
+        nr = int(P['n_recv'][(K - 1) & 1].item())
+        self.last_local_lookups = nr
+        self.last_local_lookups_total += nr * K
         return out

@@ -224,6 +224,30 @@ int64_t srm2_unique_noalloc_max_rows(void);
 int srm2_unique_inverse_noalloc_i64(const int64_t* ids, int64_t n, int64_t n_rows, int64_t* uniq, int64_t uniq_cap,
                                     int64_t* inv, int64_t* out_count, srm2_stream_t stream);
 
+/* ---------------------------------------------------------------------------------------------------------
+ * Owner routing fused with the exchange (no counterpart in the reference): routed lookups are stored directly into the
+ * owners' receive buffers through peer pointers over NVLink (plain stores), so no send buffer and no collective moves
+ * the payload.  world <= 16.  Call order per step, all on one stream, with a stream-ordered barrier across the ranks
+ * (any collective on that stream) where marked:
+ *   srm2_route_plan      this rank's stable grouping by owner; out_counts [world] int64 (device)
+ *   srm2_route_publish   counts -> row `rank` of every rank's [world, world] int64 count matrix (peer_cmat: host array of
+ *                        `world` device pointers, entry r = rank r's matrix)
+ *   -- barrier --        every matrix is complete; every rank has reset the tail of its receive buffer
+ *   srm2_route_dispatch  local ids (row_id div world) -> peer_lid[d] [cap] int64 and gradient rows -> peer_grad[d] [cap, D]
+ *                        of each owner d, at the row offsets that give rank order; n_recv (device int64) = rows this rank
+ *                        will receive; *err |= 1 if a receive buffer would overflow (those rows are not written).
+ *                        `scratch` must be the buffer srm2_route_plan was given.
+ *   -- barrier --        every row has arrived
+ * Receive buffers hold cap rows; fill their id part with -1 before the first barrier so that unused rows are ignored
+ * by srm2_unique_inverse_i64 (inverse -1) and srm2_reduce_adam_f32.
+ */
+int srm2_route_plan(const int64_t* ids, int64_t n, int64_t world, int64_t* out_counts, void* scratch, size_t scratch_bytes,
+                    srm2_stream_t stream);
+int srm2_route_publish(const int64_t* counts, void* const* peer_cmat /* host */, int64_t rank, int64_t world, srm2_stream_t stream);
+int srm2_route_dispatch(const int64_t* ids, const float* grad, int64_t n, int64_t D, int64_t world, int64_t rank,
+                        const int64_t* cmat, void* const* peer_lid /* host */, void* const* peer_grad /* host */, int64_t cap,
+                        int64_t* n_recv, uint32_t* err, void* scratch, size_t scratch_bytes, srm2_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
