@@ -21,6 +21,13 @@ inline int launch_status(int k = 1) { add_launches(k); return note_cuda(cudaGetL
 void stage_begin(cudaStream_t st);
 void stage_end(cudaStream_t st);
 
+// Effective element count of a kernel: the host bound, lowered by an optional device-resident count.
+__device__ __forceinline__ int64_t eff_count(int64_t n_host, const int64_t* n_dev) {
+  if (n_dev == nullptr) return n_host;
+  const int64_t v = *n_dev;
+  return v < 0 ? 0 : (v < n_host ? v : n_host);
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // ---- exact fp32 arithmetic: every operation rounded on its own, never contracted ----------------

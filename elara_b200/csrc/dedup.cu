@@ -53,8 +53,9 @@ static size_t dedup_layout(int64_t n_rows, char* base, DedupScratch* s) {
 constexpr int kMarkPerThread = 8;
 constexpr int kMarkSlots = 2048;
 __global__ void __launch_bounds__(kDT)
-srm2_unique_mark_kernel(const int64_t* __restrict__ ids, int64_t n, int64_t n_rows, uint32_t* __restrict__ bitmap,
-                        int64_t* __restrict__ out_count) {
+srm2_unique_mark_kernel(const int64_t* __restrict__ ids, int64_t n_host, const int64_t* __restrict__ n_dev, int64_t n_rows,
+                        uint32_t* __restrict__ bitmap, int64_t* __restrict__ out_count) {
+  const int64_t n = eff_count(n_host, n_dev);
   __shared__ uint32_t tag[kMarkSlots];
   __shared__ uint32_t val[kMarkSlots];
   for (int i = threadIdx.x; i < kMarkSlots; i += kDT) { tag[i] = 0xffffffffu; val[i] = 0u; }
@@ -158,8 +159,9 @@ srm2_unique_emit_kernel(const uint32_t* __restrict__ bitmap, const uint32_t* __r
 }
 
 __global__ void __launch_bounds__(kDT)
-srm2_unique_inverse_kernel(const int64_t* __restrict__ ids, int64_t n, int64_t n_rows, const uint32_t* __restrict__ bitmap,
-                           const uint32_t* __restrict__ wprefix, int64_t* __restrict__ inv) {
+srm2_unique_inverse_kernel(const int64_t* __restrict__ ids, int64_t n_host, const int64_t* __restrict__ n_dev, int64_t n_rows,
+                           const uint32_t* __restrict__ bitmap, const uint32_t* __restrict__ wprefix, int64_t* __restrict__ inv) {
+  const int64_t n = eff_count(n_host, n_dev);
   for (int64_t p = (int64_t)blockIdx.x * kDT + threadIdx.x; p < n; p += (int64_t)gridDim.x * kDT) {
     const int64_t id = ids[p];
     if (id < 0 || id >= n_rows) { inv[p] = -1; continue; }
@@ -178,6 +180,12 @@ extern "C" size_t srm2_unique_scratch_bytes(int64_t n_rows) {
 extern "C" int srm2_unique_inverse_i64(const int64_t* ids, int64_t n, int64_t n_rows, int64_t* uniq, int64_t uniq_cap,
                                        int64_t* inv, int64_t* out_count, void* scratch, size_t scratch_bytes,
                                        srm2_stream_t stream) {
+  return srm2_unique_inverse_nd_i64(ids, n, nullptr, n_rows, uniq, uniq_cap, inv, out_count, scratch, scratch_bytes, stream);
+}
+
+extern "C" int srm2_unique_inverse_nd_i64(const int64_t* ids, int64_t n, const int64_t* n_dev, int64_t n_rows, int64_t* uniq,
+                                          int64_t uniq_cap, int64_t* inv, int64_t* out_count, void* scratch,
+                                          size_t scratch_bytes, srm2_stream_t stream) {
   using namespace srm2;
   if (n < 0 || n_rows <= 0 || uniq_cap < 0 || out_count == nullptr) return SRM2_ERR_ARG;
   if (n > 0 && (ids == nullptr || inv == nullptr)) return SRM2_ERR_ARG;
@@ -193,10 +201,10 @@ extern "C" int srm2_unique_inverse_i64(const int64_t* ids, int64_t n, int64_t n_
   if (note_cuda(cudaMemsetAsync(out_count, 0, 16, st))) return SRM2_ERR_CUDA;
   const int grid_n = (int)((n + kDT - 1) / kDT < kSMs * 8 ? (n + kDT - 1) / kDT : kSMs * 8);
   const int64_t mark_blocks = (n + kDT * kMarkPerThread - 1) / (kDT * kMarkPerThread);
-  if (n > 0) srm2_unique_mark_kernel<<<(unsigned)mark_blocks, kDT, 0, st>>>(ids, n, n_rows, s.bitmap, out_count);
+  if (n > 0) srm2_unique_mark_kernel<<<(unsigned)mark_blocks, kDT, 0, st>>>(ids, n, n_dev, n_rows, s.bitmap, out_count);
   srm2_unique_count_kernel<<<(unsigned)s.nblocks, kDT, 0, st>>>(s.bitmap, s.bsum, s.counter, s.nblocks, out_count);
   srm2_unique_emit_kernel<<<(unsigned)s.nblocks, kDT, 0, st>>>(s.bitmap, s.bsum, s.wprefix, uniq, uniq_cap);
-  if (n > 0) srm2_unique_inverse_kernel<<<grid_n, kDT, 0, st>>>(ids, n, n_rows, s.bitmap, s.wprefix, inv);
+  if (n > 0) srm2_unique_inverse_kernel<<<grid_n, kDT, 0, st>>>(ids, n, n_dev, n_rows, s.bitmap, s.wprefix, inv);
   return launch_status(n > 0 ? 4 : 2);
 }
 

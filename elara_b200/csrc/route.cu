@@ -50,7 +50,7 @@ static size_t route_layout(int64_t n, int64_t world, char* base, SortBuffers* sb
   size_t off = 0;
   auto take = [&](size_t bytes) { size_t o = off; off = align_up_r(off + bytes, 256); return o; };
   const size_t nn = (size_t)(n > 0 ? n : 1);
-  const size_t o_ka = take(nn * 4), o_va = take(nn * 4), o_h = take(sort_hist_words(tiles, bits) * 4), o_dt = take(sort_dtot_words(bits, 1) * 4);
+  const size_t o_ka = take(nn * 4), o_va = take(nn * 4), o_h = take(sort_hist_words(tiles, bits) * 4), o_dt = take(sort_dtot_words(tiles, bits, 1) * 4);
   if (sb) {
     auto u = [&](size_t o) { return reinterpret_cast<uint32_t*>(base + o); };
     sb->keyA = u(o_ka); sb->valA = u(o_va); sb->keyB = nullptr; sb->valB = nullptr; sb->hist = u(o_h); sb->dtot = u(o_dt); sb->tiles = tiles;
@@ -84,8 +84,8 @@ extern "C" int srm2_route_by_owner(const int64_t* ids, const float* grad, int64_
   const uint32_t *skey = nullptr, *perm = nullptr;
   int launches = 0;
   const uint32_t* hb = nullptr;
-  if (note_cuda(cudaMemsetAsync(sb.dtot, 0, sort_dtot_words(route_bits(world), 1) * 4, st))) return SRM2_ERR_CUDA;
-  const int rc = radix_sort_by_key(ids, n, (int)world, 0, route_bits(world), 1, sb, &skey, &perm, &hb, &launches, st);
+  if (note_cuda(cudaMemsetAsync(sb.dtot, 0, sort_dtot_words(sb.tiles, route_bits(world), 1) * 4, st))) return SRM2_ERR_CUDA;
+  const int rc = radix_sort_by_key(ids, n, nullptr, (int)world, 0, route_bits(world), 1, sb, &skey, &perm, &hb, &launches, st);
   if (rc != SRM2_OK) return rc;
   srm2_route_counts_kernel<<<(unsigned)((world + 255) / 256), 256, 0, st>>>(sb.hist, hb, sb.tiles, (int)world, n, out_counts);
   const int lpr = (int)(D / 4);
@@ -140,17 +140,38 @@ srm2_route_dispatch_kernel(const int64_t* __restrict__ ids, const float* __restr
   }
   __syncthreads();
   const int64_t items = n * lpr;
-  for (int64_t t = (int64_t)blockIdx.x * 256 + threadIdx.x; t < items; t += (int64_t)gridDim.x * 256) {
-    int64_t i; int j4;
-    if (shift >= 0) { i = t >> shift; j4 = (int)(t & (lpr - 1)); } else { i = t / lpr; j4 = (int)(t - i * lpr); }
-    const uint32_t d = owner_sorted[i];
-    if (d >= (uint32_t)world) continue;
-    const int64_t r = s_base[d] + (i - s_start[d]);
-    if (r >= cap) { atomicOr(err, 1u); continue; }
-    const uint32_t p = perm[i];
-    const float4 g = ld_stream4(grad + (int64_t)p * D + j4 * 4);
-    *reinterpret_cast<float4*>(static_cast<float*>(grad_peers.p[d]) + r * D + j4 * 4) = g;
-    if (j4 == 0) { const int64_t id = ids[p]; static_cast<int64_t*>(lid_peers.p[d])[r] = id < 0 ? -1 : id / world; }
+  const int64_t stride = (int64_t)gridDim.x * 256;
+  constexpr int U = 8;                                 // rows in flight per thread
+  for (int64_t t0 = (int64_t)blockIdx.x * 256 + threadIdx.x; t0 < items; t0 += stride * U) {
+    float4 g[U]; int64_t r[U]; uint32_t dd[U]; int j4s[U]; int64_t lid[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t t = t0 + u * stride;
+      r[u] = -1;
+      if (t < items) {
+        int64_t i; int j4;
+        if (shift >= 0) { i = t >> shift; j4 = (int)(t & (lpr - 1)); } else { i = t / lpr; j4 = (int)(t - i * lpr); }
+        const uint32_t d = owner_sorted[i];
+        if (d < (uint32_t)world) {
+          const int64_t rr = s_base[d] + (i - s_start[d]);
+          if (rr >= cap) { atomicOr(err, 1u); }
+          else {
+            const uint32_t p = perm[i];
+            g[u] = ld_stream4(grad + (int64_t)p * D + j4 * 4);
+            lid[u] = 0;
+            if (j4 == 0) { const int64_t id = ids[p]; lid[u] = id < 0 ? -1 : id / world; }
+            r[u] = rr; dd[u] = d; j4s[u] = j4;
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (r[u] >= 0) {
+        *reinterpret_cast<float4*>(static_cast<float*>(grad_peers.p[dd[u]]) + r[u] * D + j4s[u] * 4) = g[u];
+        if (j4s[u] == 0) static_cast<int64_t*>(lid_peers.p[dd[u]])[r[u]] = lid[u];
+      }
+    }
   }
 }
 
@@ -168,8 +189,8 @@ extern "C" int srm2_route_plan(const int64_t* ids, int64_t n, int64_t world, int
   route_layout(n, world, static_cast<char*>(scratch), &sb);
   int launches = 0;
   const uint32_t *skey = nullptr, *perm = nullptr, *dt = nullptr;
-  if (note_cuda(cudaMemsetAsync(sb.dtot, 0, sort_dtot_words(route_bits(world), 1) * 4, st))) return SRM2_ERR_CUDA;
-  const int rc = radix_sort_by_key(ids, n, (int)world, 0, route_bits(world), 1, sb, &skey, &perm, &dt, &launches, st);
+  if (note_cuda(cudaMemsetAsync(sb.dtot, 0, sort_dtot_words(sb.tiles, route_bits(world), 1) * 4, st))) return SRM2_ERR_CUDA;
+  const int rc = radix_sort_by_key(ids, n, nullptr, (int)world, 0, route_bits(world), 1, sb, &skey, &perm, &dt, &launches, st);
   if (rc != SRM2_OK) return rc;
   srm2_route_counts_kernel<<<(unsigned)((world + 255) / 256), 256, 0, st>>>(sb.hist, dt, sb.tiles, (int)world, n, out_counts);
   return launch_status(launches + 1);
@@ -203,7 +224,9 @@ extern "C" int srm2_route_dispatch(const int64_t* ids, const float* grad, int64_
   const int lpr = (int)(D / 4);
   const int shift = (lpr & (lpr - 1)) == 0 ? __builtin_ctz(lpr) : -1;
   const int64_t items = n * lpr;
-  int grid = (int)((items + 255) / 256 < (int64_t)kSMs * 16 ? (items + 255) / 256 : (int64_t)kSMs * 16);
+  // a small grid: the kernel is bound by the NVLink stores, and it runs in the shadow of the previous step's shard
+  // update, which should keep most of every SM
+  int grid = (int)((items + 255) / 256 < (int64_t)kSMs * 2 ? (items + 255) / 256 : (int64_t)kSMs * 2);
   if (grid < 1) grid = 1;
   srm2_route_dispatch_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(ids, grad, sb.valA, sb.keyA, n, lpr, shift, (int)D,
                                                                                  (int)world, (int)rank, cmat, pl, pg, cap, n_recv, err);

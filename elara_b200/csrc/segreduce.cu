@@ -72,8 +72,9 @@ __device__ __forceinline__ void finish_row(const ReduceArgs& a, uint32_t j, int 
 // seg_start[j] / seg_end[j] = sorted index range of unique row j.  Both arrays are zeroed first, so a row that no
 // lookup names has an empty range.  Lookups with an invalid index carry key == cap and belong to no row.
 __global__ void __launch_bounds__(256)
-srm2_segment_bounds_kernel(const uint32_t* __restrict__ skey, int64_t n, uint32_t* __restrict__ seg_start,
-                           uint32_t* __restrict__ seg_end, int64_t cap) {
+srm2_segment_bounds_kernel(const uint32_t* __restrict__ skey, int64_t n_host, const int64_t* __restrict__ n_dev,
+                           uint32_t* __restrict__ seg_start, uint32_t* __restrict__ seg_end, int64_t cap) {
+  const int64_t n = eff_count(n_host, n_dev);
   const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
   if (i >= n) return;
   const uint32_t k = skey[i];
@@ -140,8 +141,8 @@ srm2_segment_plan_kernel(ReduceArgs a, uint32_t* __restrict__ run_off, uint32_t*
 //   mrow_info[mi] = {unique row, number of runs, first partial slot, finished-run counter = 0}
 constexpr uint32_t kMultiBit = 0x80000000u;
 __global__ void __launch_bounds__(256)
-srm2_segment_descr_kernel(const uint32_t* __restrict__ skey, const uint32_t* __restrict__ spos, int64_t n,
-                          const uint32_t* __restrict__ seg_start,
+srm2_segment_descr_kernel(const uint32_t* __restrict__ skey, const uint32_t* __restrict__ spos, int64_t n_host,
+                          const int64_t* __restrict__ n_dev, const uint32_t* __restrict__ seg_start,
                           const uint32_t* __restrict__ seg_end, const uint32_t* __restrict__ run_off,
                           const uint32_t* __restrict__ mrun_off, const uint32_t* __restrict__ mrow_off,
                           const uint32_t* __restrict__ bpre_r, const uint32_t* __restrict__ bpre_m,
@@ -150,7 +151,7 @@ srm2_segment_descr_kernel(const uint32_t* __restrict__ skey, const uint32_t* __r
                           uint32_t* __restrict__ mrows, uint4* __restrict__ mrow_info, int64_t nu_host,
                           const int64_t* __restrict__ nu_dev, int64_t cap) {
   const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
-  if (i >= n) return;
+  if (i >= eff_count(n_host, n_dev)) return;
   const uint32_t j = skey[i];
   if ((int64_t)j >= load_nu(nu_host, nu_dev, cap)) return;
   const uint32_t s = seg_start[j], e = seg_end[j];
@@ -449,7 +450,7 @@ static size_t seg_layout(int64_t n, int64_t cap, int64_t D, char* base, SegScrat
   auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return o; };
   const size_t nn = (size_t)(n > 0 ? n : 1), cc = (size_t)(cap + 1), nb = (size_t)(nblocks + 1);
   const size_t o_ka = take(nn * 4), o_va = take(nn * 4), o_kb = take(nn * 4), o_vb = take(nn * 4);
-  const size_t o_h = take(sort_hist_words(tiles, bits) * 4), o_dt = take(sort_dtot_words(bits, passes) * 4);
+  const size_t o_h = take(sort_hist_words(tiles, bits) * 4), o_dt = take(sort_dtot_words(tiles, bits, passes) * 4);
   const size_t o_ss = take(cc * 4 * 2);                          // seg_start and seg_end, contiguous (one memset)
   const size_t o_ro = take(cc * 4), o_mo = take(cc * 4), o_fo = take(cc * 4);
   const size_t o_br = take(nb * 4), o_bm = take(nb * 4), o_bf = take(nb * 4);
@@ -468,7 +469,7 @@ static size_t seg_layout(int64_t n, int64_t cap, int64_t D, char* base, SegScrat
   return off;
 }
 
-static int segment_pipeline(bool fused, int order, const float* grad, const int64_t* inv, int64_t n, int64_t D, int64_t nu_host,
+static int segment_pipeline(bool fused, int order, const float* grad, const int64_t* inv, int64_t n, const int64_t* n_dev, int64_t D, int64_t nu_host,
                             const int64_t* nu_dev, int64_t cap, float* out, float* pool, const int64_t* slots,
                             const float* sc, void* scratch, size_t scratch_bytes, cudaStream_t st) {
   if (n < 0 || D <= 0 || cap < 0 || (nu_host < 0 && nu_dev == nullptr) || order < 0 || order > 2) return SRM2_ERR_ARG;
@@ -494,10 +495,10 @@ static int segment_pipeline(bool fused, int order, const float* grad, const int6
   if (n > 0) {
     SortBuffers sb{s.keyA, s.valA, s.keyB, s.valB, s.hist, s.dtot, s.tiles};
     const uint32_t* hb = nullptr;
-    if (note_cuda(cudaMemsetAsync(s.dtot, 0, sort_dtot_words(s.bits, s.passes) * 4, st))) return SRM2_ERR_CUDA;
-    const int rc = radix_sort_by_key(inv, n, /*mod=*/0, cap, s.bits, s.passes, sb, &skey, &spos, &hb, &launches, st);
+    if (note_cuda(cudaMemsetAsync(s.dtot, 0, sort_dtot_words(s.tiles, s.bits, s.passes) * 4, st))) return SRM2_ERR_CUDA;
+    const int rc = radix_sort_by_key(inv, n, n_dev, /*mod=*/0, cap, s.bits, s.passes, sb, &skey, &spos, &hb, &launches, st);
     if (rc != SRM2_OK) return rc;
-    srm2_segment_bounds_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(skey, n, s.seg_start, s.seg_end, cap);
+    srm2_segment_bounds_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(skey, n, n_dev, s.seg_start, s.seg_end, cap);
     ++launches;
   }
   ReduceArgs a{};
@@ -524,7 +525,7 @@ static int segment_pipeline(bool fused, int order, const float* grad, const int6
     srm2_segment_plan_kernel<false><<<s.nblocks, kPlanThreads, 0, st>>>(a, s.run_off, s.mrun_off, s.mrow_off, s.bsum_r, s.bsum_m, s.bsum_f,
                                                                        s.counters, s.nblocks, 0);
   if (n > 0)
-    srm2_segment_descr_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(skey, spos, n, s.seg_start, s.seg_end, s.run_off, s.mrun_off, s.mrow_off,
+    srm2_segment_descr_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(skey, spos, n, n_dev, s.seg_start, s.seg_end, s.run_off, s.mrun_off, s.mrow_off,
                                                                           s.bsum_r, s.bsum_m, s.bsum_f, s.counters, fused ? slots : nullptr, s.run_desc, s.run_pos, s.mrows, s.mrow_info,
                                                                           nu_host, nu_dev, cap);
   // 5. run sums, 6. multi-run rows
@@ -565,13 +566,21 @@ extern "C" size_t srm2_segment_scratch_bytes(int64_t n, int64_t max_unique, int6
 extern "C" int srm2_segment_reduce_f32(const float* grad, const int64_t* inv, int64_t n, int64_t D, int64_t n_unique,
                                        const int64_t* n_unique_dev, int64_t max_unique, int order, float* out, void* scratch,
                                        size_t scratch_bytes, srm2_stream_t stream) {
-  return srm2::segment_pipeline(false, order, grad, inv, n, D, n_unique, n_unique_dev, max_unique, out, nullptr, nullptr, nullptr,
+  return srm2::segment_pipeline(false, order, grad, inv, n, nullptr, D, n_unique, n_unique_dev, max_unique, out, nullptr, nullptr, nullptr,
                                 scratch, scratch_bytes, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int srm2_reduce_adam_f32(float* pool, const int64_t* slots, const float* grad, const int64_t* inv, int64_t n,
                                     int64_t D, int64_t n_unique, const int64_t* n_unique_dev, int64_t max_unique,
                                     int order, const float sc[8], void* scratch, size_t scratch_bytes, srm2_stream_t stream) {
-  return srm2::segment_pipeline(true, order, grad, inv, n, D, n_unique, n_unique_dev, max_unique, nullptr, pool, slots, sc, scratch,
+  return srm2::segment_pipeline(true, order, grad, inv, n, nullptr, D, n_unique, n_unique_dev, max_unique, nullptr, pool, slots, sc, scratch,
                                 scratch_bytes, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int srm2_reduce_adam_nd_f32(float* pool, const int64_t* slots, const float* grad, const int64_t* inv, int64_t n,
+                                       const int64_t* n_dev, int64_t D, int64_t n_unique, const int64_t* n_unique_dev,
+                                       int64_t max_unique, int order, const float sc[8], void* scratch, size_t scratch_bytes,
+                                       srm2_stream_t stream) {
+  return srm2::segment_pipeline(true, order, grad, inv, n, n_dev, D, n_unique, n_unique_dev, max_unique, nullptr, pool, slots, sc,
+                                scratch, scratch_bytes, static_cast<cudaStream_t>(stream));
 }

@@ -14,7 +14,8 @@ constexpr int kSortWarps = kSortThreads / 32;
 constexpr int kSortRounds = 8;                               // elements per thread
 constexpr int kSortTile = kSortThreads * kSortRounds;        // 2048 elements per CTA
 constexpr int kMaxRadixBits = 11;
-constexpr int64_t kFusedOffsetsLimit = 1 << 16;              // tiles * digits up to which the scatter kernel sums the histogram itself
+constexpr int kSuperTile = 16;                               // tiles per group whose digit sums are kept as well
+constexpr int64_t kFusedOffsetsLimit = (int64_t)1 << 23;     // tiles * digits up to which the scatter kernel derives its offsets itself
 
 // Key of a 64-bit input value: mod == 0: the value itself, with anything outside [0, cap) mapped to `cap` (behind every
 // real key); mod > 0: value mod `mod` (owner of a row id), negative values mapped to 0.
@@ -25,14 +26,17 @@ __device__ __forceinline__ uint32_t make_key(int64_t k, int64_t cap, int mod) {
 
 // Histogram of one digit per tile.  Pass 0 reads the keys from the int64 source array (key32 == nullptr), later passes
 // from the u32 ping-pong buffer.  Two layouts:
-//   dtot != nullptr: tile-major hist[tile * bins + d] (coalesced), and the digit totals are accumulated into dtot[d]
-//                    (integer atomics: the result does not depend on their order); the scatter kernel sums the tiles
-//                    before its own and scans dtot itself — no scan launch;
+//   dtot != nullptr: tile-major hist[tile * bins + d] (coalesced); the digit totals are accumulated into dtot[d] and the
+//                    sums of every group of kSuperTile tiles into dtot[(1 + group) * bins + d] (integer atomics: the
+//                    result does not depend on their order); the scatter kernel adds the groups and the tiles before
+//                    its own and scans the totals itself — no scan launch;
 //   dtot == nullptr: digit-major hist[d * tiles + tile], to be scanned by a separate kernel (large problems).
 static __global__ void __launch_bounds__(kSortThreads)
-srm2_sort_hist_kernel(const int64_t* __restrict__ key64, const uint32_t* __restrict__ key32, int64_t n, int shift, int bits,
+srm2_sort_hist_kernel(const int64_t* __restrict__ key64, const uint32_t* __restrict__ key32, int64_t n_host,
+                      const int64_t* __restrict__ n_dev, int shift, int bits,
                       uint32_t* __restrict__ hist, uint32_t* __restrict__ dtot, int tiles, int64_t cap, int mod) {
   extern __shared__ uint32_t sh[];
+  const int64_t n = eff_count(n_host, n_dev);
   const int bins = 1 << bits;
   for (int b = threadIdx.x; b < bins; b += kSortThreads) sh[b] = 0;
   __syncthreads();
@@ -48,7 +52,10 @@ srm2_sort_hist_kernel(const int64_t* __restrict__ key64, const uint32_t* __restr
   __syncthreads();
   for (int b = threadIdx.x; b < bins; b += kSortThreads) {
     const uint32_t c = sh[b];
-    if (dtot) { hist[(int64_t)blockIdx.x * bins + b] = c; if (c) atomicAdd(dtot + b, c); }
+    if (dtot) {
+      hist[(int64_t)blockIdx.x * bins + b] = c;
+      if (c) { atomicAdd(dtot + b, c); atomicAdd(dtot + (int64_t)(1 + blockIdx.x / kSuperTile) * bins + b, c); }
+    }
     else hist[(int64_t)b * tiles + blockIdx.x] = c;
   }
 }
@@ -61,10 +68,11 @@ srm2_sort_hist_kernel(const int64_t* __restrict__ key64, const uint32_t* __restr
 // dtot == nullptr: hist holds the exclusive scan of the whole digit-major histogram.
 static __global__ void __launch_bounds__(kSortThreads)
 srm2_sort_scatter_kernel(const int64_t* __restrict__ key64, const uint32_t* __restrict__ key32,
-                         const uint32_t* __restrict__ val32, int64_t n, int shift, int bits,
+                         const uint32_t* __restrict__ val32, int64_t n_host, const int64_t* __restrict__ n_dev, int shift, int bits,
                          const uint32_t* __restrict__ hist, const uint32_t* __restrict__ dtot, int tiles, uint32_t* __restrict__ out_key,
                          uint32_t* __restrict__ out_val, int64_t cap, int mod) {
-  extern __shared__ uint32_t sh[];                 // [kSortWarps][bins] counts, [bins] tile offsets
+  extern __shared__ uint32_t sh[];
+  const int64_t n = eff_count(n_host, n_dev);                 // [kSortWarps][bins] counts, [bins] tile offsets
   __shared__ uint32_t ws[33];
   const int bins = 1 << bits;
   uint32_t* goff = sh + kSortWarps * bins;         // global offset of (digit, this tile)
@@ -95,7 +103,9 @@ srm2_sort_scatter_kernel(const int64_t* __restrict__ key64, const uint32_t* __re
       if (b >= bins) break;
       const uint32_t* col = hist + b;
       uint32_t before = 0;
-      int t = 0;
+      const int my_group = (int)blockIdx.x / kSuperTile;
+      for (int gq = 0; gq < my_group; ++gq) before += __ldg(dtot + (int64_t)(1 + gq) * bins + b);
+      int t = my_group * kSuperTile;
       for (; t + 8 <= (int)blockIdx.x; t += 8) {
         uint32_t v[8];
 #pragma unroll
@@ -154,13 +164,15 @@ struct SortBuffers { uint32_t *keyA, *valA, *keyB, *valB, *hist, *dtot; int tile
 
 inline int sort_tiles(int64_t n) { return (int)((n + kSortTile - 1) / kSortTile); }
 inline size_t sort_hist_words(int tiles, int bits) { return (size_t)tiles * ((size_t)1 << bits) + 8; }
-inline size_t sort_dtot_words(int bits, int passes) { return ((size_t)passes << bits) + 8; }
+// per pass: digit totals + one row of digit sums per group of kSuperTile tiles
+inline size_t sort_dtot_words_pass(int tiles, int bits) { return ((size_t)(1 + (tiles + kSuperTile - 1) / kSuperTile) << bits); }
+inline size_t sort_dtot_words(int tiles, int bits, int passes) { return sort_dtot_words_pass(tiles, bits) * passes + 8; }
 
-// Sorts positions 0..n-1 by key(src[p]) (stable).  bits*passes must cover the key range.  On return *skey / *spos point
+// Sorts positions 0..n-1 by key(src[p]) (stable); n is lowered to *n_dev when n_dev != nullptr.  bits*passes must cover the key range.  On return *skey / *spos point
 // at the buffers holding the sorted keys and positions.  *dtot_out is the digit-total array of the LAST pass (its
 // exclusive scan gives the first output index of each digit) or nullptr when the separate-scan path ran, in which case
 // sb.hist holds the scanned digit-major histogram.  sb.dtot must be zero on entry.  *launches counts the kernels.
-static int radix_sort_by_key(const int64_t* src, int64_t n, int mod, int64_t cap, int bits, int passes, const SortBuffers& sb,
+static int radix_sort_by_key(const int64_t* src, int64_t n, const int64_t* n_dev, int mod, int64_t cap, int bits, int passes, const SortBuffers& sb,
                              const uint32_t** skey, const uint32_t** spos, const uint32_t** dtot_out, int* launches, cudaStream_t st) {
   const size_t sm_hist = ((size_t)1 << bits) * 4, sm_scat = sm_hist * (kSortWarps + 1);
   if (sm_scat > 48 * 1024 &&
@@ -172,13 +184,13 @@ static int radix_sort_by_key(const int64_t* src, int64_t n, int mod, int64_t cap
   uint32_t* dt = nullptr;
   for (int p = 0; p < passes; ++p) {
     const int shiftp = p * bits;
-    dt = separate_scan ? nullptr : sb.dtot + ((size_t)p << bits);
-    srm2_sort_hist_kernel<<<sb.tiles, kSortThreads, sm_hist, st>>>(p == 0 ? src : nullptr, ki, n, shiftp, bits, sb.hist, dt, sb.tiles, cap, mod);
+    dt = separate_scan ? nullptr : sb.dtot + sort_dtot_words_pass(sb.tiles, bits) * p;
+    srm2_sort_hist_kernel<<<sb.tiles, kSortThreads, sm_hist, st>>>(p == 0 ? src : nullptr, ki, n, n_dev, shiftp, bits, sb.hist, dt, sb.tiles, cap, mod);
     if (separate_scan) {
       srm2_scan_exclusive_u32_kernel<<<1, kScanThreads, 0, st>>>(sb.hist, sb.hist, entries, nullptr, entries, 0, nullptr);
       *launches += 1;
     }
-    srm2_sort_scatter_kernel<<<sb.tiles, kSortThreads, sm_scat, st>>>(p == 0 ? src : nullptr, ki, vi, n, shiftp, bits, sb.hist, dt, sb.tiles,
+    srm2_sort_scatter_kernel<<<sb.tiles, kSortThreads, sm_scat, st>>>(p == 0 ? src : nullptr, ki, vi, n, n_dev, shiftp, bits, sb.hist, dt, sb.tiles,
                                                                      ko, vo, cap, mod);
     *launches += 2;
     ki = ko; vi = vo;

@@ -95,13 +95,14 @@ def _scratch(device, nbytes, tag):
     return buf
 
 
-def unique_inverse(ids, n_rows, sync=True):
+def unique_inverse(ids, n_rows, sync=True, n_dev=None):
     """Sorted distinct ids and the inverse index, as `torch.unique(ids, return_inverse=True)` (srm2/train.py:352).
 
     ids: cuda int64 [n] in [0, n_rows) (global row ids; n_rows = total rows of all tables).
     sync=True  -> (u [n_unique], inv [n]) exactly like torch.unique (one host sync for the size, as torch does)
     sync=False -> (u_buf [min(n, n_rows)], inv [n], count) with count a cuda int64 [2] tensor
-                  (count[0] = n_unique, count[1] = 1 if an id was out of range); nothing waits on the GPU."""
+                  (count[0] = n_unique, count[1] = 1 if an id was out of range); nothing waits on the GPU.
+    n_dev: optional cuda int64 [1]: only the first min(n, n_dev) lookups exist (the rest of ids / inv is ignored)."""
     _require_cuda(ids, 'ids')
     if ids.dtype != torch.int64:
         raise TypeError('ids must be int64')
@@ -116,8 +117,8 @@ def unique_inverse(ids, n_rows, sync=True):
     nb = L.srm2_unique_scratch_bytes(int(n_rows))
     scr = _scratch(dev, nb, 'unique')
     with torch.cuda.device(dev):
-        st = L.srm2_unique_inverse_i64(_lib.ptr(ids), n, int(n_rows), _lib.ptr(u), cap, _lib.ptr(inv), count.data_ptr(),
-                                       scr.data_ptr(), scr.numel(), _lib.stream_of(dev))
+        st = L.srm2_unique_inverse_nd_i64(_lib.ptr(ids), n, _lib.ptr(n_dev), int(n_rows), _lib.ptr(u), cap, _lib.ptr(inv),
+                                          count.data_ptr(), scr.data_ptr(), scr.numel(), _lib.stream_of(dev))
     _lib.check(st, 'unique_inverse')
     if not sync:
         return u, inv, count
@@ -161,7 +162,7 @@ def segment_reduce(grad, inv, n_unique, order=ORDER_AUTO):
     return out
 
 
-def reduce_adam(pool, slots, grad, inv, lr, b1, b2, eps, step, n_unique=None, count=None, order=ORDER_AUTO):
+def reduce_adam(pool, slots, grad, inv, lr, b1, b2, eps, step, n_unique=None, count=None, order=ORDER_AUTO, n_dev=None):
     """segment_reduce followed by gpu_adam(pool, slots, gW, ...) in one pass over the gradients: same bits, gW never
     materialised.  slots int64 [>= n_unique]: pool row of each unique row.  Give either n_unique (host int) or count
     (the cuda tensor returned by unique_inverse(sync=False)); with count nothing waits on the GPU."""
@@ -185,7 +186,7 @@ def reduce_adam(pool, slots, grad, inv, lr, b1, b2, eps, step, n_unique=None, co
     nb = L.srm2_segment_scratch_bytes(n, cap, D)
     scr = _scratch(dev, nb, 'segment')
     with torch.cuda.device(dev):
-        st = L.srm2_reduce_adam_f32(pool.data_ptr(), slots.data_ptr(), _lib.ptr(grad), _lib.ptr(inv), n, D,
+        st = L.srm2_reduce_adam_nd_f32(pool.data_ptr(), slots.data_ptr(), _lib.ptr(grad), _lib.ptr(inv), n, _lib.ptr(n_dev), D,
                                     -1 if n_unique is None else cap, 0 if count is None or n_unique is not None else count.data_ptr(),
                                     cap, order, sc, scr.data_ptr(), scr.numel(), _lib.stream_of(dev))
     _lib.check(st, 'reduce_adam')

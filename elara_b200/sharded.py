@@ -209,7 +209,7 @@ class ShardedSparseAdam:
                         p_cmat=[arr([h[2].buffer_ptrs[r] + b * W * W * 8 for r in range(W)]) for b in range(2)],
                         counts=torch.zeros(W, dtype=torch.int64, device=self.dev), n_recv=torch.zeros(2, dtype=torch.int64, device=self.dev),
                         err=torch.zeros(1, dtype=torch.int32, device=self.dev), bar=torch.zeros(1, device=self.dev),
-                        comm=torch.cuda.Stream(self.dev))
+                        comm=torch.cuda.Stream(self.dev, priority=-1))   # routing must not queue behind the shard update
             rlid.fill_(-1); cmat.zero_()
             torch.cuda.synchronize(self.dev)
             dist.barrier(group=self.group)
@@ -261,8 +261,9 @@ class ShardedSparseAdam:
             comp.wait_event(ev_payload[k])
             rl = P['rlid'][b * cap:(b + 1) * cap]
             rg = P['rgrad'][b * cap * D:(b + 1) * cap * D].view(cap, D)
-            u, inv, count = ops.unique_inverse(rl, max(self.n_local, 1), sync=False)
-            ops.reduce_adam(self.pool, u, rg, inv, *self.hyper, first_step + k, count=count, order=ops.ORDER_RUNS)
+            nd = P['n_recv'][b:b + 1]                             # rows that arrived, known to the device only
+            u, inv, count = ops.unique_inverse(rl, max(self.n_local, 1), sync=False, n_dev=nd)
+            ops.reduce_adam(self.pool, u, rg, inv, *self.hyper, first_step + k, count=count, order=ops.ORDER_RUNS, n_dev=nd)
             ev_done[k].record(comp)
             out.append(count)
         comp.wait_stream(comm)

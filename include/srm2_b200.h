@@ -248,6 +248,19 @@ int srm2_route_dispatch(const int64_t* ids, const float* grad, int64_t n, int64_
                         const int64_t* cmat, void* const* peer_lid /* host */, void* const* peer_grad /* host */, int64_t cap,
                         int64_t* n_recv, uint32_t* err, void* scratch, size_t scratch_bytes, srm2_stream_t stream);
 
+/* ---------------------------------------------------------------------------------------------------------
+ * Variants whose lookup count lives on the device (no counterpart in the reference): n is an upper bound that sizes
+ * grids and scratch, the kernels process min(n, *n_dev) lookups.  They let a receive buffer of fixed capacity be
+ * consumed without reading its fill level on the host (row-sharded exchange).  n_dev == NULL behaves like the plain
+ * entry points.  For SRM2_ORDER_AUTO the order is chosen from the bound n.
+ */
+int srm2_unique_inverse_nd_i64(const int64_t* ids, int64_t n, const int64_t* n_dev, int64_t n_rows, int64_t* uniq,
+                               int64_t uniq_cap, int64_t* inv, int64_t* out_count, void* scratch, size_t scratch_bytes,
+                               srm2_stream_t stream);
+int srm2_reduce_adam_nd_f32(float* pool, const int64_t* slots, const float* grad, const int64_t* inv, int64_t n,
+                            const int64_t* n_dev, int64_t D, int64_t n_unique, const int64_t* n_unique_dev, int64_t max_unique,
+                            int order, const float sc[8] /* host */, void* scratch, size_t scratch_bytes, srm2_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
