@@ -15,8 +15,8 @@
 namespace srm2 {
 
 constexpr int kDT = 256;                    // threads per block
-constexpr int kWordsPerThread = 16;
-constexpr int kWordsPerBlock = kDT * kWordsPerThread;   // 4096 words = 131072 rows per block
+constexpr int kWordsPerThread = 4;
+constexpr int kWordsPerBlock = kDT * kWordsPerThread;   // 1024 words = 32768 rows per block
 
 struct DedupScratch {
   uint32_t* bitmap;     // [words]
@@ -82,7 +82,7 @@ srm2_unique_mark_kernel(const int64_t* __restrict__ ids, int64_t n_host, const i
     if (tag[i] != 0xffffffffu) atomicOr(bitmap + tag[i], val[i]);
 }
 
-// Per block of 4096 words: number of set bits.  The last block to finish turns bsum into its exclusive scan and
+// Per block of 1024 words: number of set bits.  The last block to finish turns bsum into its exclusive scan and
 // writes the total (= number of unique ids).
 __global__ void __launch_bounds__(kDT)
 srm2_unique_count_kernel(const uint32_t* __restrict__ bitmap, uint32_t* __restrict__ bsum, uint32_t* __restrict__ counter,
@@ -103,23 +103,24 @@ srm2_unique_count_kernel(const uint32_t* __restrict__ bitmap, uint32_t* __restri
   __syncthreads();
   if (!last) return;
   __threadfence();
-  // exclusive scan of bsum[0..nblocks) by this block, in rounds of kDT entries
+  // exclusive scan of bsum[0..nblocks) by this block, in rounds of 4 * kDT entries (thread t: entries 4t .. 4t+3)
   uint32_t carry = 0;
-  for (int64_t base = 0; base < nblocks; base += kDT) {
-    const int64_t i = base + threadIdx.x;
-    const uint32_t v = i < nblocks ? reinterpret_cast<volatile uint32_t*>(bsum)[i] : 0u;
+  for (int64_t base = 0; base < nblocks; base += 4 * kDT) {
+    const int64_t i0 = base + 4 * (int64_t)threadIdx.x;
+    uint32_t v[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) v[e] = i0 + e < nblocks ? reinterpret_cast<volatile uint32_t*>(bsum)[i0 + e] : 0u;
     uint32_t tot;
-    const uint32_t ex = block_exclusive_scan<kDT>(v, ws, &tot);
-    if (i < nblocks) bsum[i] = carry + ex;
+    uint32_t run = carry + block_exclusive_scan<kDT>(v[0] + v[1] + v[2] + v[3], ws, &tot);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { if (i0 + e < nblocks) bsum[i0 + e] = run; run += v[e]; }
     carry += tot;
   }
   if (threadIdx.x == 0) { out_count[0] = (int64_t)carry; *counter = 0u; }
 }
 
 // Per word: exclusive prefix of distinct ids; every set bit writes its id at its rank.
-// The prefixes are computed with each thread owning 16 consecutive words; the ids are then written with the words
-// dealt round-robin to the threads, because set bits cluster (the frequent ids of a table are its smallest) and a run
-// of dense words must not end up in a single thread.
+// The prefixes are computed with each thread owning 4 consecutive words (one 16-byte load).
 __global__ void __launch_bounds__(kDT)
 srm2_unique_emit_kernel(const uint32_t* __restrict__ bitmap, const uint32_t* __restrict__ bsum, uint32_t* __restrict__ wprefix,
                         int64_t* __restrict__ uniq, int64_t uniq_cap) {
@@ -148,6 +149,8 @@ srm2_unique_emit_kernel(const uint32_t* __restrict__ bitmap, const uint32_t* __r
   for (int k = 0; k < kWordsPerThread / 4; ++k) dst[k] = make_uint4(pf[4 * k], pf[4 * k + 1], pf[4 * k + 2], pf[4 * k + 3]);
   if (total == 0) return;                            // uniform: nothing to emit in this block of words
   __syncthreads();
+  // ids: the words are dealt round-robin to the threads (word i -> thread i mod 256), so a run of dense words (the
+  // frequent ids of a table are its smallest) is spread over many threads instead of piling up in one
   for (int i = threadIdx.x; i < kWordsPerBlock; i += kDT) {
     uint32_t bits = s_w[i]; uint32_t r = s_p[i];
     while (bits) {
@@ -225,7 +228,7 @@ extern "C" int srm2_unique_inverse_nd_i64(const int64_t* ids, int64_t n, const i
 namespace srm2 {
 
 constexpr int64_t kNoAllocMaxRows = 4194304;                                   // 2^22 rows
-constexpr size_t kNoAllocScratchBytes = 2 * (size_t)(kNoAllocMaxRows / 32) * 4 + 1024;   // bitmap + word prefixes + counters
+constexpr size_t kNoAllocScratchBytes = 2 * (size_t)(kNoAllocMaxRows / 32) * 4 + 4096;   // bitmap + word prefixes + counters
 
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
 

@@ -38,6 +38,36 @@ __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* w
   return res;
 }
 
+// The same for a 64-bit value (three counters packed into one word scan together).  `ws` is 33 64-bit words.
+template <int NT>
+__device__ __forceinline__ uint64_t block_exclusive_scan64(uint64_t v, uint64_t* ws, uint64_t* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint64_t inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint64_t t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += t;
+  }
+  if (lane == 31) ws[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    uint64_t s = lane < NT / 32 ? ws[lane] : 0ull;
+    uint64_t si = s;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint64_t t = __shfl_up_sync(0xffffffffu, si, o);
+      if (lane >= o) si += t;
+    }
+    ws[lane] = si - s;
+    if (lane == 31) ws[32] = si;
+  }
+  __syncthreads();
+  const uint64_t res = ws[warp] + inc - v;
+  if (total) *total = ws[32];
+  __syncthreads();
+  return res;
+}
+
 // out[i] = sum_{k<i} in[i]  for i < count (count read from *count_dev when count_dev != nullptr, else count_host);
 // count is clamped to count_cap (the allocated length); optionally out[count] = total and *total_out = total.  One CTA of kScanThreads threads; in == out allowed.
 static __global__ void __launch_bounds__(kScanThreads)

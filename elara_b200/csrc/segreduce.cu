@@ -92,7 +92,7 @@ __global__ void __launch_bounds__(kPlanThreads)
 srm2_segment_plan_kernel(ReduceArgs a, uint32_t* __restrict__ run_off, uint32_t* __restrict__ mrun_off,
                          uint32_t* __restrict__ mrow_off, uint32_t* __restrict__ bsum_r, uint32_t* __restrict__ bsum_m,
                          uint32_t* __restrict__ bsum_f, SegCounters* __restrict__ counters, int nblocks, int small) {
-  __shared__ uint32_t ws[33];
+  __shared__ uint64_t ws[33];
   __shared__ bool last;
   const int64_t nu = load_nu(a.nu_host, a.nu_dev, a.cap);
   const int64_t j = (int64_t)blockIdx.x * kPlanThreads + threadIdx.x;
@@ -104,33 +104,35 @@ srm2_segment_plan_kernel(ReduceArgs a, uint32_t* __restrict__ run_off, uint32_t*
       for (int j4 = 0; j4 < a.lpr; ++j4) finish_row<FUSED>(a, (uint32_t)j, j4, make_float4(0.f, 0.f, 0.f, 0.f));
   }
   if (small) return;                               // the windowed order needs no runs
-  uint32_t tr, tm, tf;
-  const uint32_t er = block_exclusive_scan<kPlanThreads>(r, ws, &tr);
-  const uint32_t em = block_exclusive_scan<kPlanThreads>(m, ws, &tm);
-  const uint32_t ef = block_exclusive_scan<kPlanThreads>(f, ws, &tf);
-  if (j < a.cap) { run_off[j] = er; mrun_off[j] = em; mrow_off[j] = ef; }
+  // the three counters scan as one packed word: runs | runs of multi-run rows | multi-run rows (21 bits each; the host
+  // side rejects inputs whose totals would not fit)
+  uint64_t tot;
+  const uint64_t ex = block_exclusive_scan64<kPlanThreads>(((uint64_t)r << 42) | ((uint64_t)m << 21) | f, ws, &tot);
+  constexpr uint64_t kM = (1ull << 21) - 1;
+  if (j < a.cap) { run_off[j] = (uint32_t)(ex >> 42); mrun_off[j] = (uint32_t)((ex >> 21) & kM); mrow_off[j] = (uint32_t)(ex & kM); }
   if (threadIdx.x == 0) {
-    bsum_r[blockIdx.x] = tr; bsum_m[blockIdx.x] = tm; bsum_f[blockIdx.x] = tf;
+    bsum_r[blockIdx.x] = (uint32_t)(tot >> 42); bsum_m[blockIdx.x] = (uint32_t)((tot >> 21) & kM); bsum_f[blockIdx.x] = (uint32_t)(tot & kM);
     __threadfence();
     last = atomicAdd(&counters->done, 1u) == (uint32_t)(nblocks - 1);
   }
   __syncthreads();
   if (!last) return;
   __threadfence();
-  uint32_t cr = 0, cm = 0, cf = 0;
+  // per-CTA totals -> exclusive prefixes; these totals can exceed 21 bits, so they scan as three 64-bit sums
+  uint64_t cr = 0, cm = 0, cf = 0;
   for (int base = 0; base < nblocks; base += kPlanThreads) {
     const int i = base + threadIdx.x;
-    const uint32_t vr = i < nblocks ? reinterpret_cast<volatile uint32_t*>(bsum_r)[i] : 0u;
-    const uint32_t vm = i < nblocks ? reinterpret_cast<volatile uint32_t*>(bsum_m)[i] : 0u;
-    const uint32_t vf = i < nblocks ? reinterpret_cast<volatile uint32_t*>(bsum_f)[i] : 0u;
-    uint32_t t0, t1, t2;
-    const uint32_t xr = block_exclusive_scan<kPlanThreads>(vr, ws, &t0);
-    const uint32_t xm = block_exclusive_scan<kPlanThreads>(vm, ws, &t1);
-    const uint32_t xf = block_exclusive_scan<kPlanThreads>(vf, ws, &t2);
-    if (i < nblocks) { bsum_r[i] = cr + xr; bsum_m[i] = cm + xm; bsum_f[i] = cf + xf; }
+    const uint64_t vr = i < nblocks ? reinterpret_cast<volatile uint32_t*>(bsum_r)[i] : 0u;
+    const uint64_t vm = i < nblocks ? reinterpret_cast<volatile uint32_t*>(bsum_m)[i] : 0u;
+    const uint64_t vf = i < nblocks ? reinterpret_cast<volatile uint32_t*>(bsum_f)[i] : 0u;
+    uint64_t t0, t1, t2;
+    const uint64_t xr = block_exclusive_scan64<kPlanThreads>(vr, ws, &t0);
+    const uint64_t xm = block_exclusive_scan64<kPlanThreads>(vm, ws, &t1);
+    const uint64_t xf = block_exclusive_scan64<kPlanThreads>(vf, ws, &t2);
+    if (i < nblocks) { bsum_r[i] = (uint32_t)(cr + xr); bsum_m[i] = (uint32_t)(cm + xm); bsum_f[i] = (uint32_t)(cf + xf); }
     cr += t0; cm += t1; cf += t2;
   }
-  if (threadIdx.x == 0) { counters->n_runs = cr; counters->n_mruns = cm; counters->n_mrows = cf; counters->done = 0u; }
+  if (threadIdx.x == 0) { counters->n_runs = (uint32_t)cr; counters->n_mruns = (uint32_t)cm; counters->n_mrows = (uint32_t)cf; counters->done = 0u; }
 }
 
 // Run descriptors and the multi-run rows; one thread per sorted lookup, the first lookup of a run writes.
@@ -212,6 +214,7 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 #define SRM2_RUN_PREFETCH 1
 #endif
 constexpr bool kRunPrefetch = SRM2_RUN_PREFETCH != 0;
+constexpr int kInplaceMaxRuns = 1 << 30;  // rows with more runs would be left to the multi-run kernel (measured: not worth a launch)
 constexpr int kRunThreads = 256;
 constexpr int kRunStageVecs = kRun + 3;                                  // gradient rows + w, m, v
 constexpr int kRunSmemBytes = kRunStageVecs * kRunThreads * 16;         // 53,248 B per CTA
@@ -281,17 +284,17 @@ srm2_segment_runsum_kernel(ReduceArgs a) {
     float* pp = a.partial + (int64_t)d.z * a.D + j4 * 4;
     if (!a.inplace) { *reinterpret_cast<float4*>(pp) = acc; continue; }
     __stcg(reinterpret_cast<float4*>(pp), acc);
-    __threadfence();
-    __syncwarp(gmask);
+    __syncwarp(gmask);                                 // the group's stores are ordered before the leader's fence
     uint4 info = make_uint4(0u, 0u, 0u, 0u);
     if (lane == gleader) {
       info = __ldcg(reinterpret_cast<const uint4*>(a.mrow_info + d.w));
+      __threadfence();                                 // release: the run sum is visible before the count
       const uint32_t old = atomicAdd(&a.mrow_info[d.w].w, 1u);
       info.w = old;
     }
     info.x = __shfl_sync(gmask, info.x, gleader); info.y = __shfl_sync(gmask, info.y, gleader);
     info.z = __shfl_sync(gmask, info.z, gleader); info.w = __shfl_sync(gmask, info.w, gleader);
-    if (info.w != info.y - 1u) continue;               // not the last run of the row to finish
+    if (info.w != info.y - 1u || info.y > (uint32_t)kInplaceMaxRuns) continue;   // not the last run to finish, or a long row
     __threadfence();
     // the group that completes a row adds its run sums in order, staging kRun of them at a time the same way
     const float* p = a.partial + (int64_t)info.z * a.D + j4 * 4;
@@ -361,6 +364,7 @@ srm2_segment_final_kernel(ReduceArgs a, int short_rows, int chunk_rows) {
       nr = (a.seg_end[j] - a.seg_start[j] + kRun - 1) / kRun;
       pb = a.bpre_m[j / kPlanThreads] + a.mrun_off[j];
     }
+    if (a.inplace && nr <= (uint32_t)kInplaceMaxRuns) nr = 0;      // finished inside the run-sum kernel
     if (lane == 0) { s_j[warp] = j; s_nr[warp] = nr; s_pb[warp] = pb; }
     if (nr > 0 && nr <= (uint32_t)short_rows) {
       const float* p = a.partial + (int64_t)pb * a.D;
@@ -477,7 +481,8 @@ static int segment_pipeline(bool fused, int order, const float* grad, const int6
   if (cap == 0) return SRM2_OK;
   if (n > 0 && (grad == nullptr || inv == nullptr)) return SRM2_ERR_ARG;
   if (fused ? (pool == nullptr || slots == nullptr || sc == nullptr) : out == nullptr) return SRM2_ERR_ARG;
-  if ((D & 3) != 0 || D > 128 * kMaxColsPerLane || n >= ((int64_t)1 << 31) || cap >= ((int64_t)1 << 31)) return SRM2_ERR_UNSUPPORTED;
+  // n < 2^21: the plan kernel scans three run counters packed into 21-bit fields of one word
+  if ((D & 3) != 0 || D > 128 * kMaxColsPerLane || n >= ((int64_t)1 << 21) || cap >= ((int64_t)1 << 31)) return SRM2_ERR_UNSUPPORTED;
   if ((n > 0 && !aligned16(grad)) || (fused ? !aligned16(pool) : !aligned16(out))) return SRM2_ERR_UNSUPPORTED;
   if (scratch == nullptr || !aligned16(scratch) || scratch_bytes < seg_layout(n, cap, D, nullptr, nullptr)) return SRM2_ERR_SCRATCH;
   SegScratch s;

@@ -103,7 +103,7 @@ int srm2_unique_inverse_i64(const int64_t* ids, int64_t n, int64_t n_rows, int64
  * Segment-reduce of per-lookup gradients.  Replaces the driver's
  * `torch.ops.aten.embedding_dense_backward(grad, inv, n_unique, -1, False)` (srm2/train.py:429), in that
  * operator's CUDA summation order (torch 2.11.0): see elara_b200/csrc/segreduce.cu.
- *   grad [n,D] fp32 (D % 4 == 0, 16-byte aligned);  inv [n] int64 in [0, n_unique)
+ *   grad [n,D] fp32 (D % 4 == 0, D <= 512, 16-byte aligned; n < 2,097,152);  inv [n] int64 in [0, n_unique)
  *   out  [n_unique, D] fp32; rows without lookups are zero
  *   n_unique      host value, used when n_unique_dev == NULL
  *   n_unique_dev  optional device int64: the count is read on the device (no host sync after a dedup);
