@@ -23,6 +23,7 @@ struct DedupScratch {
   uint32_t* wprefix;    // [words]    number of distinct ids below word w
   uint32_t* bsum;       // [nblocks]  distinct ids per block of words, then its exclusive scan
   uint32_t* counter;    // [1]        blocks finished (returns to 0 at the end of every call)
+  uint32_t* flag;       // [1]        an id outside [0, n_rows) was seen
   int64_t words, nblocks;
 };
 
@@ -33,13 +34,12 @@ static size_t dedup_layout(int64_t n_rows, char* base, DedupScratch* s) {
   const int64_t nblocks = (words + kWordsPerBlock - 1) / kWordsPerBlock;
   size_t off = 0;
   auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return o; };
-  const size_t o_bm = take((size_t)(nblocks * kWordsPerBlock) * 4);   // padded to whole blocks
+  const size_t o_bm = take((size_t)(nblocks * kWordsPerBlock) * 4 + 256);   // padded to whole blocks; counter and flag behind it
   const size_t o_wp = take((size_t)(nblocks * kWordsPerBlock) * 4);
   const size_t o_bs = take((size_t)(nblocks + 1) * 4);
-  const size_t o_ct = take(4);
   if (s) {
     s->bitmap = reinterpret_cast<uint32_t*>(base + o_bm); s->wprefix = reinterpret_cast<uint32_t*>(base + o_wp);
-    s->bsum = reinterpret_cast<uint32_t*>(base + o_bs); s->counter = reinterpret_cast<uint32_t*>(base + o_ct);
+    s->bsum = reinterpret_cast<uint32_t*>(base + o_bs); s->counter = s->bitmap + nblocks * kWordsPerBlock; s->flag = s->counter + 1;
     s->words = words; s->nblocks = nblocks;
   }
   return off;
@@ -49,12 +49,12 @@ static size_t dedup_layout(int64_t n_rows, char* base, DedupScratch* s) {
 // table share a bitmap word, so naive atomics serialise on a few words in L2.  Each CTA therefore first ORs its bits
 // into a direct-mapped shared-memory cache keyed by word index (collisions fall through to a global atomic) and then
 // flushes every cached word with a single global atomicOr.
-// out_count[1] = 1 if an id outside [0, n_rows) was seen (it is ignored; its inverse is -1).
+// *flag = 1 if an id outside [0, n_rows) was seen (it is ignored; its inverse is -1); the count kernel reports it.
 constexpr int kMarkPerThread = 8;
 constexpr int kMarkSlots = 2048;
 __global__ void __launch_bounds__(kDT)
 srm2_unique_mark_kernel(const int64_t* __restrict__ ids, int64_t n_host, const int64_t* __restrict__ n_dev, int64_t n_rows,
-                        uint32_t* __restrict__ bitmap, int64_t* __restrict__ out_count) {
+                        uint32_t* __restrict__ bitmap, uint32_t* __restrict__ flag) {
   const int64_t n = eff_count(n_host, n_dev);
   __shared__ uint32_t tag[kMarkSlots];
   __shared__ uint32_t val[kMarkSlots];
@@ -70,7 +70,7 @@ srm2_unique_mark_kernel(const int64_t* __restrict__ ids, int64_t n_host, const i
 #pragma unroll
   for (int k = 0; k < kMarkPerThread; ++k) {
     if (id[k] == -2) continue;
-    if (id[k] < 0 || id[k] >= n_rows) { out_count[1] = 1; continue; }
+    if (id[k] < 0 || id[k] >= n_rows) { *flag = 1u; continue; }
     const uint32_t w = (uint32_t)(id[k] >> 5), bit = 1u << (id[k] & 31);
     const uint32_t slot = (w * 2654435761u) >> (32 - 11);
     const uint32_t prev = atomicCAS(&tag[slot], 0xffffffffu, w);
@@ -86,7 +86,7 @@ srm2_unique_mark_kernel(const int64_t* __restrict__ ids, int64_t n_host, const i
 // writes the total (= number of unique ids).
 __global__ void __launch_bounds__(kDT)
 srm2_unique_count_kernel(const uint32_t* __restrict__ bitmap, uint32_t* __restrict__ bsum, uint32_t* __restrict__ counter,
-                         int64_t nblocks, int64_t* __restrict__ out_count) {
+                         const uint32_t* __restrict__ flag, int64_t nblocks, int64_t* __restrict__ out_count) {
   __shared__ uint32_t ws[33];
   __shared__ bool last;
   const uint4* src = reinterpret_cast<const uint4*>(bitmap + (int64_t)blockIdx.x * kWordsPerBlock) + threadIdx.x * (kWordsPerThread / 4);
@@ -116,7 +116,7 @@ srm2_unique_count_kernel(const uint32_t* __restrict__ bitmap, uint32_t* __restri
     for (int e = 0; e < 4; ++e) { if (i0 + e < nblocks) bsum[i0 + e] = run; run += v[e]; }
     carry += tot;
   }
-  if (threadIdx.x == 0) { out_count[0] = (int64_t)carry; *counter = 0u; }
+  if (threadIdx.x == 0) { out_count[0] = (int64_t)carry; out_count[1] = (int64_t)*flag; *counter = 0u; }
 }
 
 // Per word: exclusive prefix of distinct ids; every set bit writes its id at its rank.
@@ -199,13 +199,11 @@ extern "C" int srm2_unique_inverse_nd_i64(const int64_t* ids, int64_t n, const i
   DedupScratch s;
   dedup_layout(n_rows, static_cast<char*>(scratch), &s);
   // bitmap (padded to whole blocks), block sums and the finished-blocks counter start at zero
-  if (note_cuda(cudaMemsetAsync(s.bitmap, 0, (size_t)(s.nblocks * kWordsPerBlock) * 4, st))) return SRM2_ERR_CUDA;
-  if (note_cuda(cudaMemsetAsync(s.counter, 0, 4, st))) return SRM2_ERR_CUDA;
-  if (note_cuda(cudaMemsetAsync(out_count, 0, 16, st))) return SRM2_ERR_CUDA;
+  if (note_cuda(cudaMemsetAsync(s.bitmap, 0, (size_t)(s.nblocks * kWordsPerBlock) * 4 + 8, st))) return SRM2_ERR_CUDA;   // + counter, flag
   const int grid_n = (int)((n + kDT - 1) / kDT < kSMs * 8 ? (n + kDT - 1) / kDT : kSMs * 8);
   const int64_t mark_blocks = (n + kDT * kMarkPerThread - 1) / (kDT * kMarkPerThread);
-  if (n > 0) srm2_unique_mark_kernel<<<(unsigned)mark_blocks, kDT, 0, st>>>(ids, n, n_dev, n_rows, s.bitmap, out_count);
-  srm2_unique_count_kernel<<<(unsigned)s.nblocks, kDT, 0, st>>>(s.bitmap, s.bsum, s.counter, s.nblocks, out_count);
+  if (n > 0) srm2_unique_mark_kernel<<<(unsigned)mark_blocks, kDT, 0, st>>>(ids, n, n_dev, n_rows, s.bitmap, s.flag);
+  srm2_unique_count_kernel<<<(unsigned)s.nblocks, kDT, 0, st>>>(s.bitmap, s.bsum, s.counter, s.flag, s.nblocks, out_count);
   srm2_unique_emit_kernel<<<(unsigned)s.nblocks, kDT, 0, st>>>(s.bitmap, s.bsum, s.wprefix, uniq, uniq_cap);
   if (n > 0) srm2_unique_inverse_kernel<<<grid_n, kDT, 0, st>>>(ids, n, n_dev, n_rows, s.bitmap, s.wprefix, inv);
   return launch_status(n > 0 ? 4 : 2);

@@ -437,7 +437,7 @@ srm2_segment_windowed_kernel(ReduceArgs a) {
 struct SegScratch {
   uint32_t *keyA, *valA, *keyB, *valB, *hist, *dtot, *seg_start, *seg_end, *run_off, *mrun_off, *mrow_off, *bsum_r, *bsum_m, *bsum_f, *mrows;
   uint4* run_desc; uint32_t* run_pos; uint4* mrow_info; SegCounters* counters; float* partial;
-  int tiles, bits, passes, nblocks;
+  int tiles, bits, passes, nblocks; char* zero; size_t zero_bytes;
 };
 
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -454,11 +454,14 @@ static size_t seg_layout(int64_t n, int64_t cap, int64_t D, char* base, SegScrat
   auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return o; };
   const size_t nn = (size_t)(n > 0 ? n : 1), cc = (size_t)(cap + 1), nb = (size_t)(nblocks + 1);
   const size_t o_ka = take(nn * 4), o_va = take(nn * 4), o_kb = take(nn * 4), o_vb = take(nn * 4);
-  const size_t o_h = take(sort_hist_words(tiles, bits) * 4), o_dt = take(sort_dtot_words(tiles, bits, passes) * 4);
-  const size_t o_ss = take(cc * 4 * 2);                          // seg_start and seg_end, contiguous (one memset)
+  const size_t o_h = take(sort_hist_words(tiles, bits) * 4);
+  // one zero-filled region per call: counters | digit totals | seg_start | seg_end
+  const size_t zero_bytes = 256 + align_up(sort_dtot_words(tiles, bits, passes) * 4, 256) + cc * 4 * 2;
+  const size_t o_z = take(zero_bytes);
+  const size_t o_ct = o_z, o_dt = o_z + 256, o_ss = o_dt + align_up(sort_dtot_words(tiles, bits, passes) * 4, 256);
   const size_t o_ro = take(cc * 4), o_mo = take(cc * 4), o_fo = take(cc * 4);
   const size_t o_br = take(nb * 4), o_bm = take(nb * 4), o_bf = take(nb * 4);
-  const size_t o_mr = take(cc * 4), o_rd = take(nn * 16), o_rp = take((nn * kRun + 16) * 4), o_mi = take((nn / (kRun + 1) + 2) * 16), o_ct = take(sizeof(SegCounters));
+  const size_t o_mr = take(cc * 4), o_rd = take(nn * 16), o_rp = take((nn * kRun + 16) * 4), o_mi = take((nn / (kRun + 1) + 2) * 16);
   const size_t max_partial = (size_t)(n / kRun + n / (kRun + 1) + 2);
   const size_t o_p = take(max_partial * (size_t)D * 4);
   if (s) {
@@ -468,7 +471,7 @@ static size_t seg_layout(int64_t n, int64_t cap, int64_t D, char* base, SegScrat
     s->run_off = u(o_ro); s->mrun_off = u(o_mo); s->mrow_off = u(o_fo); s->bsum_r = u(o_br); s->bsum_m = u(o_bm); s->bsum_f = u(o_bf);
     s->mrows = u(o_mr); s->run_desc = reinterpret_cast<uint4*>(base + o_rd); s->run_pos = u(o_rp); s->mrow_info = reinterpret_cast<uint4*>(base + o_mi); s->counters = reinterpret_cast<SegCounters*>(base + o_ct);
     s->partial = reinterpret_cast<float*>(base + o_p);
-    s->tiles = tiles; s->bits = bits; s->passes = passes; s->nblocks = nblocks;
+    s->tiles = tiles; s->bits = bits; s->passes = passes; s->nblocks = nblocks; s->zero = base + o_z; s->zero_bytes = zero_bytes;
   }
   return off;
 }
@@ -493,14 +496,12 @@ static int segment_pipeline(bool fused, int order, const float* grad, const int6
   int launches = 0;
 
   // empty ranges for rows that no lookup names; counters (incl. the finished-CTA count) start at zero
-  if (note_cuda(cudaMemsetAsync(s.seg_start, 0, (size_t)(cap + 1) * 8, st))) return SRM2_ERR_CUDA;
-  if (note_cuda(cudaMemsetAsync(s.counters, 0, sizeof(SegCounters), st))) return SRM2_ERR_CUDA;
+  if (note_cuda(cudaMemsetAsync(s.zero, 0, s.zero_bytes, st))) return SRM2_ERR_CUDA;
   // 1. sort (key = inv, value = position), 2. boundaries
   const uint32_t *skey = nullptr, *spos = nullptr;
   if (n > 0) {
     SortBuffers sb{s.keyA, s.valA, s.keyB, s.valB, s.hist, s.dtot, s.tiles};
     const uint32_t* hb = nullptr;
-    if (note_cuda(cudaMemsetAsync(s.dtot, 0, sort_dtot_words(s.tiles, s.bits, s.passes) * 4, st))) return SRM2_ERR_CUDA;
     const int rc = radix_sort_by_key(inv, n, n_dev, /*mod=*/0, cap, s.bits, s.passes, sb, &skey, &spos, &hb, &launches, st);
     if (rc != SRM2_OK) return rc;
     srm2_segment_bounds_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(skey, n, n_dev, s.seg_start, s.seg_end, cap);
