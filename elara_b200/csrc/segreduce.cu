@@ -136,7 +136,7 @@ srm2_segment_plan_kernel(ReduceArgs a, uint32_t* __restrict__ run_off, uint32_t*
 }
 
 // Run descriptors and the multi-run rows; one thread per sorted lookup, the first lookup of a run writes.
-//   run_desc[c] = {first sorted index, length | kMultiBit, z, w}
+//   run_desc[c] = {x, length | kMultiBit, z, w};  x = the lookup position itself when the run has one lookup
 //     run of a multi-run row: c = its partial slot (these runs come first), z = partial slot, w = index of the row in
 //                             mrow_info;  single-run row: c = n_mruns + rank among single-run rows, (z, w) = 64-bit
 //                             target: the pool row (fused) or the unique row index.
@@ -167,11 +167,11 @@ srm2_segment_descr_kernel(const uint32_t* __restrict__ skey, const uint32_t* __r
   const uint32_t len = min((uint32_t)kRun, e - (uint32_t)i);
   if (multi) {
     const uint32_t mi = bpre_f[blk] + mrow_off[j];
-    run_desc[c] = make_uint4((uint32_t)i, len | kMultiBit, c, mi);
+    run_desc[c] = make_uint4(len == 1 ? spos[i] : (uint32_t)i, len | kMultiBit, c, mi);
     if (off == 0) { mrows[mi] = j; mrow_info[mi] = make_uint4(j, (e - s + kRun - 1) / kRun, mbase, 0u); }
   } else {
     const uint64_t target = slots ? (uint64_t)slots[j] : (uint64_t)j;
-    run_desc[c] = make_uint4((uint32_t)i, len, (uint32_t)target, (uint32_t)(target >> 32));
+    run_desc[c] = make_uint4(len == 1 ? spos[i] : (uint32_t)i, len, (uint32_t)target, (uint32_t)(target >> 32));
   }
 }
 
@@ -308,6 +308,103 @@ srm2_segment_runsum_kernel(ReduceArgs a) {
 #pragma unroll
       for (int e = 0; e < kRun; ++e)
         if (e < cnt) tot = add4(tot, mine[e * kRunThreads]);
+    }
+    finish_row<FUSED>(a, info.x, j4, tot);
+  }
+}
+
+// The same kernel for rows of 16 or 32 lanes (D = 64 or 128), where a run's lane group is an aligned half or whole warp
+// with at least kRun lanes.  Differences that cut the instruction count by about a third:
+//  - the positions of a run are held one per lane (lane q of the group holds position q) and broadcast with a shuffle
+//    when row q is copied: one coalesced 40-byte load per run instead of ten loads per lane;
+//  - a run of a single lookup carries its position in the descriptor and needs no position load at all;
+//  - the copy and add loops run `len` times (len is uniform over the group) instead of ten predicated times;
+//  - descriptors are fetched two items ahead and positions one item ahead, so neither is waited for.
+template <bool FUSED>
+__global__ void __launch_bounds__(kRunThreads)
+srm2_segment_runsum_wide_kernel(ReduceArgs a) {
+  extern __shared__ float4 stage[];                 // [kRunStageVecs][kRunThreads]
+  float4* mine = stage + threadIdx.x;
+  const int64_t items = (int64_t)a.counters->n_runs * a.lpr;
+  const int lane = threadIdx.x & 31;
+  const unsigned gmask = a.lpr >= 32 ? 0xffffffffu : (((1u << a.lpr) - 1u) << (lane & ~(a.lpr - 1)));
+  const int gleader = a.lpr >= 32 ? 0 : (lane & ~(a.lpr - 1));
+  const int gl = lane - gleader;                    // lane within the group
+  const int64_t stride = (int64_t)gridDim.x * kRunThreads;
+  int64_t t = (int64_t)blockIdx.x * kRunThreads + threadIdx.x;
+  const int j4 = (int)(t & (a.lpr - 1));
+  auto run_of = [&](int64_t tt) { return tt >> a.shift; };
+  auto load_pos = [&](const uint4& d, int64_t c) -> uint32_t {   // position gl of run c, for runs of more than one lookup
+    const int len = (int)(d.y & 0xffu);
+    return (len > 1 && gl < len) ? __ldg(a.run_pos + c * kRun + gl) : 0u;
+  };
+  uint4 d0 = make_uint4(0u, 0u, 0u, 0u), d1 = d0, d2 = d0;
+  uint32_t p0 = 0, p1 = 0;
+  if (t < items) d0 = __ldg(a.run_desc + run_of(t));
+  if (t + stride < items) d1 = __ldg(a.run_desc + run_of(t + stride));
+  if (t < items) p0 = load_pos(d0, run_of(t));
+  for (; t < items; t += stride) {
+    const uint4 d = d0;
+    const int len = (int)(d.y & 0xffu);
+    const bool multi = (d.y & kMultiBit) != 0;
+    // ---- copies of this item ----
+    float* b = nullptr;
+    if (!multi) {
+      const int64_t target = (int64_t)((uint64_t)d.z | ((uint64_t)d.w << 32));
+      if (FUSED) {
+        b = a.pool + target * (3 * (int64_t)a.D) + j4 * 4;
+        cp_async16(mine + kRun * kRunThreads, b); cp_async16(mine + (kRun + 1) * kRunThreads, b + a.D);
+        cp_async16(mine + (kRun + 2) * kRunThreads, b + 2 * a.D);
+      } else {
+        b = a.out + target * (int64_t)a.D + j4 * 4;
+      }
+    }
+    if (len == 1) {
+      cp_async16(mine, a.grad + (int64_t)d.x * a.D + j4 * 4);
+    } else {
+      for (int q = 0; q < len; ++q) {
+        const uint32_t pos = __shfl_sync(gmask, p0, gleader + q);
+        cp_async16(mine + q * kRunThreads, a.grad + (int64_t)pos * a.D + j4 * 4);
+      }
+    }
+    cp_async_commit();
+    // ---- next items: descriptor two ahead, positions one ahead ----
+    if (t + 2 * stride < items) d2 = __ldg(a.run_desc + run_of(t + 2 * stride));
+    if (t + stride < items) p1 = load_pos(d1, run_of(t + stride));
+    cp_async_wait<0>();
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int q = 0; q < len; ++q) acc = add4(acc, mine[q * kRunThreads]);
+    d0 = d1; d1 = d2; p0 = p1;
+    if (!multi) {
+      const float4 g = add4(make_float4(0.f, 0.f, 0.f, 0.f), acc);
+      if (FUSED) {
+        float4 w = mine[kRun * kRunThreads], m = mine[(kRun + 1) * kRunThreads], v = mine[(kRun + 2) * kRunThreads];
+        adam_vec4(w, m, v, g, a.sc);
+        *reinterpret_cast<float4*>(b) = w; *reinterpret_cast<float4*>(b + a.D) = m; *reinterpret_cast<float4*>(b + 2 * a.D) = v;
+      } else {
+        *reinterpret_cast<float4*>(b) = g;
+      }
+      continue;
+    }
+    __stcg(reinterpret_cast<float4*>(a.partial + (int64_t)d.z * a.D + j4 * 4), acc);
+    __syncwarp(gmask);                                 // the group's stores are ordered before the leader's fence
+    uint4 info = make_uint4(0u, 0u, 0u, 0u);
+    if (gl == 0) {
+      info = __ldcg(reinterpret_cast<const uint4*>(a.mrow_info + d.w));
+      __threadfence();                                 // release: the run sum is visible before the count
+      info.w = atomicAdd(&a.mrow_info[d.w].w, 1u);
+    }
+    info.x = __shfl_sync(gmask, info.x, gleader); info.y = __shfl_sync(gmask, info.y, gleader);
+    info.z = __shfl_sync(gmask, info.z, gleader); info.w = __shfl_sync(gmask, info.w, gleader);
+    if (info.w != info.y - 1u) continue;               // not the last run of the row to finish
+    __threadfence();
+    const float* p = a.partial + (int64_t)info.z * a.D + j4 * 4;
+    float4 tot = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (uint32_t r0 = 0; r0 < info.y; r0 += kRun) {
+      const int cnt = (int)min((uint32_t)kRun, info.y - r0);
+      for (int e = 0; e < cnt; ++e) cp_async16(mine + e * kRunThreads, p + (int64_t)(r0 + e) * a.D);
+      cp_async_commit(); cp_async_wait<0>();
+      for (int e = 0; e < cnt; ++e) tot = add4(tot, mine[e * kRunThreads]);
     }
     finish_row<FUSED>(a, info.x, j4, tot);
   }
@@ -542,19 +639,30 @@ static int segment_pipeline(bool fused, int order, const float* grad, const int6
   const size_t sm_final = kFinalSmemBytes;
   const int64_t groups_max = (n / (kRun + 1) + kFinalWarps) / kFinalWarps;
   const int grid_final = (int)(groups_max < (int64_t)kSMs * 3 ? groups_max : (int64_t)kSMs * 3);
+  const bool wide = (lpr == 16 || lpr == 32);            // a run's lanes are an aligned half or whole warp of >= kRun lanes
   stage_begin(st);
   if (n > 0) {
     if (fused) {
       if (sm_final > 48 * 1024 && note_cuda(cudaFuncSetAttribute(srm2_segment_final_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm_final)))
         return SRM2_ERR_CUDA;
       if (note_cuda(cudaFuncSetAttribute(srm2_segment_runsum_kernel<true, kRunPrefetch>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRunSmemBytes))) return SRM2_ERR_CUDA;
-      srm2_segment_runsum_kernel<true, kRunPrefetch><<<grid_runs, kRunThreads, kRunSmemBytes, st>>>(a);
+      if (wide) {
+        if (note_cuda(cudaFuncSetAttribute(srm2_segment_runsum_wide_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRunSmemBytes))) return SRM2_ERR_CUDA;
+        srm2_segment_runsum_wide_kernel<true><<<grid_runs, kRunThreads, kRunSmemBytes, st>>>(a);
+      } else {
+        srm2_segment_runsum_kernel<true, kRunPrefetch><<<grid_runs, kRunThreads, kRunSmemBytes, st>>>(a);
+      }
       if (!a.inplace) srm2_segment_final_kernel<true><<<grid_final, kFinalThreads, sm_final, st>>>(a, short_rows, chunk_rows);
     } else {
       if (sm_final > 48 * 1024 && note_cuda(cudaFuncSetAttribute(srm2_segment_final_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm_final)))
         return SRM2_ERR_CUDA;
       if (note_cuda(cudaFuncSetAttribute(srm2_segment_runsum_kernel<false, kRunPrefetch>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRunSmemBytes))) return SRM2_ERR_CUDA;
-      srm2_segment_runsum_kernel<false, kRunPrefetch><<<grid_runs, kRunThreads, kRunSmemBytes, st>>>(a);
+      if (wide) {
+        if (note_cuda(cudaFuncSetAttribute(srm2_segment_runsum_wide_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRunSmemBytes))) return SRM2_ERR_CUDA;
+        srm2_segment_runsum_wide_kernel<false><<<grid_runs, kRunThreads, kRunSmemBytes, st>>>(a);
+      } else {
+        srm2_segment_runsum_kernel<false, kRunPrefetch><<<grid_runs, kRunThreads, kRunSmemBytes, st>>>(a);
+      }
       if (!a.inplace) srm2_segment_final_kernel<false><<<grid_final, kFinalThreads, sm_final, st>>>(a, short_rows, chunk_rows);
     }
   }

@@ -11,8 +11,8 @@ namespace srm2 {
 
 constexpr int kSortThreads = 256;
 constexpr int kSortWarps = kSortThreads / 32;
-constexpr int kSortRounds = 8;                               // elements per thread
-constexpr int kSortTile = kSortThreads * kSortRounds;        // 2048 elements per CTA
+constexpr int kSortRounds = 4;                               // elements per thread
+constexpr int kSortTile = kSortThreads * kSortRounds;        // 1024 elements per CTA
 constexpr int kMaxRadixBits = 11;
 constexpr int kSuperTile = 16;                               // tiles per group whose digit sums are kept as well
 constexpr int64_t kFusedOffsetsLimit = (int64_t)1 << 23;     // tiles * digits up to which the scatter kernel derives its offsets itself
@@ -60,7 +60,7 @@ srm2_sort_hist_kernel(const int64_t* __restrict__ key64, const uint32_t* __restr
   }
 }
 
-// Stable scatter of one tile.  Warp w owns elements [w*256, (w+1)*256) of the tile and walks them in rounds of 32
+// Stable scatter of one tile.  Warp w owns elements [w*128, (w+1)*128) of the tile and walks them in rounds of 32
 // consecutive elements; __match_any_sync groups equal digits of a round, so the rank of an element among the equal
 // digits of its warp's sub-range is (count so far) + (equal digits in lower lanes).  Warp counts are then scanned
 // across the warps of the tile and added to the tile's global digit offset.
