@@ -288,6 +288,137 @@ def run_ours(a, world, rank, local_rank):
     return out
 
 
+
+# ------------------------------------------------------------------------------------------------ per-kernel figures
+def kernel_figures(dev, peak):
+    """Device-resident timings of the other kernels of the path (CUDA events, L2 flushed between repetitions by
+    writing a 256 MB buffer): row-sparse Adam at the 1 M x 16 and d = 128 shapes, counter-hash init, replay of 1..3
+    logged gradients into 262,144 x 64 rows, dedup, and one directory step (with the reference's ATen op chain on the
+    same GPU beside it where its compiled extension is present)."""
+    import torch
+    from elara_b200 import synth, ops
+    from elara_b200.gpu_ops import init_rows, replay_rows, ScalarTable
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timed(fn, reps=10):
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(reps):
+            flush.zero_()
+            e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(); e1.record(); torch.cuda.synchronize(dev)
+            ts.append(e0.elapsed_time(e1) * 1e3)
+        return float(np.median(ts))
+
+    def fig(us, nbytes, units, unit_name):
+        gbs = nbytes / us / 1e3
+        return {'us': us, 'GB/s': gbs, 'frac_of_measured_hbm': gbs / peak, unit_name + '/s': units / us * 1e6, 'algorithmic_bytes': nbytes}
+    out = {}
+    # row-sparse Adam, 1,000,000 x 16 table, 65,536 distinct Zipf(1.05) rows
+    R, d, n = 1_000_000, 16, 65_536
+    pool = init_rows(torch.arange(R, device=dev), d, SEED, 0.01)
+    rows = torch.from_numpy(synth.zipf_rows_without_replacement(R, n, 1.05, SEED, 1)).to(dev)
+    g = torch.randn(n, d, device=dev) * 1e-3
+    out['adam_1Mx16_65536rows'] = fig(timed(lambda: ops.gpu_adam(pool, rows, g, *HYP, 3)), n * (7 * d * 4 + 8), n, 'rows')
+    del pool, rows, g
+    # row-sparse Adam, d = 128, 262,144 distinct rows of an 8 M-row table
+    R, d, n = 8_000_000, 128, 262_144
+    pool = torch.empty(R, 3, d, device=dev)
+    for c in range(0, R, 1 << 20):
+        init_rows(torch.arange(c, min(R, c + (1 << 20)), device=dev), d, SEED, 0.01, out=pool[c:c + (1 << 20)])
+    rows = torch.randperm(R, device=dev)[:n].sort().values
+    g = torch.randn(n, d, device=dev) * 1e-3
+    out['adam_8Mx128_262144rows'] = fig(timed(lambda: ops.gpu_adam(pool, rows, g, *HYP, 3)), n * (7 * d * 4 + 8), n, 'rows')
+    del pool, rows, g
+    # init + replay, 262,144 rows x 64, histories of 1..3 gradients
+    n, d, K = 262_144, 64, 3
+    c = synth.replay_case(n, 4_000_000, d, K, 50, 1234)
+    t = {k: torch.from_numpy(v).to(dev) for k, v in c.items()}
+    table = ScalarTable(*HYP, 50, dev)
+    o = torch.empty(n, 3, d, device=dev)
+    out['init_262144x64'] = fig(timed(lambda: init_rows(t['rows'], d, 1234, 0.01, out=o)), n * (3 * d * 4 + 8), n, 'rows')
+    nbytes = n * (3 * d * 4 + 8 + 8 + 4 + 4 * K) + c['logs'].nbytes
+    out['replay_262144x64_k3'] = fig(timed(lambda: replay_rows(t['rows'], t['logs'], t['offs'], t['steps'], t['cnt'], d, K, 1234, 0.01, table, out=o)),
+                                     nbytes, n, 'rows')
+    out['replay_262144x64_k3']['note'] = 'bound by fp32 issue (3 IEEE divisions + 1 square root per element and entry), not by HBM'
+    # dedup of one batch
+    sizes, offs = synth.table_sizes(33_800_000, N_TABLES, seed=SEED)
+    ids = torch.from_numpy(synth.zipf_lookups(sizes, offs, 8192, ALPHA, SEED, 1)).to(dev)
+    out['dedup_212992_lookups_33.8M_rows'] = {'us': timed(lambda: ops.unique_inverse(ids, 33_800_000, sync=False)),
+                                              'torch_unique_us': timed(lambda: torch.unique(ids, return_inverse=True))}
+    out['directory_step'] = directory_figures(dev, timed)
+    return out
+
+
+def directory_figures(dev, timed):
+    """One synthetic plan step (call A: 50 k hits, 30 k replay rows, ~33 k evictions; admissions; call B: 45 k appends,
+    20 k compactions) on a 400 k-row directory: microseconds and kernel launches, ours and the reference's."""
+    import torch
+    from elara_b200 import _lib
+    from elara_b200.ops import dir_ext
+    rng = np.random.default_rng(11)
+    R, K, C, n0, T = 400_000, 3, 120_000, 20_000, 5
+    Lcap, Cdyn, MAT = 2 * R, C - n0, K + 1
+    code = rng.choice([0, 1, 2, 3, MAT], size=R, p=[0.4, 0.2, 0.1, 0.1, 0.2]).astype(np.int8)
+    ent = np.full((R + 1) * K, -1, np.int32); lstep = np.zeros(Lcap + 1, np.int32); top = 0
+    for c in (1, 2, 3):
+        rows = np.nonzero(code == c)[0]
+        for k in range(c):
+            ent[rows * K + k] = np.arange(top, top + len(rows)); lstep[top:top + len(rows)] = 7; top += len(rows)
+    nfree = 30_000
+    lfree = np.zeros(Lcap + 1, np.int32); lfree[:nfree] = np.arange(top, top + nfree); live = top; top += nfree
+    loc = np.full(R + 1, -1, np.int32); mrows = np.nonzero(code == MAT)[0]; loc[mrows] = np.arange(len(mrows))
+    res = rng.choice(R, C, replace=False)
+    slot_of = np.full(R, -1, np.int32); slot_of[res] = np.arange(C)
+    adm_c0 = np.where(code[res] == MAT, -1, code[res]).astype(np.int8)
+    rj = rng.integers(0, 3, C).astype(np.int8); rok = ((adm_c0 >= 0) & (rng.random(C) < 0.8)).astype(np.int8); rj[:n0] = 0; rok[:n0] = 0
+    st_np = [code, loc, ent, lstep, lfree, np.array([nfree]), np.array([top]), np.array([len(mrows)]), np.array([live]), adm_c0, rj,
+             rng.integers(1, 50, (Cdyn + 1, K)).astype(np.int32), np.array([3, 2, 3, 1, 3], np.int8), (np.arange(T) * (R // T)).astype(np.int64),
+             slot_of, res.astype(np.int64), rok]
+    pv = [R, K, Lcap, n0, Cdyn, MAT, R, 1]
+    slots = rng.permutation(C)
+    hs = np.sort(slots[:50_000]); ev = slots[30_000:70_000]; ev = ev[ev >= n0]
+    non_res = np.setdiff1d(np.arange(R), res)
+    L_row = non_res[(code[non_res] >= 1) & (code[non_res] <= K)][:30_000]; L_cnt = code[L_row].astype(np.int32)
+    adm = non_res[-len(ev):]; lazy = adm[code[adm] != MAT]; adm = np.concatenate([lazy, adm[code[adm] == MAT]])
+    cand = np.setdiff1d(non_res, adm)
+    a_rows = cand[code[cand] < K][:45_000]; a_k = code[a_rows].astype(np.int64)
+    c_rows = cand[code[cand] == K][:20_000]; c_cnt = np.full(len(c_rows), K, np.int64)
+    d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    args = dict(hs=d(hs), L_row=d(L_row), L_cnt=d(L_cnt), ev=d(ev), adm=d(adm), a_rows=d(a_rows), a_k=d(a_k), c_rows=d(c_rows), c_cnt=d(c_cnt))
+    fresh = lambda: [d(x.copy()) for x in st_np]
+
+    def one_step(dx, st, with_admit):
+        dx.elara_dir_a(st, pv, args['hs'], args['L_row'], args['L_cnt'], args['ev'], 60)
+        if with_admit:
+            dx.admit(st, pv, args['adm'], args['ev'], len(lazy), 60)
+        dx.elara_dir_b(st, pv, args['a_rows'], args['a_k'], args['c_rows'], args['c_cnt'], 60)
+    L = _lib.lib()
+    mine = dir_ext()
+    def timed_fresh(dx, with_admit, reps=8):                  # a directory step consumes its inputs: fresh state every time
+        ts = []
+        for r in range(reps + 2):
+            st = fresh(); torch.cuda.synchronize(dev)
+            e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+            e0.record(); one_step(dx, st, with_admit); e1.record(); torch.cuda.synchronize(dev)
+            if r >= 2:
+                ts.append(e0.elapsed_time(e1) * 1e3)
+        return float(np.median(ts))
+    l0 = L.srm2_launch_count(); st = fresh(); one_step(mine, st, True); launches = L.srm2_launch_count() - l0
+    out = {'us': timed_fresh(mine, True), 'kernel_launches': int(launches),
+           'sizes': {'hits': len(hs), 'replay_rows': len(L_row), 'evictions': len(ev), 'admissions': len(adm), 'appends': len(a_rows), 'compactions': len(c_rows)}}
+    try:
+        from oracle import oracle as O
+        ref = O.ref_dir()
+        if ref is not None:
+            out['reference_aten_chain_us'] = timed_fresh(ref, False)
+            out['reference_note'] = 'srm2/csrc/elara_dir.cpp (compiled in oracle/_ref) on CUDA tensors of the same GPU, calls A and B only'
+    except Exception as e:                                      # the comparison is optional
+        out['reference_note'] = 'reference extension not available: ' + repr(e)[:80]
+    return out
+
+
 def add_cpu_baseline(out, a):
     """Reference CPU path timed on this box's host cores on a bounded sample (N = 1 only)."""
     import torch
@@ -318,6 +449,7 @@ def main():
     ap.add_argument('--rows', type=int, default=0, help='rows per GPU (default: 33.8M at 1 GPU, 25M per GPU above)')
     ap.add_argument('--batch', type=int, default=8192, help='samples per GPU per step (x26 lookups)')
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--no-kernels', action='store_true', help='skip the per-kernel figures (N = 1 only)')
     a = ap.parse_args()
     world = int(os.environ.get('WORLD_SIZE', '1'))
     rank = int(os.environ.get('RANK', '0'))
@@ -342,6 +474,10 @@ def main():
         dist.init_process_group('nccl', device_id=torch.device('cuda', local_rank))
     out = run_ours(a, world, rank, local_rank)
     if out is not None:
+        if world == 1 and not a.no_kernels:
+            import torch as _t
+            _t.cuda.empty_cache()
+            out['kernels'] = kernel_figures(_t.device('cuda', local_rank), out['roofline']['peak'])
         if world == 1 and not a.no_cpu_baseline:
             add_cpu_baseline(out, a)
         print(json.dumps(out), flush=True)
