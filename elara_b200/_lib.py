@@ -39,7 +39,7 @@ SIGNATURES = {
     'srm2_unique_inverse_noalloc_i64': (C.c_int, [_vp, _i64, _i64, _vp, _i64, _vp, _vp, _vp]),
     'srm2_route_plan': (C.c_int, [_vp, _i64, _i64, _vp, _vp, _sz, _vp]),
     'srm2_route_publish': (C.c_int, [_vp, _vp, _i64, _i64, _vp]),
-    'srm2_route_dispatch': (C.c_int, [_vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _sz, _vp]),
+    'srm2_route_dispatch': (C.c_int, [_vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _i32, _vp, _sz, _vp]),
     'srm2_unique_inverse_nd_i64': (C.c_int, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _sz, _vp]),
     'srm2_reduce_adam_nd_f32': (C.c_int, [_vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _vp, _i64, _i32, _f8, _vp, _sz, _vp]),
 }

@@ -175,6 +175,140 @@ srm2_route_dispatch_kernel(const int64_t* __restrict__ ids, const float* __restr
   }
 }
 
+// ---- the same dispatch with the copy engines of the SMs (bulk asynchronous copies) ---------------------------------
+// One warp per CTA, one CTA per SM.  Lane l of a warp owns one routed lookup of a batch of 32: it issues a bulk copy
+// of the lookup's gradient row from HBM into the warp's shared-memory stage (completion counted on the stage's
+// mbarrier) and, once the batch has landed, a bulk copy from shared memory to the owner's receive buffer (peer memory,
+// no multicast).  Three stages keep two batches of loads in flight per SM.  The warp issues a few instructions per
+// 512-byte row and holds 48 KB of shared memory, so the shard update of the previous step keeps nearly all of every SM
+// while the rows move.  Every wait is bounded: if an mbarrier does not complete within kTmaSpinLimit polls the kernel
+// records err |= 4, drains its own copy groups and returns.
+constexpr int kTmaStages = 3;
+constexpr int kTmaRows = 32;
+constexpr uint32_t kTmaSpinLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+               ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\n" ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;\n" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory"); }
+
+__global__ void __launch_bounds__(32)
+srm2_route_dispatch_tma_kernel(const int64_t* __restrict__ ids, const float* __restrict__ grad, const uint32_t* __restrict__ perm,
+                               const uint32_t* __restrict__ owner_sorted, int64_t n, int D, int world, int rank,
+                               const int64_t* __restrict__ cmat, PeerPtrs lid_peers, PeerPtrs grad_peers, int64_t cap,
+                               int64_t* __restrict__ n_recv, uint32_t* __restrict__ err) {
+  extern __shared__ __align__(128) unsigned char stage_mem[];      // [kTmaStages][kTmaRows][row bytes]
+  __shared__ __align__(8) uint64_t bar[kTmaStages];
+  __shared__ int64_t s_start[kMaxPeers], s_base[kMaxPeers];
+  const int lane = threadIdx.x;
+  const uint32_t row_bytes = (uint32_t)D * 4u;
+  if (lane < world) {
+    const int d = lane;
+    int64_t start = 0, base = 0;
+    for (int e = 0; e < d; ++e) start += cmat[rank * world + e];
+    for (int q = 0; q < rank; ++q) base += cmat[q * world + d];
+    s_start[d] = start; s_base[d] = base;
+    if (blockIdx.x == 0 && d == rank) {
+      int64_t tot = 0;
+      for (int q = 0; q < world; ++q) tot += cmat[q * world + rank];
+      *n_recv = tot;
+      if (tot > cap) atomicOr(err, 1u);
+    }
+  }
+  if (lane == 0) {
+    for (int q = 0; q < kTmaStages; ++q) mbar_init(&bar[q], 1u);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  __syncwarp();
+  // this CTA's contiguous share of the routed order, in batches of 32
+  int64_t per = (n + gridDim.x - 1) / gridDim.x; per = (per + kTmaRows - 1) / kTmaRows * kTmaRows;
+  const int64_t lo = (int64_t)blockIdx.x * per, hi = lo + per < n ? lo + per : n;
+  const int64_t nb = hi > lo ? (hi - lo + kTmaRows - 1) / kTmaRows : 0;
+  char* dst[kTmaStages];
+  bool pending[kTmaStages];                              // a batch of loads is in flight into this stage
+#pragma unroll
+  for (int q = 0; q < kTmaStages; ++q) pending[q] = false;
+  bool failed = false;
+
+  auto issue_load = [&](int64_t b, int st) {
+    const int64_t i = lo + b * kTmaRows + lane;
+    bool valid = i < hi;
+    uint32_t d = 0, p = 0; int64_t r = 0;
+    if (valid) {
+      d = owner_sorted[i];
+      valid = d < (uint32_t)world;
+      if (valid) { r = s_base[d] + (i - s_start[d]); if (r >= cap) { atomicOr(err, 1u); valid = false; } }
+      if (valid) p = perm[i];
+    }
+    const unsigned vm = __ballot_sync(0xffffffffu, valid);
+    if (lane == 0) mbar_expect_tx(&bar[st], (uint32_t)__popc(vm) * row_bytes);
+    __syncwarp();
+    dst[st] = nullptr;
+    pending[st] = true;
+    if (valid) {
+      bulk_load(stage_mem + ((size_t)st * kTmaRows + lane) * row_bytes, grad + (int64_t)p * D, row_bytes, &bar[st]);
+      const int64_t id = ids[p];
+      static_cast<int64_t*>(lid_peers.p[d])[r] = id < 0 ? -1 : id / world;
+      dst[st] = static_cast<char*>(grad_peers.p[d]) + r * (int64_t)row_bytes;
+    }
+  };
+
+#pragma unroll
+  for (int q = 0; q < kTmaStages - 1; ++q)
+    if (q < nb) issue_load(q, q);
+  for (int64_t b0 = 0; b0 < nb && !failed; b0 += kTmaStages) {
+    const uint32_t parity = (uint32_t)((b0 / kTmaStages) & 1);
+#pragma unroll
+    for (int st = 0; st < kTmaStages; ++st) {
+      const int64_t b = b0 + st;
+      if (b >= nb || failed) break;
+      uint32_t spins = 0;
+      while (!mbar_try_wait(&bar[st], parity)) {
+        if (++spins > kTmaSpinLimit) { failed = true; break; }
+      }
+      failed = __any_sync(0xffffffffu, failed);
+      if (failed) break;
+      pending[st] = false;
+      if (dst[st] != nullptr) bulk_store(dst[st], stage_mem + ((size_t)st * kTmaRows + lane) * row_bytes, row_bytes);
+      bulk_commit();
+      // refill the stage that batch b-1 was stored from: its reads of shared memory must be over
+      constexpr int kPrev = kTmaStages - 1;
+      const int rs = (st + kPrev) % kTmaStages;
+      if (b + kPrev < nb) { bulk_wait_read<1>(); issue_load(b + kPrev, rs); }
+    }
+  }
+  if (failed) {
+    // give the loads that are still in flight a bounded chance to land before the shared memory is given back
+    if (lane == 0) atomicOr(err, 4u);
+#pragma unroll
+    for (int st = 0; st < kTmaStages; ++st) {
+      if (!pending[st]) continue;
+      for (uint32_t spins = 0; spins < kTmaSpinLimit; ++spins)
+        if (mbar_try_wait(&bar[st], 0u) || mbar_try_wait(&bar[st], 1u)) break;
+    }
+  }
+  bulk_wait_all();
+}
+
 }  // namespace srm2
 
 extern "C" int srm2_route_plan(const int64_t* ids, int64_t n, int64_t world, int64_t* out_counts, void* scratch,
@@ -207,7 +341,8 @@ extern "C" int srm2_route_publish(const int64_t* counts, void* const* peer_cmat,
 
 extern "C" int srm2_route_dispatch(const int64_t* ids, const float* grad, int64_t n, int64_t D, int64_t world, int64_t rank,
                                    const int64_t* cmat, void* const* peer_lid, void* const* peer_grad, int64_t cap,
-                                   int64_t* n_recv, uint32_t* err, void* scratch, size_t scratch_bytes, srm2_stream_t stream) {
+                                   int64_t* n_recv, uint32_t* err, int use_tma, void* scratch, size_t scratch_bytes,
+                                   srm2_stream_t stream) {
   using namespace srm2;
   if (n < 0 || D <= 0 || world < 1 || world > kMaxPeers || rank < 0 || rank >= world || cap < 0) return SRM2_ERR_ARG;
   if (cmat == nullptr || peer_lid == nullptr || peer_grad == nullptr || n_recv == nullptr || err == nullptr) return SRM2_ERR_ARG;
@@ -228,7 +363,19 @@ extern "C" int srm2_route_dispatch(const int64_t* ids, const float* grad, int64_
   // update, which should keep most of every SM
   int grid = (int)((items + 255) / 256 < (int64_t)kSMs * 2 ? (items + 255) / 256 : (int64_t)kSMs * 2);
   if (grid < 1) grid = 1;
-  srm2_route_dispatch_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(ids, grad, sb.valA, sb.keyA, n, lpr, shift, (int)D,
-                                                                                 (int)world, (int)rank, cmat, pl, pg, cap, n_recv, err);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t tma_smem = (size_t)kTmaStages * kTmaRows * D * 4;
+  if (use_tma && n > 0 && D * 4 <= 1024) {
+    if (tma_smem > 48 * 1024 &&
+        note_cuda(cudaFuncSetAttribute(srm2_route_dispatch_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tma_smem)))
+      return SRM2_ERR_CUDA;
+    const int64_t batches = (n + kTmaRows - 1) / kTmaRows;
+    const int tgrid = (int)(batches < kSMs ? batches : kSMs);
+    srm2_route_dispatch_tma_kernel<<<tgrid, 32, tma_smem, st>>>(ids, grad, sb.valA, sb.keyA, n, (int)D, (int)world, (int)rank, cmat, pl, pg,
+                                                               cap, n_recv, err);
+    return launch_status(1);
+  }
+  srm2_route_dispatch_kernel<<<grid, 256, 0, st>>>(ids, grad, sb.valA, sb.keyA, n, lpr, shift, (int)D, (int)world, (int)rank, cmat, pl, pg,
+                                                  cap, n_recv, err);
   return launch_status(1);
 }

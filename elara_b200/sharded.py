@@ -57,6 +57,7 @@ class ShardedSparseAdam:
             init_rows(l * world + rank, D, seed, bound, out=self.pool[c:c + l.numel()])
         self.last_local_lookups = 0
         self.last_local_lookups_total = 0
+        self.use_tma = True          # dispatch rows with bulk asynchronous copies (one warp per SM) instead of load/store threads
         if world > 1:
             n = int(max_lookups_per_rank)
             self._lid = torch.empty(n, dtype=torch.int64, device=device)
@@ -248,7 +249,7 @@ class ShardedSparseAdam:
                 dist.all_reduce(P['bar'], group=self.group)       # barrier: count matrices complete, receive buffers reset
                 _lib.check(L.srm2_route_dispatch(_lib.ptr(ids), _lib.ptr(grads), n, D, W, self.rank, cmat_b.data_ptr(), P['p_lid'][b],
                                                  P['p_grad'][b], cap, P['n_recv'][b:b + 1].data_ptr(), P['err'].data_ptr(),
-                                                 scr.data_ptr(), scr.numel(), s), 'route_dispatch')
+                                                 int(self.use_tma), scr.data_ptr(), scr.numel(), s), 'route_dispatch')
                 dist.all_reduce(P['bar'], group=self.group)       # barrier: every row has arrived
                 ev_payload[k].record(comm)
 
@@ -268,7 +269,7 @@ class ShardedSparseAdam:
             out.append(count)
         comp.wait_stream(comm)
         if int(P['err'].item()) != 0:
-            raise RuntimeError('a receive buffer overflowed: raise the slack of enable_p2p')
+            raise RuntimeError('row dispatch failed (status %d: 1 = receive buffer overflow, 4 = a copy did not complete)' % int(P['err'].item()))
         nr = int(P['n_recv'][(K - 1) & 1].item())
         self.last_local_lookups = nr
         self.last_local_lookups_total += nr * K

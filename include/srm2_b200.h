@@ -236,6 +236,8 @@ int srm2_unique_inverse_noalloc_i64(const int64_t* ids, int64_t n, int64_t n_row
  *   srm2_route_dispatch  local ids (row_id div world) -> peer_lid[d] [cap] int64 and gradient rows -> peer_grad[d] [cap, D]
  *                        of each owner d, at the row offsets that give rank order; n_recv (device int64) = rows this rank
  *                        will receive; *err |= 1 if a receive buffer would overflow (those rows are not written).
+ *                        use_tma != 0 (rows of at most 1 KiB): the rows move as bulk asynchronous copies HBM -> shared
+ *                        memory -> owner, one warp per SM; *err |= 4 if a bounded wait on such a copy ran out.
  *                        `scratch` must be the buffer srm2_route_plan was given.
  *   -- barrier --        every row has arrived
  * Receive buffers hold cap rows; fill their id part with -1 before the first barrier so that unused rows are ignored
@@ -246,7 +248,7 @@ int srm2_route_plan(const int64_t* ids, int64_t n, int64_t world, int64_t* out_c
 int srm2_route_publish(const int64_t* counts, void* const* peer_cmat /* host */, int64_t rank, int64_t world, srm2_stream_t stream);
 int srm2_route_dispatch(const int64_t* ids, const float* grad, int64_t n, int64_t D, int64_t world, int64_t rank,
                         const int64_t* cmat, void* const* peer_lid /* host */, void* const* peer_grad /* host */, int64_t cap,
-                        int64_t* n_recv, uint32_t* err, void* scratch, size_t scratch_bytes, srm2_stream_t stream);
+                        int64_t* n_recv, uint32_t* err, int use_tma, void* scratch, size_t scratch_bytes, srm2_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------------
  * Variants whose lookup count lives on the device (no counterpart in the reference): n is an upper bound that sizes
