@@ -175,35 +175,17 @@ srm2_route_dispatch_kernel(const int64_t* __restrict__ ids, const float* __restr
   }
 }
 
-// ---- the same dispatch with the copy engines of the SMs (bulk asynchronous copies) ---------------------------------
-// One warp per CTA, one CTA per SM.  Lane l of a warp owns one routed lookup of a batch of 32: it issues a bulk copy
-// of the lookup's gradient row from HBM into the warp's shared-memory stage (completion counted on the stage's
-// mbarrier) and, once the batch has landed, a bulk copy from shared memory to the owner's receive buffer (peer memory,
-// no multicast).  Three stages keep two batches of loads in flight per SM.  The warp issues a few instructions per
-// 512-byte row and holds 48 KB of shared memory, so the shard update of the previous step keeps nearly all of every SM
-// while the rows move.  Every wait is bounded: if an mbarrier does not complete within kTmaSpinLimit polls the kernel
-// records err |= 4, drains its own copy groups and returns.
+// ---- the same dispatch with asynchronous copies, one small CTA per SM --------------------------------------------------
+// A CTA of four warps moves batches of 32 routed lookups through a shared-memory stage: the gradient rows are gathered from HBM
+// with cp.async (16 bytes per lane, 512 contiguous stage bytes per instruction, nothing held in registers) and, once a
+// batch has landed, sent to the owner's receive buffer with one bulk asynchronous copy shared -> global (peer memory,
+// no multicast) — one copy for the whole batch, because consecutive lookups of a group go to consecutive rows.
+// Three stages keep two batches of loads in flight per SM.  The CTA has 128 threads and holds 48 KB of shared memory, so the shard update of the previous step keeps nearly all of every SM while the rows move.
+// The only waits are cp.async.wait_group / cp.async.bulk.wait_group on a thread's own copies and CTA barriers.
 constexpr int kTmaStages = 3;
 constexpr int kTmaRows = 32;
-constexpr uint32_t kTmaSpinLimit = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
-               ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
-}
 __device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
   asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\n" ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
 }
@@ -211,18 +193,18 @@ __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.comm
 template <int N> __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;\n" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory"); }
 
-__global__ void __launch_bounds__(32)
+constexpr int kTmaWarps = 4;
+__global__ void __launch_bounds__(32 * kTmaWarps)
 srm2_route_dispatch_tma_kernel(const int64_t* __restrict__ ids, const float* __restrict__ grad, const uint32_t* __restrict__ perm,
                                const uint32_t* __restrict__ owner_sorted, int64_t n, int D, int world, int rank,
                                const int64_t* __restrict__ cmat, PeerPtrs lid_peers, PeerPtrs grad_peers, int64_t cap,
                                int64_t* __restrict__ n_recv, uint32_t* __restrict__ err) {
   extern __shared__ __align__(128) unsigned char stage_mem[];      // [kTmaStages][kTmaRows][row bytes]
-  __shared__ __align__(8) uint64_t bar[kTmaStages];
   __shared__ int64_t s_start[kMaxPeers], s_base[kMaxPeers];
-  const int lane = threadIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const uint32_t row_bytes = (uint32_t)D * 4u;
-  if (lane < world) {
-    const int d = lane;
+  if (threadIdx.x < world) {
+    const int d = threadIdx.x;
     int64_t start = 0, base = 0;
     for (int e = 0; e < d; ++e) start += cmat[rank * world + e];
     for (int q = 0; q < rank; ++q) base += cmat[q * world + d];
@@ -234,78 +216,92 @@ srm2_route_dispatch_tma_kernel(const int64_t* __restrict__ ids, const float* __r
       if (tot > cap) atomicOr(err, 1u);
     }
   }
-  if (lane == 0) {
-    for (int q = 0; q < kTmaStages; ++q) mbar_init(&bar[q], 1u);
-    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-  }
-  __syncwarp();
+  __syncthreads();
   // this CTA's contiguous share of the routed order, in batches of 32
   int64_t per = (n + gridDim.x - 1) / gridDim.x; per = (per + kTmaRows - 1) / kTmaRows * kTmaRows;
   const int64_t lo = (int64_t)blockIdx.x * per, hi = lo + per < n ? lo + per : n;
   const int64_t nb = hi > lo ? (hi - lo + kTmaRows - 1) / kTmaRows : 0;
-  char* dst[kTmaStages];
-  bool pending[kTmaStages];                              // a batch of loads is in flight into this stage
-#pragma unroll
-  for (int q = 0; q < kTmaStages; ++q) pending[q] = false;
-  bool failed = false;
 
-  auto issue_load = [&](int64_t b, int st) {
+  // Metadata of a batch (owner, permutation entry, destination row, local id) is fetched one iteration before the
+  // batch's copies are issued, so those plain loads are never waited for.  Lane l holds the metadata of row l.
+  struct Meta { uint32_t d, p; int64_t r, lid; bool valid; };
+  Meta meta[kTmaStages];                                     // metadata of the batch held by each stage
+  auto fetch_meta = [&](int64_t b) -> Meta {
+    Meta m{0u, 0u, 0, 0, false};
     const int64_t i = lo + b * kTmaRows + lane;
-    bool valid = i < hi;
-    uint32_t d = 0, p = 0; int64_t r = 0;
-    if (valid) {
-      d = owner_sorted[i];
-      valid = d < (uint32_t)world;
-      if (valid) { r = s_base[d] + (i - s_start[d]); if (r >= cap) { atomicOr(err, 1u); valid = false; } }
-      if (valid) p = perm[i];
+    if (b < nb && i < hi) {
+      m.d = owner_sorted[i];
+      if (m.d < (uint32_t)world) {
+        m.r = s_base[m.d] + (i - s_start[m.d]);
+        if (m.r >= cap) atomicOr(err, 1u);
+        else { m.p = perm[i]; const int64_t id = ids[m.p]; m.lid = id < 0 ? -1 : id / world; m.valid = true; }
+      }
     }
-    const unsigned vm = __ballot_sync(0xffffffffu, valid);
-    if (lane == 0) mbar_expect_tx(&bar[st], (uint32_t)__popc(vm) * row_bytes);
-    __syncwarp();
-    dst[st] = nullptr;
-    pending[st] = true;
-    if (valid) {
-      bulk_load(stage_mem + ((size_t)st * kTmaRows + lane) * row_bytes, grad + (int64_t)p * D, row_bytes, &bar[st]);
-      const int64_t id = ids[p];
-      static_cast<int64_t*>(lid_peers.p[d])[r] = id < 0 ? -1 : id / world;
-      dst[st] = static_cast<char*>(grad_peers.p[d]) + r * (int64_t)row_bytes;
+    return m;
+  };
+  // Gather of one batch into a stage: the warp copies 512 contiguous bytes of the stage per instruction (16 bytes per
+  // lane, cp.async), i.e. whole rows or row halves depending on the row size; the source row of each piece comes from the
+  // lane that holds that row's metadata.  No registers hold data, so two batches (32 rows each) stay in flight.
+  const int pieces = (int)(kTmaRows * row_bytes / 512u);           // instructions per batch
+  auto issue_gather = [&](const Meta& m, int st) {
+    unsigned char* base = stage_mem + (size_t)st * kTmaRows * row_bytes;
+    for (int k = warp; k < pieces; k += kTmaWarps) {               // the warps of the CTA share the pieces of a batch
+      const uint32_t o = (uint32_t)k * 512u + (uint32_t)lane * 16u;
+      const int row = (int)(o / row_bytes);
+      const uint32_t col = o - (uint32_t)row * row_bytes;
+      const uint32_t p = __shfl_sync(0xffffffffu, m.p, row);
+      const bool ok = __shfl_sync(0xffffffffu, (int)m.valid, row) != 0;
+      if (ok) {
+        const unsigned sa = smem_u32(base + o);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sa), "l"(reinterpret_cast<const char*>(grad) + (int64_t)p * row_bytes + col) : "memory");
+      }
     }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+    meta[st] = m;
+    if (warp == 0 && m.valid) static_cast<int64_t*>(lid_peers.p[m.d])[m.r] = m.lid;
+  };
+  // Stores of a landed batch: one bulk copy for the whole batch when its rows go to consecutive rows of one owner
+  // (always, except where two owners' groups meet and at the tail), otherwise one bulk copy per row.
+  auto issue_stores = [&](int st) {
+    const Meta& m = meta[st];
+    unsigned char* base = stage_mem + (size_t)st * kTmaRows * row_bytes;
+    const unsigned vm = __ballot_sync(0xffffffffu, m.valid);
+    const uint32_t d0 = __shfl_sync(0xffffffffu, m.d, 0);
+    const int64_t r0 = __shfl_sync(0xffffffffu, m.r, 0);
+    const bool fits = !m.valid || (m.d == d0 && m.r == r0 + lane);
+    const bool prefix = (vm & (vm + 1u)) == 0u;                     // the valid lanes are lanes 0..k-1
+    const bool merged = __all_sync(0xffffffffu, fits) && prefix && vm != 0u;
+    if (merged) {
+      if (lane == 0) bulk_store(static_cast<char*>(grad_peers.p[d0]) + r0 * (int64_t)row_bytes, base, (uint32_t)__popc(vm) * row_bytes);
+    } else if (m.valid) {
+      bulk_store(static_cast<char*>(grad_peers.p[m.d]) + m.r * (int64_t)row_bytes, base + (size_t)lane * row_bytes, row_bytes);
+    }
+    bulk_commit();
   };
 
 #pragma unroll
-  for (int q = 0; q < kTmaStages - 1; ++q)
-    if (q < nb) issue_load(q, q);
-  for (int64_t b0 = 0; b0 < nb && !failed; b0 += kTmaStages) {
-    const uint32_t parity = (uint32_t)((b0 / kTmaStages) & 1);
+  for (int q = 0; q < kTmaStages - 1; ++q) issue_gather(fetch_meta(q), q);     // empty batches commit empty groups
+  Meta next = fetch_meta(kTmaStages - 1);
+  for (int64_t b0 = 0; b0 < nb; b0 += kTmaStages) {
 #pragma unroll
     for (int st = 0; st < kTmaStages; ++st) {
       const int64_t b = b0 + st;
-      if (b >= nb || failed) break;
-      uint32_t spins = 0;
-      while (!mbar_try_wait(&bar[st], parity)) {
-        if (++spins > kTmaSpinLimit) { failed = true; break; }
-      }
-      failed = __any_sync(0xffffffffu, failed);
-      if (failed) break;
-      pending[st] = false;
-      if (dst[st] != nullptr) bulk_store(dst[st], stage_mem + ((size_t)st * kTmaRows + lane) * row_bytes, row_bytes);
-      bulk_commit();
-      // refill the stage that batch b-1 was stored from: its reads of shared memory must be over
+      if (b >= nb) break;
+      asm volatile("cp.async.wait_group %0;\n" ::"n"(kTmaStages - 2) : "memory");   // this thread's pieces of batch b have landed
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");                 // ... and are visible to the bulk-copy engine
+      __syncthreads();                                                               // ... and so have everybody's
       constexpr int kPrev = kTmaStages - 1;
       const int rs = (st + kPrev) % kTmaStages;
-      if (b + kPrev < nb) { bulk_wait_read<1>(); issue_load(b + kPrev, rs); }
+      if (warp == 0) {
+        issue_stores(st);
+        bulk_wait_read<1>();     // the bulk copy of batch b-1 has finished reading stage rs, which is refilled next
+      }
+      __syncthreads();
+      issue_gather(next, rs);                                      // beyond the last batch this commits an empty group
+      next = fetch_meta(b + kPrev + 1);
     }
   }
-  if (failed) {
-    // give the loads that are still in flight a bounded chance to land before the shared memory is given back
-    if (lane == 0) atomicOr(err, 4u);
-#pragma unroll
-    for (int st = 0; st < kTmaStages; ++st) {
-      if (!pending[st]) continue;
-      for (uint32_t spins = 0; spins < kTmaSpinLimit; ++spins)
-        if (mbar_try_wait(&bar[st], 0u) || mbar_try_wait(&bar[st], 1u)) break;
-    }
-  }
+  asm volatile("cp.async.wait_group 0;\n" ::: "memory");
   bulk_wait_all();
 }
 
@@ -366,12 +362,12 @@ extern "C" int srm2_route_dispatch(const int64_t* ids, const float* grad, int64_
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const size_t tma_smem = (size_t)kTmaStages * kTmaRows * D * 4;
   if (use_tma && n > 0 && D * 4 <= 1024) {
-    if (tma_smem > 48 * 1024 &&
+    if (tma_smem + 1024 > 48 * 1024 &&                       // static shared memory counts against the same limit
         note_cuda(cudaFuncSetAttribute(srm2_route_dispatch_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tma_smem)))
       return SRM2_ERR_CUDA;
     const int64_t batches = (n + kTmaRows - 1) / kTmaRows;
     const int tgrid = (int)(batches < kSMs ? batches : kSMs);
-    srm2_route_dispatch_tma_kernel<<<tgrid, 32, tma_smem, st>>>(ids, grad, sb.valA, sb.keyA, n, (int)D, (int)world, (int)rank, cmat, pl, pg,
+    srm2_route_dispatch_tma_kernel<<<tgrid, 32 * kTmaWarps, tma_smem, st>>>(ids, grad, sb.valA, sb.keyA, n, (int)D, (int)world, (int)rank, cmat, pl, pg,
                                                                cap, n_recv, err);
     return launch_status(1);
   }

@@ -65,6 +65,31 @@ class ShardedSparseAdam:
             self._counts = torch.empty(world, dtype=torch.int64, device=device)
             self._pipe = None
 
+    # ---- lean host path: cached pointers and preallocated buffers, two C calls per shard update --------------------
+    def _fast_state(self, n_max):
+        f = getattr(self, '_fast', None)
+        if f is None or f['n'] < n_max:
+            L = _lib.lib()
+            n_rows = max(self.n_local if self.world > 1 else self.total_rows, 1)
+            cap_u = min(n_max, n_rows)
+            mk = lambda n, dt: torch.empty(max(n, 1), dtype=dt, device=self.dev)
+            f = dict(n=n_max, n_rows=n_rows, cap_u=cap_u, u=mk(cap_u, torch.int64), inv=mk(n_max, torch.int64),
+                     scr_u=mk(L.srm2_unique_scratch_bytes(n_rows), torch.uint8),
+                     scr_s=mk(L.srm2_segment_scratch_bytes(n_max, cap_u, self.D), torch.uint8))
+            self._fast = f
+        return f
+
+    def _update_fast(self, ids_ptr, n, grad_ptr, n_dev_ptr, step, count_ptr, order, stream):
+        """dedup + fused segment-reduce + Adam of n (or *n_dev) lookups on the shard; everything by address."""
+        L = _lib.lib()
+        f = self._fast_state(n)
+        _lib.check(L.srm2_unique_inverse_nd_i64(ids_ptr, n, n_dev_ptr, f['n_rows'], f['u'].data_ptr(), f['cap_u'], f['inv'].data_ptr(),
+                                                count_ptr, f['scr_u'].data_ptr(), f['scr_u'].numel(), stream), 'unique_inverse')
+        sc = ops._scalars(*self.hyper, step)
+        _lib.check(L.srm2_reduce_adam_nd_f32(self.pool.data_ptr(), f['u'].data_ptr(), grad_ptr, f['inv'].data_ptr(), n, n_dev_ptr, self.D,
+                                             -1, count_ptr, min(n, f['cap_u']), order, sc, f['scr_s'].data_ptr(), f['scr_s'].numel(),
+                                             stream), 'reduce_adam')
+
     def route(self, ids, grads):
         """-> (lids grouped by owner, gradient rows in the same order, per-owner counts on the device)."""
         n = ids.numel()
@@ -85,8 +110,9 @@ class ShardedSparseAdam:
         count tensor of the local dedup (count[0] = rows updated on this rank).  Nothing waits on the GPU when
         world == 1; with world > 1 the all-to-all split sizes are read on the host once per step."""
         if self.world == 1:
-            u, inv, count = ops.unique_inverse(ids, self.total_rows, sync=False)
-            ops.reduce_adam(self.pool, u, grads, inv, *self.hyper, step, count=count)
+            count = torch.empty(2, dtype=torch.int64, device=self.dev)
+            self._update_fast(ids.data_ptr(), ids.numel(), grads.data_ptr(), 0, step, count.data_ptr(), ops.ORDER_AUTO,
+                              torch.cuda.current_stream(self.dev).cuda_stream)
             self.last_local_lookups = ids.numel()
             self.last_local_lookups_total += ids.numel()
             return count
@@ -232,24 +258,30 @@ class ShardedSparseAdam:
         ev_start = torch.cuda.Event(); ev_start.record(comp)
         comm.wait_event(ev_start)
 
+        counts_out = torch.zeros(K, 2, dtype=torch.int64, device=self.dev)
+        n_max = max(i.numel() for i, _ in batches)
+        scr = ops._scratch(self.dev, L.srm2_route_scratch_bytes(n_max, W), 'route')
+        scr_ptr, scr_len = scr.data_ptr(), scr.numel()
+        cs, ms = comm.cuda_stream, comp.cuda_stream
+        counts_ptr, err_ptr = P['counts'].data_ptr(), P['err'].data_ptr()
+        cmat_ptr = [P['cmat'][b * W * W:].data_ptr() for b in range(2)]
+        nrecv_ptr = [P['n_recv'][b:].data_ptr() for b in range(2)]
+        rl_ptr = [P['rlid'][b * cap:].data_ptr() for b in range(2)]
+        rg_ptr = [P['rgrad'][b * cap * D:].data_ptr() for b in range(2)]
+        self._fast_state(cap)
+
         def prepare(k):
             ids, grads = batches[k]
             b, n = k & 1, ids.numel()
-            rlid_b = P['rlid'][b * cap:(b + 1) * cap]
-            cmat_b = P['cmat'][b * W * W:(b + 1) * W * W]
             with torch.cuda.stream(comm):
                 if k >= 2:
                     comm.wait_event(ev_done[k - 2])               # this parity's receive buffer has been consumed
-                rlid_b.fill_(-1)
-                nb = L.srm2_route_scratch_bytes(n, W)
-                scr = ops._scratch(self.dev, nb, 'route')
-                s = comm.cuda_stream
-                _lib.check(L.srm2_route_plan(_lib.ptr(ids), n, W, P['counts'].data_ptr(), scr.data_ptr(), scr.numel(), s), 'route_plan')
-                _lib.check(L.srm2_route_publish(P['counts'].data_ptr(), P['p_cmat'][b], self.rank, W, s), 'route_publish')
-                dist.all_reduce(P['bar'], group=self.group)       # barrier: count matrices complete, receive buffers reset
-                _lib.check(L.srm2_route_dispatch(_lib.ptr(ids), _lib.ptr(grads), n, D, W, self.rank, cmat_b.data_ptr(), P['p_lid'][b],
-                                                 P['p_grad'][b], cap, P['n_recv'][b:b + 1].data_ptr(), P['err'].data_ptr(),
-                                                 int(self.use_tma), scr.data_ptr(), scr.numel(), s), 'route_dispatch')
+                _lib.check(L.srm2_route_plan(ids.data_ptr(), n, W, counts_ptr, scr_ptr, scr_len, cs), 'route_plan')
+                _lib.check(L.srm2_route_publish(counts_ptr, P['p_cmat'][b], self.rank, W, cs), 'route_publish')
+                dist.all_reduce(P['bar'], group=self.group)       # barrier: count matrices complete, receive buffers free
+                _lib.check(L.srm2_route_dispatch(ids.data_ptr(), grads.data_ptr(), n, D, W, self.rank, cmat_ptr[b], P['p_lid'][b],
+                                                 P['p_grad'][b], cap, nrecv_ptr[b], err_ptr, int(self.use_tma), scr_ptr, scr_len, cs),
+                           'route_dispatch')
                 dist.all_reduce(P['bar'], group=self.group)       # barrier: every row has arrived
                 ev_payload[k].record(comm)
 
@@ -260,13 +292,10 @@ class ShardedSparseAdam:
             if k + 1 < K:
                 prepare(k + 1)
             comp.wait_event(ev_payload[k])
-            rl = P['rlid'][b * cap:(b + 1) * cap]
-            rg = P['rgrad'][b * cap * D:(b + 1) * cap * D].view(cap, D)
-            nd = P['n_recv'][b:b + 1]                             # rows that arrived, known to the device only
-            u, inv, count = ops.unique_inverse(rl, max(self.n_local, 1), sync=False, n_dev=nd)
-            ops.reduce_adam(self.pool, u, rg, inv, *self.hyper, first_step + k, count=count, order=ops.ORDER_RUNS, n_dev=nd)
+            # the number of rows that arrived is known to the device only (n_recv); cap bounds it
+            self._update_fast(rl_ptr[b], cap, rg_ptr[b], nrecv_ptr[b], first_step + k, counts_out[k].data_ptr(), ops.ORDER_RUNS, ms)
             ev_done[k].record(comp)
-            out.append(count)
+            out.append(counts_out[k])
         comp.wait_stream(comm)
         if int(P['err'].item()) != 0:
             raise RuntimeError('row dispatch failed (status %d: 1 = receive buffer overflow, 4 = a copy did not complete)' % int(P['err'].item()))

@@ -236,8 +236,8 @@ int srm2_unique_inverse_noalloc_i64(const int64_t* ids, int64_t n, int64_t n_row
  *   srm2_route_dispatch  local ids (row_id div world) -> peer_lid[d] [cap] int64 and gradient rows -> peer_grad[d] [cap, D]
  *                        of each owner d, at the row offsets that give rank order; n_recv (device int64) = rows this rank
  *                        will receive; *err |= 1 if a receive buffer would overflow (those rows are not written).
- *                        use_tma != 0 (rows of at most 1 KiB): the rows move as bulk asynchronous copies HBM -> shared
- *                        memory -> owner, one warp per SM; *err |= 4 if a bounded wait on such a copy ran out.
+ *                        use_tma != 0 (rows of at most 1 KiB): one warp per SM gathers the rows into shared memory with
+ *                        cp.async and sends them with bulk asynchronous copies shared -> owner.
  *                        `scratch` must be the buffer srm2_route_plan was given.
  *   -- barrier --        every row has arrived
  * Receive buffers hold cap rows; fill their id part with -1 before the first barrier so that unused rows are ignored
