@@ -214,10 +214,57 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 #define SRM2_RUN_PREFETCH 1
 #endif
 constexpr bool kRunPrefetch = SRM2_RUN_PREFETCH != 0;
-constexpr int kInplaceMaxRuns = 1 << 30;  // rows with more runs would be left to the multi-run kernel (measured: not worth a launch)
+constexpr int kInplaceMaxRuns = 512;      // rows with more runs (> 5120 lookups) are finished by a whole CTA after its last item
+                                          // instead of the lane group that completed them: 256 threads copy ten times more
+                                          // at once; shorter chains hide behind the single-run rows still streaming
 constexpr int kRunThreads = 256;
 constexpr int kRunStageVecs = kRun + 3;                                  // gradient rows + w, m, v
-constexpr int kRunSmemBytes = kRunStageVecs * kRunThreads * 16;         // 53,248 B per CTA
+constexpr int kLongCap = 16;              // long rows one CTA can take over; further ones are finished by their lane group
+constexpr int kRunSmemBytes = kRunStageVecs * kRunThreads * 16 + 128;   // 53,248 B of staging slots + the long-row list
+
+// Long multi-run rows whose last run this CTA summed: all threads copy a block of consecutive run sums (they are
+// contiguous in the partial buffer) into the staging memory, then the first lpr lanes of warp 0 add them in order.
+// The fp32 add chain of a row is serial by definition; the copies are not, and 256 threads keep 52 KB in flight.
+// Sum of the `nr` consecutive run sums at p, in order from +0, for column threadIdx.x (threads < lpr; others return 0).
+// Called by every thread of the CTA.
+__device__ __noinline__ float4 sum_long_row(const float* p, uint32_t nr, int D, int lpr, float4* stage) {
+  const int chunk_rows = kRunStageVecs * kRunThreads / lpr;
+  float4 tot = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (uint32_t c0 = 0; c0 < nr; c0 += chunk_rows) {
+    const int cnt = (int)min((uint32_t)chunk_rows, nr - c0);
+    const float* src = p + (int64_t)c0 * D;
+    for (int idx = threadIdx.x; idx < cnt * lpr; idx += kRunThreads) cp_async16(stage + idx, src + (int64_t)idx * 4);
+    cp_async_commit(); cp_async_wait<0>();
+    __syncthreads();
+    if ((int)threadIdx.x < lpr) {
+      const float4* q = stage + threadIdx.x;
+      int r = 0;
+      for (; r + 8 <= cnt; r += 8) {
+        float4 x[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[e] = q[(r + e) * lpr];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) tot = add4(tot, x[e]);
+      }
+      for (; r < cnt; ++r) tot = add4(tot, q[r * lpr]);
+    }
+    __syncthreads();
+  }
+  return tot;
+}
+
+template <bool FUSED>
+__device__ __forceinline__ void finish_long_rows(const ReduceArgs& a, float4* stage, const uint32_t* s_long, const uint32_t* s_nlong) {
+  __syncthreads();                                   // every thread is past its last item; the list is complete
+  const uint32_t n_long = min(*s_nlong, (uint32_t)kLongCap);
+  if (n_long == 0) return;
+  __threadfence();                                   // acquire side of the rows' completion counts
+  for (uint32_t w = 0; w < n_long; ++w) {
+    const uint4 info = __ldcg(a.mrow_info + s_long[w]);   // {row, runs, first run sum, count}
+    const float4 tot = sum_long_row(a.partial + (int64_t)info.z * a.D, info.y, a.D, a.lpr, stage);
+    if ((int)threadIdx.x < a.lpr) finish_row<FUSED>(a, info.x, (int)threadIdx.x, tot);
+  }
+}
 
 // Every thread stages its own 16-byte pieces — up to 10 gradient rows and, for a single-run row, w, m, v — in shared
 // memory with cp.async: the bytes in flight no longer occupy registers, so four CTAs fit an SM and each thread keeps
@@ -225,7 +272,11 @@ constexpr int kRunSmemBytes = kRunStageVecs * kRunThreads * 16;         // 53,24
 template <bool FUSED, bool PREFETCH>
 __global__ void __launch_bounds__(kRunThreads)
 srm2_segment_runsum_kernel(ReduceArgs a) {
-  extern __shared__ float4 stage[];                 // [kRunStageVecs][kRunThreads]
+  extern __shared__ __align__(128) float4 stage[];                 // [kRunStageVecs][kRunThreads]
+  uint32_t* s_long = reinterpret_cast<uint32_t*>(stage + kRunStageVecs * kRunThreads);   // behind the staging slots, so
+  uint32_t& s_nlong = s_long[kLongCap];                                                  // that those stay 128-byte aligned
+  if (threadIdx.x == 0) s_nlong = 0;
+  __syncthreads();
   float4* mine = stage + threadIdx.x;
   const int64_t items = (int64_t)a.counters->n_runs * a.lpr;
   const int lane = threadIdx.x & 31;
@@ -294,7 +345,13 @@ srm2_segment_runsum_kernel(ReduceArgs a) {
     }
     info.x = __shfl_sync(gmask, info.x, gleader); info.y = __shfl_sync(gmask, info.y, gleader);
     info.z = __shfl_sync(gmask, info.z, gleader); info.w = __shfl_sync(gmask, info.w, gleader);
-    if (info.w != info.y - 1u || info.y > (uint32_t)kInplaceMaxRuns) continue;   // not the last run to finish, or a long row
+    if (info.w != info.y - 1u) continue;               // not the last run of the row to finish
+    if (info.y > (uint32_t)kInplaceMaxRuns) {          // a long row: left to the whole CTA, after its last item
+      uint32_t slot = 0;
+      if (lane == gleader) slot = atomicAdd(&s_nlong, 1u);
+      slot = __shfl_sync(gmask, slot, gleader);
+      if (slot < (uint32_t)kLongCap) { if (lane == gleader) s_long[slot] = d.w; continue; }
+    }
     __threadfence();
     // the group that completes a row adds its run sums in order, staging kRun of them at a time the same way
     const float* p = a.partial + (int64_t)info.z * a.D + j4 * 4;
@@ -311,6 +368,7 @@ srm2_segment_runsum_kernel(ReduceArgs a) {
     }
     finish_row<FUSED>(a, info.x, j4, tot);
   }
+  if (a.inplace) finish_long_rows<FUSED>(a, stage, s_long, &s_nlong);
 }
 
 // The same kernel for rows of 16 or 32 lanes (D = 64 or 128), where a run's lane group is an aligned half or whole warp
@@ -323,7 +381,11 @@ srm2_segment_runsum_kernel(ReduceArgs a) {
 template <bool FUSED>
 __global__ void __launch_bounds__(kRunThreads)
 srm2_segment_runsum_wide_kernel(ReduceArgs a) {
-  extern __shared__ float4 stage[];                 // [kRunStageVecs][kRunThreads]
+  extern __shared__ __align__(128) float4 stage[];                 // [kRunStageVecs][kRunThreads]
+  uint32_t* s_long = reinterpret_cast<uint32_t*>(stage + kRunStageVecs * kRunThreads);   // behind the staging slots, so
+  uint32_t& s_nlong = s_long[kLongCap];                                                  // that those stay 128-byte aligned
+  if (threadIdx.x == 0) s_nlong = 0;
+  __syncthreads();
   float4* mine = stage + threadIdx.x;
   const int64_t items = (int64_t)a.counters->n_runs * a.lpr;
   const int lane = threadIdx.x & 31;
@@ -397,6 +459,12 @@ srm2_segment_runsum_wide_kernel(ReduceArgs a) {
     info.x = __shfl_sync(gmask, info.x, gleader); info.y = __shfl_sync(gmask, info.y, gleader);
     info.z = __shfl_sync(gmask, info.z, gleader); info.w = __shfl_sync(gmask, info.w, gleader);
     if (info.w != info.y - 1u) continue;               // not the last run of the row to finish
+    if (info.y > (uint32_t)kInplaceMaxRuns) {          // a long row: left to the whole CTA, after its last item
+      uint32_t slot = 0;
+      if (lane == gleader) slot = atomicAdd(&s_nlong, 1u);
+      slot = __shfl_sync(gmask, slot, gleader);
+      if (slot < (uint32_t)kLongCap) { if (lane == gleader) s_long[slot] = d.w; continue; }
+    }
     __threadfence();
     const float* p = a.partial + (int64_t)info.z * a.D + j4 * 4;
     float4 tot = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -408,6 +476,7 @@ srm2_segment_runsum_wide_kernel(ReduceArgs a) {
     }
     finish_row<FUSED>(a, info.x, j4, tot);
   }
+  if (a.inplace) finish_long_rows<FUSED>(a, stage, s_long, &s_nlong);
 }
 
 // ------------------------------------------------------------------------------------------ multi-run rows
@@ -448,7 +517,7 @@ __device__ __forceinline__ void add_staged(float4 (&tot)[kMaxColsPerLane], const
 template <bool FUSED>
 __global__ void __launch_bounds__(kFinalThreads)
 srm2_segment_final_kernel(ReduceArgs a, int short_rows, int chunk_rows) {
-  extern __shared__ float4 smf[];                  // kFinalSmemBytes
+  extern __shared__ __align__(128) float4 smf[];                  // kFinalSmemBytes
   __shared__ uint32_t s_j[kFinalWarps], s_nr[kFinalWarps], s_pb[kFinalWarps];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float4* mine = smf + (size_t)warp * short_rows * a.lpr;
@@ -461,7 +530,6 @@ srm2_segment_final_kernel(ReduceArgs a, int short_rows, int chunk_rows) {
       nr = (a.seg_end[j] - a.seg_start[j] + kRun - 1) / kRun;
       pb = a.bpre_m[j / kPlanThreads] + a.mrun_off[j];
     }
-    if (a.inplace && nr <= (uint32_t)kInplaceMaxRuns) nr = 0;      // finished inside the run-sum kernel
     if (lane == 0) { s_j[warp] = j; s_nr[warp] = nr; s_pb[warp] = pb; }
     if (nr > 0 && nr <= (uint32_t)short_rows) {
       const float* p = a.partial + (int64_t)pb * a.D;

@@ -60,7 +60,7 @@ def test_unique_inverse_edges(dev):
 
 # ---------------------------------------------------------------------------------------- segment-reduce
 CASES = [(1, 16, 1), (33, 16, 3), (100, 128, 7), (1000, 4, 40), (3072, 16, 40), (3072, 24, 3), (3073, 16, 900), (3073, 16, 3), (5000, 64, 40),
-         (20000, 128, 600), (70000, 16, 5000), (212992, 128, 50000), (9000, 8, 1)]
+         (20000, 128, 600), (70000, 16, 5000), (212992, 128, 50000), (9000, 8, 1), (200000, 64, 30), (120000, 128, 9)]
 
 
 @pytest.mark.parametrize('n,D,nk', CASES)
