@@ -147,7 +147,7 @@ def config_dict(a, world, total_rows):
     name = ('dlrm_sparse_step: 26 fp32 tables, d=128, 33.8M rows, batch 8192x26 Zipf(1.1) lookups, dedup+segment-reduce+Adam'
             if world == 1 and a.rows == 33_800_000 else
             f'row-sharded sparse step: 26 fp32 tables, d=128, {total_rows / 1e6:.1f}M rows by row_id mod {world}, '
-            f'global batch {a.batch * world}x26 Zipf(1.1) lookups, NCCL all-to-all routing')
+            f'global batch {a.batch * world}x26 Zipf(1.1) lookups')
     return {'workload': name, 'rows_total': int(total_rows), 'rows_per_gpu': int(a.rows), 'lookups_per_step': int(a.batch * N_TABLES * world),
             'd': D, 'tables': N_TABLES, 'hyper': {'lr': HYP[0], 'b1': HYP[1], 'b2': HYP[2], 'eps': HYP[3]},
             'parallelism': f'row-shard x{world}' if world > 1 else 'single GPU',
@@ -170,13 +170,19 @@ def run_ours(a, world, rank, local_rank):
     bound = float(np.sqrt(1.0 / sizes.max()))
     eng = ShardedSparseAdam(total_rows, D, world, rank, dev, seed=SEED, bound=bound, hyper=HYP,
                             max_lookups_per_rank=n, group=dist.group.WORLD if world > 1 else None)
-    p2p = eng.enable_p2p(n) if world > 1 else False
+    p2p = eng.enable_p2p(n, pull=(a.exchange == 'pull'), grad_slots=4) if world > 1 and a.exchange != 'nccl' else False
+    pull = bool(p2p) and a.exchange == 'pull'
     nsteps = a.warmup + a.steps
     ids_np = [step_ids(sizes, offs, a.batch, world, rank, s + 1) for s in range(nsteps)]
     ids_dev = [torch.from_numpy(x).to(dev) for x in ids_np]
     gen = torch.Generator(device=dev).manual_seed(SEED + rank)
     NBUF = 4
-    grads_dev = [torch.randn(n, D, device=dev, generator=gen) * 1e-3 for _ in range(NBUF)]
+    if pull:       # the gradients are produced straight into the peer-visible slots the owners read from
+        grads_dev = [eng.grad_slot(b)[:n] for b in range(NBUF)]
+        for g in grads_dev:
+            g.copy_(torch.randn(n, D, device=dev, generator=gen) * 1e-3)
+    else:
+        grads_dev = [torch.randn(n, D, device=dev, generator=gen) * 1e-3 for _ in range(NBUF)]
 
     def barrier():
         if world > 1:
@@ -184,11 +190,11 @@ def run_ours(a, world, rank, local_rank):
         torch.cuda.synchronize(dev)
 
     # ---- device-resident timing (value) ----
-    if world == 1:
+    if world == 1 and a.no_pipeline:
         for s in range(a.warmup):
             eng.step(ids_dev[s], grads_dev[s % NBUF], s + 1)
     else:
-        eng.run_steps([(ids_dev[s], grads_dev[s % NBUF]) for s in range(a.warmup)], 1)
+        eng.run_steps([(ids_dev[s], grads_dev[k % NBUF]) for k, s in enumerate(range(a.warmup))], 1)
     ev_pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(a.steps)]
     for e0, e1 in ev_pairs:
         e0.record(); e1.record()              # materialise the handles
@@ -197,23 +203,28 @@ def run_ours(a, world, rank, local_rank):
     sampler = ClockSampler(local_rank) if rank == 0 else None
     t_begin = torch.cuda.Event(enable_timing=True); t_end = torch.cuda.Event(enable_timing=True)
     counts = []
+    t_host0 = time.perf_counter()
     t_begin.record()
-    if world == 1:
+    if world == 1 and a.no_pipeline:
         for k, s in enumerate(range(a.warmup, nsteps)):
             L.srm2_stage_events(ev_pairs[k][0].cuda_event, ev_pairs[k][1].cuda_event)
             counts.append(eng.step(ids_dev[s], grads_dev[s % NBUF], s + 1))
         L.srm2_stage_events(None, None)
     else:
-        # routing + all-to-all of step s+1 overlap the shard update of step s (inputs are known ahead, as in a training loop)
-        counts = eng.run_steps([(ids_dev[s], grads_dev[s % NBUF]) for s in range(a.warmup, nsteps)], a.warmup + 1)
+        # the lookup ids are known ahead (as in a training loop that prefetches its batches): everything that depends on
+        # the ids only — routing and the exchange of names (N > 1), dedup, sort and run descriptors — runs one step ahead on
+        # side streams while the kernels that stream the gradient rows update the table on the main stream
+        counts = eng.run_steps([(ids_dev[s], grads_dev[k % NBUF]) for k, s in enumerate(range(a.warmup, nsteps))], a.warmup + 1,
+                               stage_events=ev_pairs if (world == 1 or pull) else None)
     t_end.record()
+    host_enqueue_us = (time.perf_counter() - t_host0) * 1e6 / a.steps
     barrier()
     ms = t_begin.elapsed_time(t_end)
     launches = L.srm2_launch_count() - launches0
     clocks = sampler.stop() if sampler else None
     rows_local = int(sum(int(c[0]) for c in counts))
     lookups_local = eng.last_local_lookups_total
-    if world > 1:      # stage timing of the shard update alone, on a few extra steps outside the timed region
+    if world > 1 and not pull:      # stage timing of the shard update alone, on a few extra steps outside the timed region
         for k in range(min(a.steps, 5)):
             L.srm2_stage_events(ev_pairs[k][0].cuda_event, ev_pairs[k][1].cuda_event)
             eng.step(ids_dev[a.warmup + k], grads_dev[k % NBUF], nsteps + 100 + k)
@@ -282,9 +293,13 @@ def run_ours(a, world, rank, local_rank):
            'e2e': {'value': e_rows_all / (e_ms * 1e-3), 'unit': 'rows/s', 'h2d_bytes_per_step': int(n * 8 + n * D * 4) * world,
                    'd2h_bytes_per_step': 16 * world, 'steps': e2e_steps},
            'gpu_launches': int(launches_all), 'clocks': clocks,
-           'rows_updated_per_step': rows / a.steps, 'lookups_per_step_per_gpu': n}
+           'rows_updated_per_step': rows / a.steps, 'lookups_per_step_per_gpu': n, 'host_enqueue_us_per_step': host_enqueue_us}
+    out['config']['pipeline'] = ('none: one call after another on one stream' if (world == 1 and a.no_pipeline) else
+                                 'ids known one step ahead: dedup, sort and run descriptors of step s+1 run on a side stream while the run-sum + Adam '
+                                 'kernel of step s streams the gradient rows')
     if world > 1:
-        out['config']['exchange'] = 'fused routing kernel: peer stores over NVLink' if p2p else 'NCCL all-to-all'
+        out['config']['exchange'] = ('pull: lookup names by peer stores, gradient rows read from their source rank by the fused reduce+Adam kernel (NVLink)'
+                                     if pull else 'fused routing kernel: peer stores over NVLink' if p2p else 'NCCL all-to-all')
     return out
 
 
@@ -448,6 +463,9 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--rows', type=int, default=0, help='rows per GPU (default: 33.8M at 1 GPU, 25M per GPU above)')
     ap.add_argument('--batch', type=int, default=8192, help='samples per GPU per step (x26 lookups)')
+    ap.add_argument('--exchange', default='pull', choices=['pull', 'push', 'nccl'],
+                    help='N > 1: how routed lookups reach their owner (pull = rows read over NVLink by the reduce kernel)')
+    ap.add_argument('--no-pipeline', action='store_true', help='N = 1: one step after the other on one stream (no look-ahead on the ids)')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-kernels', action='store_true', help='skip the per-kernel figures (N = 1 only)')
     a = ap.parse_args()

@@ -42,6 +42,11 @@ SIGNATURES = {
     'srm2_route_dispatch': (C.c_int, [_vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _i32, _vp, _sz, _vp]),
     'srm2_unique_inverse_nd_i64': (C.c_int, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _sz, _vp]),
     'srm2_reduce_adam_nd_f32': (C.c_int, [_vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _vp, _i64, _i32, _f8, _vp, _sz, _vp]),
+    'srm2_reduce_adam_index': (C.c_int, [_vp, _vp, _vp, _i64, _vp, _i64, _i64, _vp, _i64, _vp, _sz, _vp]),
+    'srm2_reduce_adam_apply_f32': (C.c_int, [_vp, _vp, _vp, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _f8, _vp, _sz, _vp]),
+    'srm2_peer_barrier': (C.c_int, [_vp, _i64, _i64, C.c_uint64, _vp, _i64, _vp]),
+    'srm2_route_dispatch_ids': (C.c_int, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _sz, _vp]),
+    'srm2_reduce_adam_pull_f32': (C.c_int, [_vp, _vp, _vp, _i64, _vp, _vp, _i64, _vp, _i64, _i64, _vp, _i64, _f8, _vp, _sz, _vp]),
 }
 
 _lib = None

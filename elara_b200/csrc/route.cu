@@ -305,6 +305,72 @@ srm2_route_dispatch_tma_kernel(const int64_t* __restrict__ ids, const float* __r
   bulk_wait_all();
 }
 
+// ---- pull mode: only the names of the lookups travel ------------------------------------------------------------------
+// One thread per routed lookup stores, into the owner's receive buffers at the same offsets as above, the local row id
+// (8 bytes) and the code (rank << 24) | position that tells the owner where the gradient row lies.  The rows stay where
+// they were produced; the owner's run-sum kernel reads them from there.
+__global__ void __launch_bounds__(256)
+srm2_route_dispatch_ids_kernel(const int64_t* __restrict__ ids, const uint32_t* __restrict__ perm, const uint32_t* __restrict__ owner_sorted,
+                               int64_t n, int world, int rank, const int64_t* __restrict__ cmat, PeerPtrs lid_peers, PeerPtrs src_peers,
+                               int64_t cap, int64_t* __restrict__ n_recv, uint32_t* __restrict__ err) {
+  __shared__ int64_t s_start[kMaxPeers], s_base[kMaxPeers];
+  if (threadIdx.x < world) {
+    const int d = threadIdx.x;
+    int64_t start = 0, base = 0;
+    for (int e = 0; e < d; ++e) start += cmat[rank * world + e];
+    for (int q = 0; q < rank; ++q) base += cmat[q * world + d];
+    s_start[d] = start; s_base[d] = base;
+    if (blockIdx.x == 0 && d == rank) {
+      int64_t tot = 0;
+      for (int q = 0; q < world; ++q) tot += cmat[q * world + rank];
+      *n_recv = tot;
+      if (tot > cap) atomicOr(err, 1u);
+    }
+  }
+  __syncthreads();
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (int64_t)gridDim.x * 256) {
+    const uint32_t d = owner_sorted[i];
+    if (d >= (uint32_t)world) continue;
+    const int64_t r = s_base[d] + (i - s_start[d]);
+    if (r >= cap) { atomicOr(err, 1u); continue; }
+    const uint32_t p = perm[i];
+    const int64_t id = ids[p];
+    static_cast<int64_t*>(lid_peers.p[d])[r] = id < 0 ? -1 : id / world;
+    static_cast<uint32_t*>(src_peers.p[d])[r] = ((uint32_t)rank << 24) | p;
+  }
+}
+
+// ---- barrier across the ranks' GPUs ------------------------------------------------------------------------------------
+// Every rank owns an array of kMaxPeers 64-bit tickets in peer-visible memory.  Thread r of the one-warp kernel stores
+// this barrier's ticket into entry `rank` of rank r's array (release, system scope: everything this stream wrote to peer
+// memory before the kernel is visible to whoever reads the ticket), then polls entry r of its own array until rank r's
+// ticket has arrived (acquire).  Tickets only grow, so the arrays need no reset.  The wait is bounded by a time limit
+// (and an iteration limit behind it): when it runs out the kernel sets bit 1 of *err and returns, so a rank that never
+// arrives costs the others the time limit, never the GPU.
+__global__ void srm2_peer_barrier_kernel(PeerPtrs sig, int rank, int world, unsigned long long ticket, uint32_t* __restrict__ err,
+                                         long long timeout_ns) {
+  const int r = threadIdx.x;
+  if (r >= world) return;
+  unsigned long long* dst = static_cast<unsigned long long*>(sig.p[r]) + rank;
+  __threadfence_system();
+  asm volatile("st.release.sys.global.u64 [%0], %1;\n" ::"l"(dst), "l"(ticket) : "memory");
+  const unsigned long long* src = static_cast<const unsigned long long*>(sig.p[rank]) + r;
+  long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t0));
+  for (uint32_t it = 0; it < (1u << 27); ++it) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];\n" : "=l"(v) : "l"(src) : "memory");
+    if (v >= ticket) return;
+    if ((it & 15u) == 15u) {
+      long long t1;
+      asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t1));
+      if (t1 - t0 > timeout_ns) break;
+    }
+    __nanosleep(40);
+  }
+  atomicOr(err, 2u);
+}
+
 }  // namespace srm2
 
 extern "C" int srm2_route_plan(const int64_t* ids, int64_t n, int64_t world, int64_t* out_counts, void* scratch,
@@ -373,5 +439,41 @@ extern "C" int srm2_route_dispatch(const int64_t* ids, const float* grad, int64_
   }
   srm2_route_dispatch_kernel<<<grid, 256, 0, st>>>(ids, grad, sb.valA, sb.keyA, n, lpr, shift, (int)D, (int)world, (int)rank, cmat, pl, pg,
                                                   cap, n_recv, err);
+  return launch_status(1);
+}
+
+extern "C" int srm2_route_dispatch_ids(const int64_t* ids, int64_t n, int64_t world, int64_t rank, const int64_t* cmat,
+                                       void* const* peer_lid, void* const* peer_src, int64_t cap, int64_t* n_recv, uint32_t* err,
+                                       void* scratch, size_t scratch_bytes, srm2_stream_t stream) {
+  using namespace srm2;
+  if (n < 0 || world < 1 || world > kMaxPeers || rank < 0 || rank >= world || cap < 0) return SRM2_ERR_ARG;
+  if (cmat == nullptr || peer_lid == nullptr || peer_src == nullptr || n_recv == nullptr || err == nullptr) return SRM2_ERR_ARG;
+  if (n > 0 && ids == nullptr) return SRM2_ERR_ARG;
+  if (n >= ((int64_t)1 << 24)) return SRM2_ERR_UNSUPPORTED;          // the position field of the code
+  if (scratch == nullptr || !aligned16(scratch) || scratch_bytes < route_layout(n, world, nullptr, nullptr)) return SRM2_ERR_SCRATCH;
+  PeerPtrs pl{}, ps{};
+  for (int r = 0; r < world; ++r) {
+    if (peer_lid[r] == nullptr || peer_src[r] == nullptr) return SRM2_ERR_ARG;
+    pl.p[r] = peer_lid[r]; ps.p[r] = peer_src[r];
+  }
+  SortBuffers sb;
+  route_layout(n, world, static_cast<char*>(scratch), &sb);     // keyA / valA hold the owners and the permutation of srm2_route_plan
+  int grid = (int)((n + 255) / 256 < (int64_t)kSMs * 4 ? (n + 255) / 256 : (int64_t)kSMs * 4);
+  if (grid < 1) grid = 1;
+  srm2_route_dispatch_ids_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(ids, sb.valA, sb.keyA, n, (int)world, (int)rank, cmat, pl, ps, cap,
+                                                                                     n_recv, err);
+  return launch_status(1);
+}
+
+extern "C" int srm2_peer_barrier(void* const* peer_tickets, int64_t rank, int64_t world, uint64_t ticket, uint32_t* err, int64_t timeout_ns,
+                                 srm2_stream_t stream) {
+  using namespace srm2;
+  if (peer_tickets == nullptr || err == nullptr || world < 1 || world > kMaxPeers || rank < 0 || rank >= world || timeout_ns <= 0) return SRM2_ERR_ARG;
+  PeerPtrs pp{};
+  for (int r = 0; r < world; ++r) {
+    if (peer_tickets[r] == nullptr || (reinterpret_cast<uintptr_t>(peer_tickets[r]) & 7u) != 0) return SRM2_ERR_ARG;
+    pp.p[r] = peer_tickets[r];
+  }
+  srm2_peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pp, (int)rank, (int)world, (unsigned long long)ticket, err, (long long)timeout_ns);
   return launch_status(1);
 }

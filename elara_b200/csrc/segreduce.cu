@@ -33,6 +33,8 @@ constexpr int kWindow = 32;
 constexpr int kPlanThreads = 256;
 
 struct SegCounters { uint32_t n_runs, n_mrows, n_mruns, done; };
+constexpr int kMaxGradPeers = 16;
+constexpr int kPeerShift = 24;      // pull mode: a lookup is named by (source rank << 24) | row in that rank's gradient buffer
 
 struct ReduceArgs {
   const float* grad; int D; int lpr; int shift;
@@ -43,6 +45,7 @@ struct ReduceArgs {
   float* out;                                     // [nu, D] (unfused) or nullptr
   float* pool; const int64_t* slots; AdamSc sc;   // fused Adam: pool [C,3,D], slots[j] = pool row of unique row j
   int64_t nu_host; const int64_t* nu_dev; int64_t cap; int64_t n;
+  const float* peer[kMaxGradPeers];               // pull mode: gradient buffers of all ranks (peer pointers), see grad_row
 };
 
 __device__ __forceinline__ int64_t load_nu(int64_t nu_host, const int64_t* nu_dev, int64_t cap) {
@@ -52,6 +55,14 @@ __device__ __forceinline__ int64_t load_nu(int64_t nu_host, const int64_t* nu_de
 
 __device__ __forceinline__ float4 add4(const float4& a, const float4& b) {
   return make_float4(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y), __fadd_rn(a.z, b.z), __fadd_rn(a.w, b.w));
+}
+
+// Address of a lookup's gradient row.  Local mode: `code` is the row of a.grad.  Pull mode: the row lives in the buffer
+// of the rank that produced it and is read from there (peer memory over NVLink, plain 16-byte asynchronous copies).
+template <bool PEER>
+__device__ __forceinline__ const float* grad_row(const ReduceArgs& a, uint32_t code) {
+  if (PEER) return a.peer[code >> kPeerShift] + (int64_t)(code & ((1u << kPeerShift) - 1u)) * a.D;
+  return a.grad + (int64_t)code * a.D;
 }
 
 // Writes the finished gradient sum of unique row j (lane j4): either into out, or through Adam into the pool.
@@ -91,7 +102,7 @@ template <bool FUSED>
 __global__ void __launch_bounds__(kPlanThreads)
 srm2_segment_plan_kernel(ReduceArgs a, uint32_t* __restrict__ run_off, uint32_t* __restrict__ mrun_off,
                          uint32_t* __restrict__ mrow_off, uint32_t* __restrict__ bsum_r, uint32_t* __restrict__ bsum_m,
-                         uint32_t* __restrict__ bsum_f, SegCounters* __restrict__ counters, int nblocks, int small) {
+                         uint32_t* __restrict__ bsum_f, SegCounters* __restrict__ counters, int nblocks, int skip_empty) {
   __shared__ uint64_t ws[33];
   __shared__ bool last;
   const int64_t nu = load_nu(a.nu_host, a.nu_dev, a.cap);
@@ -100,10 +111,9 @@ srm2_segment_plan_kernel(ReduceArgs a, uint32_t* __restrict__ run_off, uint32_t*
   if (j < nu) {
     const uint32_t len = a.seg_end[j] - a.seg_start[j];
     r = (len + kRun - 1) / kRun; f = r > 1; m = f ? r : 0u;
-    if (len == 0 && !small)
+    if (len == 0 && !skip_empty)
       for (int j4 = 0; j4 < a.lpr; ++j4) finish_row<FUSED>(a, (uint32_t)j, j4, make_float4(0.f, 0.f, 0.f, 0.f));
   }
-  if (small) return;                               // the windowed order needs no runs
   // the three counters scan as one packed word: runs | runs of multi-run rows | multi-run rows (21 bits each; the host
   // side rejects inputs whose totals would not fit)
   uint64_t tot;
@@ -149,7 +159,8 @@ srm2_segment_descr_kernel(const uint32_t* __restrict__ skey, const uint32_t* __r
                           const uint32_t* __restrict__ mrun_off, const uint32_t* __restrict__ mrow_off,
                           const uint32_t* __restrict__ bpre_r, const uint32_t* __restrict__ bpre_m,
                           const uint32_t* __restrict__ bpre_f, const SegCounters* __restrict__ counters,
-                          const int64_t* __restrict__ slots, uint4* __restrict__ run_desc, uint32_t* __restrict__ run_pos,
+                          const int64_t* __restrict__ slots, const uint32_t* __restrict__ src_code,
+                          uint4* __restrict__ run_desc, uint32_t* __restrict__ run_pos,
                           uint32_t* __restrict__ mrows, uint4* __restrict__ mrow_info, int64_t nu_host,
                           const int64_t* __restrict__ nu_dev, int64_t cap) {
   const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
@@ -162,16 +173,18 @@ srm2_segment_descr_kernel(const uint32_t* __restrict__ skey, const uint32_t* __r
   const uint32_t blk = j / kPlanThreads, ri = off / kRun, rq = off - ri * kRun;
   const uint32_t rbase = bpre_r[blk] + run_off[j], mbase = bpre_m[blk] + mrun_off[j];
   const uint32_t c = multi ? mbase + ri : counters->n_mruns + (rbase - mbase);
-  run_pos[(int64_t)c * kRun + rq] = spos[i];             // positions of run c, padded to kRun per run
+  // what names the lookup's gradient row from here on: its position, or in pull mode its (rank, row) code
+  const uint32_t code = src_code ? src_code[spos[i]] : spos[i];
+  run_pos[(int64_t)c * kRun + rq] = code;                // rows of run c, padded to kRun per run
   if (rq != 0) return;
   const uint32_t len = min((uint32_t)kRun, e - (uint32_t)i);
   if (multi) {
     const uint32_t mi = bpre_f[blk] + mrow_off[j];
-    run_desc[c] = make_uint4(len == 1 ? spos[i] : (uint32_t)i, len | kMultiBit, c, mi);
+    run_desc[c] = make_uint4(len == 1 ? code : (uint32_t)i, len | kMultiBit, c, mi);
     if (off == 0) { mrows[mi] = j; mrow_info[mi] = make_uint4(j, (e - s + kRun - 1) / kRun, mbase, 0u); }
   } else {
     const uint64_t target = slots ? (uint64_t)slots[j] : (uint64_t)j;
-    run_desc[c] = make_uint4(len == 1 ? spos[i] : (uint32_t)i, len, (uint32_t)target, (uint32_t)(target >> 32));
+    run_desc[c] = make_uint4(len == 1 ? code : (uint32_t)i, len, (uint32_t)target, (uint32_t)(target >> 32));
   }
 }
 
@@ -269,7 +282,7 @@ __device__ __forceinline__ void finish_long_rows(const ReduceArgs& a, float4* st
 // Every thread stages its own 16-byte pieces — up to 10 gradient rows and, for a single-run row, w, m, v — in shared
 // memory with cp.async: the bytes in flight no longer occupy registers, so four CTAs fit an SM and each thread keeps
 // up to 208 B outstanding.  A thread only reads back what it copied itself: cp.async.wait_group is the only wait.
-template <bool FUSED, bool PREFETCH>
+template <bool FUSED, bool PREFETCH, bool PEER>
 __global__ void __launch_bounds__(kRunThreads)
 srm2_segment_runsum_kernel(ReduceArgs a) {
   extern __shared__ __align__(128) float4 stage[];                 // [kRunStageVecs][kRunThreads]
@@ -311,7 +324,7 @@ srm2_segment_runsum_kernel(ReduceArgs a) {
 #pragma unroll
     for (int q = 0; q < kRun; ++q) {
       const uint32_t pos = (q & 1) ? cur.p[q / 2].y : cur.p[q / 2].x;
-      if (q < len) cp_async16(mine + q * kRunThreads, a.grad + (int64_t)pos * a.D + j4 * 4);
+      if (q < len) cp_async16(mine + q * kRunThreads, grad_row<PEER>(a, pos) + j4 * 4);
     }
     cp_async_commit();
     if (PREFETCH && t + stride < items) { int64_t cn; int jn; split(t + stride, cn, jn); load_item(a, cn, nxt); }
@@ -378,7 +391,7 @@ srm2_segment_runsum_kernel(ReduceArgs a) {
 //  - a run of a single lookup carries its position in the descriptor and needs no position load at all;
 //  - the copy and add loops run `len` times (len is uniform over the group) instead of ten predicated times;
 //  - descriptors are fetched two items ahead and positions one item ahead, so neither is waited for.
-template <bool FUSED>
+template <bool FUSED, bool PEER>
 __global__ void __launch_bounds__(kRunThreads)
 srm2_segment_runsum_wide_kernel(ReduceArgs a) {
   extern __shared__ __align__(128) float4 stage[];                 // [kRunStageVecs][kRunThreads]
@@ -422,11 +435,11 @@ srm2_segment_runsum_wide_kernel(ReduceArgs a) {
       }
     }
     if (len == 1) {
-      cp_async16(mine, a.grad + (int64_t)d.x * a.D + j4 * 4);
+      cp_async16(mine, grad_row<PEER>(a, d.x) + j4 * 4);
     } else {
       for (int q = 0; q < len; ++q) {
         const uint32_t pos = __shfl_sync(gmask, p0, gleader + q);
-        cp_async16(mine + q * kRunThreads, a.grad + (int64_t)pos * a.D + j4 * 4);
+        cp_async16(mine + q * kRunThreads, grad_row<PEER>(a, pos) + j4 * 4);
       }
     }
     cp_async_commit();
@@ -641,17 +654,48 @@ static size_t seg_layout(int64_t n, int64_t cap, int64_t D, char* base, SegScrat
   return off;
 }
 
+// Launch of the run-sum kernel that fits the row width.
+template <bool FUSED, bool PEER>
+static int launch_runsum(const ReduceArgs& a, bool wide, int grid, cudaStream_t st) {
+  if (wide) {
+    if (note_cuda(cudaFuncSetAttribute(srm2_segment_runsum_wide_kernel<FUSED, PEER>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRunSmemBytes))) return SRM2_ERR_CUDA;
+    srm2_segment_runsum_wide_kernel<FUSED, PEER><<<grid, kRunThreads, kRunSmemBytes, st>>>(a);
+  } else {
+    if (note_cuda(cudaFuncSetAttribute(srm2_segment_runsum_kernel<FUSED, kRunPrefetch, PEER>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRunSmemBytes))) return SRM2_ERR_CUDA;
+    srm2_segment_runsum_kernel<FUSED, kRunPrefetch, PEER><<<grid, kRunThreads, kRunSmemBytes, st>>>(a);
+  }
+  return SRM2_OK;
+}
+
+struct PullSource { const float* const* peer_grad; int world; const uint32_t* src_code; };   // pull mode (fused, runs order only)
+
+// phase: kIndexPhase = everything that depends on the lookups' row indices only (sort, boundaries, plan, descriptors);
+// kSumPhase = the kernels that read gradients and write rows.  The two halves of a split call communicate through the
+// scratch buffer alone, so they may run on different streams (ordered by an event), and the index half of the next
+// step may run while the sum half of this one is still streaming.
+constexpr int kIndexPhase = 1, kSumPhase = 2, kBothPhases = 3;
+
 static int segment_pipeline(bool fused, int order, const float* grad, const int64_t* inv, int64_t n, const int64_t* n_dev, int64_t D, int64_t nu_host,
                             const int64_t* nu_dev, int64_t cap, float* out, float* pool, const int64_t* slots,
-                            const float* sc, void* scratch, size_t scratch_bytes, cudaStream_t st) {
+                            const float* sc, void* scratch, size_t scratch_bytes, cudaStream_t st, const PullSource* pull = nullptr,
+                            int phase = kBothPhases) {
   if (n < 0 || D <= 0 || cap < 0 || (nu_host < 0 && nu_dev == nullptr) || order < 0 || order > 2) return SRM2_ERR_ARG;
   if (nu_dev == nullptr) cap = nu_host;
   if (cap == 0) return SRM2_OK;
-  if (n > 0 && (grad == nullptr || inv == nullptr)) return SRM2_ERR_ARG;
-  if (fused ? (pool == nullptr || slots == nullptr || sc == nullptr) : out == nullptr) return SRM2_ERR_ARG;
+  const bool index_phase = (phase & kIndexPhase) != 0, sum_phase = (phase & kSumPhase) != 0;
+  if (n > 0 && ((sum_phase && grad == nullptr && pull == nullptr) || (index_phase && inv == nullptr))) return SRM2_ERR_ARG;
+  if (phase != kBothPhases && (!fused || order != SRM2_ORDER_RUNS)) return SRM2_ERR_ARG;
+  if (pull) {
+    if (!fused || order != SRM2_ORDER_RUNS || pull->world < 1 || pull->world > kMaxGradPeers || (sum_phase && pull->peer_grad == nullptr) ||
+        (index_phase && pull->src_code == nullptr))
+      return SRM2_ERR_ARG;
+    for (int r = 0; sum_phase && r < pull->world; ++r)
+      if (pull->peer_grad[r] == nullptr || !aligned16(pull->peer_grad[r])) return SRM2_ERR_ARG;
+  }
+  if (fused ? (slots == nullptr || (sum_phase && (pool == nullptr || sc == nullptr))) : out == nullptr) return SRM2_ERR_ARG;
   // n < 2^21: the plan kernel scans three run counters packed into 21-bit fields of one word
   if ((D & 3) != 0 || D > 128 * kMaxColsPerLane || n >= ((int64_t)1 << 21) || cap >= ((int64_t)1 << 31)) return SRM2_ERR_UNSUPPORTED;
-  if ((n > 0 && !aligned16(grad)) || (fused ? !aligned16(pool) : !aligned16(out))) return SRM2_ERR_UNSUPPORTED;
+  if (sum_phase && ((n > 0 && !pull && !aligned16(grad)) || (fused ? !aligned16(pool) : !aligned16(out)))) return SRM2_ERR_UNSUPPORTED;
   if (scratch == nullptr || !aligned16(scratch) || scratch_bytes < seg_layout(n, cap, D, nullptr, nullptr)) return SRM2_ERR_SCRATCH;
   SegScratch s;
   seg_layout(n, cap, D, static_cast<char*>(scratch), &s);
@@ -661,10 +705,10 @@ static int segment_pipeline(bool fused, int order, const float* grad, const int6
   int launches = 0;
 
   // empty ranges for rows that no lookup names; counters (incl. the finished-CTA count) start at zero
-  if (note_cuda(cudaMemsetAsync(s.zero, 0, s.zero_bytes, st))) return SRM2_ERR_CUDA;
+  if (index_phase && note_cuda(cudaMemsetAsync(s.zero, 0, s.zero_bytes, st))) return SRM2_ERR_CUDA;
   // 1. sort (key = inv, value = position), 2. boundaries
   const uint32_t *skey = nullptr, *spos = nullptr;
-  if (n > 0) {
+  if (n > 0 && index_phase) {
     SortBuffers sb{s.keyA, s.valA, s.keyB, s.valB, s.hist, s.dtot, s.tiles};
     const uint32_t* hb = nullptr;
     const int rc = radix_sort_by_key(inv, n, n_dev, /*mod=*/0, cap, s.bits, s.passes, sb, &skey, &spos, &hb, &launches, st);
@@ -677,8 +721,9 @@ static int segment_pipeline(bool fused, int order, const float* grad, const int6
   a.run_desc = s.run_desc; a.run_pos = s.run_pos; a.mrows = s.mrows; a.mrow_info = s.mrow_info; a.counters = s.counters;
   a.inplace = (lpr <= 32 && (lpr & (lpr - 1)) == 0) ? 1 : 0; a.mrun_off = s.mrun_off; a.bpre_m = s.bsum_m; a.partial = s.partial;
   a.out = out; a.pool = pool; a.slots = slots;
-  if (fused) a.sc = AdamSc{sc[0], sc[1], sc[2], sc[3], sc[4], sc[5], sc[6], sc[7]};
+  if (fused && sum_phase) a.sc = AdamSc{sc[0], sc[1], sc[2], sc[3], sc[4], sc[5], sc[6], sc[7]};
   a.nu_host = nu_host; a.nu_dev = nu_dev; a.cap = cap; a.n = n;
+  if (pull && sum_phase) for (int r = 0; r < pull->world; ++r) a.peer[r] = pull->peer_grad[r];
   if (small) {
     const int64_t row_items = cap * lpr;
     const int grid_rows = (int)((row_items + 255) / 256 < (int64_t)kSMs * 16 ? (row_items + 255) / 256 : (int64_t)kSMs * 16);
@@ -688,20 +733,29 @@ static int segment_pipeline(bool fused, int order, const float* grad, const int6
     stage_end(st);
     return launch_status(launches + 1);
   }
-  // 3. plan, 4. descriptors
-  if (fused)
-    srm2_segment_plan_kernel<true><<<s.nblocks, kPlanThreads, 0, st>>>(a, s.run_off, s.mrun_off, s.mrow_off, s.bsum_r, s.bsum_m, s.bsum_f,
-                                                                      s.counters, s.nblocks, 0);
-  else
-    srm2_segment_plan_kernel<false><<<s.nblocks, kPlanThreads, 0, st>>>(a, s.run_off, s.mrun_off, s.mrow_off, s.bsum_r, s.bsum_m, s.bsum_f,
-                                                                       s.counters, s.nblocks, 0);
-  if (n > 0)
-    srm2_segment_descr_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(skey, spos, n, n_dev, s.seg_start, s.seg_end, s.run_off, s.mrun_off, s.mrow_off,
-                                                                          s.bsum_r, s.bsum_m, s.bsum_f, s.counters, fused ? slots : nullptr, s.run_desc, s.run_pos, s.mrows, s.mrow_info,
-                                                                          nu_host, nu_dev, cap);
+  // 3. plan, 4. descriptors.  A split call leaves rows without lookups alone (its index half must not write rows).
+  if (index_phase) {
+    const int skip_empty = phase != kBothPhases;
+    if (fused)
+      srm2_segment_plan_kernel<true><<<s.nblocks, kPlanThreads, 0, st>>>(a, s.run_off, s.mrun_off, s.mrow_off, s.bsum_r, s.bsum_m, s.bsum_f,
+                                                                        s.counters, s.nblocks, skip_empty);
+    else
+      srm2_segment_plan_kernel<false><<<s.nblocks, kPlanThreads, 0, st>>>(a, s.run_off, s.mrun_off, s.mrow_off, s.bsum_r, s.bsum_m, s.bsum_f,
+                                                                         s.counters, s.nblocks, skip_empty);
+    if (n > 0)
+      srm2_segment_descr_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(skey, spos, n, n_dev, s.seg_start, s.seg_end, s.run_off, s.mrun_off, s.mrow_off,
+                                                                            s.bsum_r, s.bsum_m, s.bsum_f, s.counters, fused ? slots : nullptr, pull ? pull->src_code : nullptr, s.run_desc, s.run_pos, s.mrows, s.mrow_info,
+                                                                            nu_host, nu_dev, cap);
+    launches += n > 0 ? 2 : 1;
+    if (!sum_phase) return launch_status(launches);
+  }
   // 5. run sums, 6. multi-run rows
   const int64_t run_items_max = n * lpr;
-  const int grid_runs = (int)((run_items_max + 255) / 256 < (int64_t)kSMs * 8 ? (run_items_max + 255) / 256 : (int64_t)kSMs * 8);
+  // One-call form: two waves of CTAs that loop over the runs.  Split form: the sum half shares the GPU with other streams'
+  // small kernels (the next steps' index work), so it is cut into many short-lived CTAs — SM room frees up every few
+  // microseconds and the block scheduler hands it to whichever stream has work.
+  const int64_t cta_cap = (int64_t)kSMs * (phase == kSumPhase ? 32 : 8);
+  const int grid_runs = (int)((run_items_max + 255) / 256 < cta_cap ? (run_items_max + 255) / 256 : cta_cap);
   const int rows_fit = (int)(kFinalSmemBytes / (D * 4));                 // run sums that fit the CTA's staging buffer
   const int short_rows = rows_fit / kFinalWarps, chunk_rows = rows_fit;
   const size_t sm_final = kFinalSmemBytes;
@@ -710,32 +764,22 @@ static int segment_pipeline(bool fused, int order, const float* grad, const int6
   const bool wide = (lpr == 16 || lpr == 32);            // a run's lanes are an aligned half or whole warp of >= kRun lanes
   stage_begin(st);
   if (n > 0) {
-    if (fused) {
-      if (sm_final > 48 * 1024 && note_cuda(cudaFuncSetAttribute(srm2_segment_final_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm_final)))
-        return SRM2_ERR_CUDA;
-      if (note_cuda(cudaFuncSetAttribute(srm2_segment_runsum_kernel<true, kRunPrefetch>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRunSmemBytes))) return SRM2_ERR_CUDA;
-      if (wide) {
-        if (note_cuda(cudaFuncSetAttribute(srm2_segment_runsum_wide_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRunSmemBytes))) return SRM2_ERR_CUDA;
-        srm2_segment_runsum_wide_kernel<true><<<grid_runs, kRunThreads, kRunSmemBytes, st>>>(a);
+    int rc;
+    if (fused) rc = pull ? launch_runsum<true, true>(a, wide, grid_runs, st) : launch_runsum<true, false>(a, wide, grid_runs, st);
+    else rc = launch_runsum<false, false>(a, wide, grid_runs, st);
+    if (rc != SRM2_OK) return rc;
+    if (!a.inplace) {
+      if (fused) {
+        if (note_cuda(cudaFuncSetAttribute(srm2_segment_final_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm_final))) return SRM2_ERR_CUDA;
+        srm2_segment_final_kernel<true><<<grid_final, kFinalThreads, sm_final, st>>>(a, short_rows, chunk_rows);
       } else {
-        srm2_segment_runsum_kernel<true, kRunPrefetch><<<grid_runs, kRunThreads, kRunSmemBytes, st>>>(a);
+        if (note_cuda(cudaFuncSetAttribute(srm2_segment_final_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm_final))) return SRM2_ERR_CUDA;
+        srm2_segment_final_kernel<false><<<grid_final, kFinalThreads, sm_final, st>>>(a, short_rows, chunk_rows);
       }
-      if (!a.inplace) srm2_segment_final_kernel<true><<<grid_final, kFinalThreads, sm_final, st>>>(a, short_rows, chunk_rows);
-    } else {
-      if (sm_final > 48 * 1024 && note_cuda(cudaFuncSetAttribute(srm2_segment_final_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm_final)))
-        return SRM2_ERR_CUDA;
-      if (note_cuda(cudaFuncSetAttribute(srm2_segment_runsum_kernel<false, kRunPrefetch>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRunSmemBytes))) return SRM2_ERR_CUDA;
-      if (wide) {
-        if (note_cuda(cudaFuncSetAttribute(srm2_segment_runsum_wide_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRunSmemBytes))) return SRM2_ERR_CUDA;
-        srm2_segment_runsum_wide_kernel<false><<<grid_runs, kRunThreads, kRunSmemBytes, st>>>(a);
-      } else {
-        srm2_segment_runsum_kernel<false, kRunPrefetch><<<grid_runs, kRunThreads, kRunSmemBytes, st>>>(a);
-      }
-      if (!a.inplace) srm2_segment_final_kernel<false><<<grid_final, kFinalThreads, sm_final, st>>>(a, short_rows, chunk_rows);
     }
   }
   stage_end(st);
-  return launch_status(launches + (n > 0 ? (a.inplace ? 3 : 4) : 1));
+  return launch_status(launches + (n > 0 ? (a.inplace ? 1 : 2) : 0));
 }
 
 }  // namespace srm2
@@ -757,6 +801,34 @@ extern "C" int srm2_reduce_adam_f32(float* pool, const int64_t* slots, const flo
                                     int order, const float sc[8], void* scratch, size_t scratch_bytes, srm2_stream_t stream) {
   return srm2::segment_pipeline(true, order, grad, inv, n, nullptr, D, n_unique, n_unique_dev, max_unique, nullptr, pool, slots, sc, scratch,
                                 scratch_bytes, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int srm2_reduce_adam_pull_f32(float* pool, const int64_t* slots, const float* const* peer_grad, int64_t world,
+                                         const uint32_t* src_code, const int64_t* inv, int64_t n, const int64_t* n_dev, int64_t D,
+                                         int64_t n_unique, const int64_t* n_unique_dev, int64_t max_unique, const float sc[8],
+                                         void* scratch, size_t scratch_bytes, srm2_stream_t stream) {
+  if (peer_grad == nullptr || world < 1 || world > srm2::kMaxGradPeers) return SRM2_ERR_ARG;
+  const srm2::PullSource pull{peer_grad, (int)world, src_code};
+  return srm2::segment_pipeline(true, SRM2_ORDER_RUNS, nullptr, inv, n, n_dev, D, n_unique, n_unique_dev, max_unique, nullptr, pool, slots, sc,
+                                scratch, scratch_bytes, static_cast<cudaStream_t>(stream), &pull);
+}
+
+extern "C" int srm2_reduce_adam_index(const int64_t* slots, const uint32_t* src_code, const int64_t* inv, int64_t n, const int64_t* n_dev,
+                                      int64_t D, int64_t n_unique, const int64_t* n_unique_dev, int64_t max_unique, void* scratch,
+                                      size_t scratch_bytes, srm2_stream_t stream) {
+  const srm2::PullSource pull{nullptr, 1, src_code};
+  return srm2::segment_pipeline(true, SRM2_ORDER_RUNS, nullptr, inv, n, n_dev, D, n_unique, n_unique_dev, max_unique, nullptr, nullptr, slots, nullptr,
+                                scratch, scratch_bytes, static_cast<cudaStream_t>(stream), src_code ? &pull : nullptr, srm2::kIndexPhase);
+}
+
+extern "C" int srm2_reduce_adam_apply_f32(float* pool, const int64_t* slots, const float* grad, const float* const* peer_grad, int64_t world,
+                                          int64_t n, const int64_t* n_dev, int64_t D, int64_t n_unique, const int64_t* n_unique_dev,
+                                          int64_t max_unique, const float sc[8], void* scratch, size_t scratch_bytes, srm2_stream_t stream) {
+  if ((grad == nullptr) == (peer_grad == nullptr) && n > 0) return SRM2_ERR_ARG;       // exactly one gradient source
+  if (peer_grad != nullptr && (world < 1 || world > srm2::kMaxGradPeers)) return SRM2_ERR_ARG;
+  const srm2::PullSource pull{peer_grad, (int)world, nullptr};
+  return srm2::segment_pipeline(true, SRM2_ORDER_RUNS, grad, nullptr, n, n_dev, D, n_unique, n_unique_dev, max_unique, nullptr, pool, slots, sc,
+                                scratch, scratch_bytes, static_cast<cudaStream_t>(stream), peer_grad ? &pull : nullptr, srm2::kSumPhase);
 }
 
 extern "C" int srm2_reduce_adam_nd_f32(float* pool, const int64_t* slots, const float* grad, const int64_t* inv, int64_t n,

@@ -76,6 +76,10 @@ class ShardedSparseAdam:
             f = dict(n=n_max, n_rows=n_rows, cap_u=cap_u, u=mk(cap_u, torch.int64), inv=mk(n_max, torch.int64),
                      scr_u=mk(L.srm2_unique_scratch_bytes(n_rows), torch.uint8),
                      scr_s=mk(L.srm2_segment_scratch_bytes(n_max, cap_u, self.D), torch.uint8))
+            # second set for the pipelined forms: the index half of step s+1 runs while the sum half of step s reads its own
+            f['u2'] = [f['u'], mk(cap_u, torch.int64)]
+            f['inv2'] = [f['inv'], mk(n_max, torch.int64)]
+            f['scr_s2'] = [f['scr_s'], mk(L.srm2_segment_scratch_bytes(n_max, cap_u, self.D), torch.uint8)]
             self._fast = f
         return f
 
@@ -141,12 +145,17 @@ class ShardedSparseAdam:
                               rlid=[mk(cap, dt=torch.int64) for _ in range(2)], rgrad=[mk(cap, self.D) for _ in range(2)])
         return self._pipe
 
-    def run_steps(self, batches, first_step):
+    def run_steps(self, batches, first_step, stage_events=None):
         """batches: list of (ids, grads) of this rank, one per step; step numbers first_step, first_step+1, ...
-        Returns the list of per-step count tensors (see step())."""
+        Returns the list of per-step count tensors (see step()).  stage_events: optional list of (start, end) CUDA events
+        per step, recorded by the library around the sum half of that step (the kernels that stream the gradient rows)."""
+        self._stage_events = stage_events
         import torch.distributed as dist
         if self.world == 1:
-            return [self.step(i, g, first_step + k) for k, (i, g) in enumerate(batches)]
+            n0 = batches[0][0].numel() if batches else 0
+            if n0 <= 3072 or any(i.numel() != n0 for i, _ in batches):     # small or ragged batches: the one-call form
+                return [self.step(i, g, first_step + k) for k, (i, g) in enumerate(batches)]
+            return self._run_steps_staged(batches, first_step)
         if getattr(self, '_peer', None) is not None:
             return self._run_steps_p2p(batches, first_step)
         K = len(batches)
@@ -214,30 +223,48 @@ class ShardedSparseAdam:
     # Exchange fused into the routing kernel: routed lookups are stored straight into the owners' receive buffers through
     # peer pointers (NVLink), see srm2_route_plan / publish / dispatch.  Nothing is read on the host: the receive buffers
     # have a fixed capacity, unused rows carry id -1 and are ignored by the shard update.
-    def enable_p2p(self, max_lookups_per_rank, slack=1.5):
-        """Allocates the symmetric receive buffers and exchanges their addresses.  Collective over the group.
+    def enable_p2p(self, max_lookups_per_rank, slack=1.5, pull=True, grad_slots=4):
+        """Allocates the symmetric buffers and exchanges their addresses.  Collective over the group.
+        pull=True: only lookup names are exchanged and the owners read the gradient rows from `grad_slots` peer-visible
+        gradient buffers of [max_lookups_per_rank, D] (grad_slot(k) is the one step k uses: write the gradients there to
+        avoid a copy).  pull=False: the rows are stored into the owners' receive buffers.
         Returns True when peer access is available; otherwise the NCCL all-to-all path stays in use."""
         import ctypes as C
         import torch.distributed as dist
         if self.world == 1 or self.world > 16:
             return False
+        if pull and (max_lookups_per_rank >= 1 << 24 or grad_slots < 4):
+            raise ValueError('pull mode: at most 2^24-1 lookups per rank; at least four gradient slots (the exchange runs three steps ahead)')
         try:
             import torch.distributed._symmetric_memory as symm
             W, D = self.world, self.D
-            cap = int(max_lookups_per_rank * slack) + 4096
+            n_max = int(max_lookups_per_rank)
+            cap = int(n_max * slack) + 4096
             rlid = symm.empty(2 * cap, dtype=torch.int64, device=self.dev)
-            rgrad = symm.empty(2 * cap * D, dtype=torch.float32, device=self.dev)
             cmat = symm.empty(2 * W * W, dtype=torch.int64, device=self.dev)
-            h = [symm.rendezvous(t, self.group) for t in (rlid, rgrad, cmat)]
+            if pull:
+                payload = symm.empty(2 * cap, dtype=torch.int32, device=self.dev)              # source codes
+                gbuf = symm.empty(grad_slots * n_max * D, dtype=torch.float32, device=self.dev)
+            else:
+                payload = symm.empty(2 * cap * D, dtype=torch.float32, device=self.dev)        # gradient rows
+                gbuf = None
+            sig = symm.empty(16, dtype=torch.int64, device=self.dev)                               # barrier tickets
+            ts = [rlid, payload, cmat, sig] + ([gbuf] if pull else [])
+            h = [symm.rendezvous(t, self.group) for t in ts]
             arr = lambda ptrs: (C.c_void_p * W)(*[int(x) for x in ptrs])
-            peer = dict(cap=cap, rlid=rlid, rgrad=rgrad, cmat=cmat, handles=h,
+            pbytes = 4 if pull else D * 4
+            peer = dict(cap=cap, n_max=n_max, pull=bool(pull), rlid=rlid, payload=payload, cmat=cmat, gbuf=gbuf, sig=sig, handles=h, ticket=0,
+                        p_sig=arr([h[3].buffer_ptrs[r] for r in range(W)]),
                         p_lid=[arr([h[0].buffer_ptrs[r] + b * cap * 8 for r in range(W)]) for b in range(2)],
-                        p_grad=[arr([h[1].buffer_ptrs[r] + b * cap * D * 4 for r in range(W)]) for b in range(2)],
+                        p_payload=[arr([h[1].buffer_ptrs[r] + b * cap * pbytes for r in range(W)]) for b in range(2)],
                         p_cmat=[arr([h[2].buffer_ptrs[r] + b * W * W * 8 for r in range(W)]) for b in range(2)],
                         counts=torch.zeros(W, dtype=torch.int64, device=self.dev), n_recv=torch.zeros(2, dtype=torch.int64, device=self.dev),
                         err=torch.zeros(1, dtype=torch.int32, device=self.dev), bar=torch.zeros(1, device=self.dev),
                         comm=torch.cuda.Stream(self.dev, priority=-1))   # routing must not queue behind the shard update
-            rlid.fill_(-1); cmat.zero_()
+            if pull:
+                peer['slots'] = grad_slots
+                peer['p_gbuf'] = [arr([h[4].buffer_ptrs[r] + s * n_max * D * 4 for r in range(W)]) for s in range(grad_slots)]
+            rlid.fill_(-1); cmat.zero_(); sig.zero_()
             torch.cuda.synchronize(self.dev)
             dist.barrier(group=self.group)
             self._peer = peer
@@ -247,9 +274,34 @@ class ShardedSparseAdam:
             self._peer_error = repr(e)
             return False
 
+    barrier_timeout_ns = 5_000_000_000     # a rank whose peers do not arrive within this time flags an error and carries on
+
+    def _barrier(self, stream_handle):
+        """Stream-ordered barrier across the ranks (one one-warp kernel with a bounded wait, srm2_peer_barrier)."""
+        P = self._peer
+        P['ticket'] += 1
+        _lib.check(_lib.lib().srm2_peer_barrier(P['p_sig'], self.rank, self.world, P['ticket'], P['err'].data_ptr(), self.barrier_timeout_ns,
+                                                stream_handle), 'peer_barrier')
+
+    def _check_exchange(self):
+        e = int(self._peer['err'].item())
+        if e != 0:
+            self._peer['err'].zero_()
+            raise RuntimeError('exchange failed (status %d: 1 = a receive buffer overflowed, 2 = a rank did not reach a barrier in time, '
+                               '4 = a copy did not complete)' % e)
+
+    def grad_slot(self, k):
+        """Pull mode: the peer-visible gradient buffer [max_lookups_per_rank, D] that step k reads (k mod grad_slots)."""
+        P = self._peer
+        s = k % P['slots']
+        n_max, D = P['n_max'], self.D
+        return P['gbuf'][s * n_max * D:(s + 1) * n_max * D].view(n_max, D)
+
     def _run_steps_p2p(self, batches, first_step):
         import torch.distributed as dist
         P, W, D = self._peer, self.world, self.D
+        if P['pull']:
+            return self._run_steps_staged(batches, first_step)
         cap, comm, comp = P['cap'], P['comm'], torch.cuda.current_stream(self.dev)
         L = _lib.lib()
         K = len(batches)
@@ -267,7 +319,7 @@ class ShardedSparseAdam:
         cmat_ptr = [P['cmat'][b * W * W:].data_ptr() for b in range(2)]
         nrecv_ptr = [P['n_recv'][b:].data_ptr() for b in range(2)]
         rl_ptr = [P['rlid'][b * cap:].data_ptr() for b in range(2)]
-        rg_ptr = [P['rgrad'][b * cap * D:].data_ptr() for b in range(2)]
+        rg_ptr = [P['payload'][b * cap * D:].data_ptr() for b in range(2)]
         self._fast_state(cap)
 
         def prepare(k):
@@ -278,11 +330,11 @@ class ShardedSparseAdam:
                     comm.wait_event(ev_done[k - 2])               # this parity's receive buffer has been consumed
                 _lib.check(L.srm2_route_plan(ids.data_ptr(), n, W, counts_ptr, scr_ptr, scr_len, cs), 'route_plan')
                 _lib.check(L.srm2_route_publish(counts_ptr, P['p_cmat'][b], self.rank, W, cs), 'route_publish')
-                dist.all_reduce(P['bar'], group=self.group)       # barrier: count matrices complete, receive buffers free
+                self._barrier(cs)                                 # count matrices complete, receive buffers free
                 _lib.check(L.srm2_route_dispatch(ids.data_ptr(), grads.data_ptr(), n, D, W, self.rank, cmat_ptr[b], P['p_lid'][b],
-                                                 P['p_grad'][b], cap, nrecv_ptr[b], err_ptr, int(self.use_tma), scr_ptr, scr_len, cs),
+                                                 P['p_payload'][b], cap, nrecv_ptr[b], err_ptr, int(self.use_tma), scr_ptr, scr_len, cs),
                            'route_dispatch')
-                dist.all_reduce(P['bar'], group=self.group)       # barrier: every row has arrived
+                self._barrier(cs)                                 # every row has arrived
                 ev_payload[k].record(comm)
 
         prepare(0)
@@ -297,9 +349,172 @@ class ShardedSparseAdam:
             ev_done[k].record(comp)
             out.append(counts_out[k])
         comp.wait_stream(comm)
-        if int(P['err'].item()) != 0:
-            raise RuntimeError('row dispatch failed (status %d: 1 = receive buffer overflow, 4 = a copy did not complete)' % int(P['err'].item()))
+        self._check_exchange()
         nr = int(P['n_recv'][(K - 1) & 1].item())
+        self.last_local_lookups = nr
+        self.last_local_lookups_total += nr * K
+        return out
+
+    # ------------------------------------------------------------------------------------------------------------
+    # The step as a pipeline of stages on separate streams, each stage one step ahead of the next.  Only the last stage
+    # needs the gradients; the others depend on the lookup ids alone, which a training loop knows ahead (prefetched batches).
+    #   exchange (s+3, world > 1): plan / publish / barrier / names -> owners / barrier
+    #   dedup    (s+2)           : unique rows + inverse of the (received) lookups
+    #   index    (s+1)           : index half of the fused reduce: sort, boundaries, plan, run descriptors
+    #   sums     (s)             : sum half: streams the gradient rows — at world > 1 from the ranks that produced them, over
+    #                              NVLink — and updates the shard
+    # The stages are chains of small latency-bound kernels except the last, which is bandwidth-bound and made of many
+    # short-lived CTAs, so the other streams' (high-priority) kernels find room on the SMs whenever they become ready.
+    # world > 1: step k's rows live in gradient slot k mod grad_slots of every rank; a batch whose gradients are not
+    # already that slot is copied into it between the two barriers of its exchange (every rank has finished the sums of
+    # the step that used the slot before: each rank waits for them before it enters the first barrier).
+    # Buffers: receive buffers, inverse, unique rows and reduce scratch exist twice (step parity); each stage waits for
+    # the last reader of what it overwrites.  Results are identical to calling step() in order.
+    def _run_steps_staged(self, batches, first_step):
+        P, W, D = getattr(self, '_peer', None), self.world, self.D
+        pull = W > 1
+        L = _lib.lib()
+        K = len(batches)
+        n_max = max(i.numel() for i, _ in batches)
+        comp = torch.cuda.current_stream(self.dev)
+        st = getattr(self, '_stage_streams', None)
+        if st is None:
+            st = self._stage_streams = [torch.cuda.Stream(self.dev, priority=-1) for _ in range(3)]
+        xs, ds, ix = st
+        xss, dss, ixs, ms = xs.cuda_stream, ds.cuda_stream, ix.cuda_stream, comp.cuda_stream
+        if pull:
+            if n_max > P['n_max']:
+                raise RuntimeError('more lookups than max_lookups_per_rank')
+            cap, S = P['cap'], P['slots']
+            scr = ops._scratch(self.dev, L.srm2_route_scratch_bytes(n_max, W), 'route')
+            scr_ptr, scr_len = scr.data_ptr(), scr.numel()
+            counts_ptr, err_ptr = P['counts'].data_ptr(), P['err'].data_ptr()
+            if 'n_recv4' not in P:
+                P['n_recv4'] = torch.zeros(4, dtype=torch.int64, device=self.dev)
+            cmat_ptr = [P['cmat'][b * W * W:].data_ptr() for b in range(2)]
+            nrecv_ptr = [P['n_recv4'][q:].data_ptr() for q in range(4)]
+            rl_ptr = [P['rlid'][b * cap:].data_ptr() for b in range(2)]
+            rs_ptr = [P['payload'][b * cap:].data_ptr() for b in range(2)]
+            slot_ptr = [self.grad_slot(q).data_ptr() for q in range(S)]
+            n = cap                                                   # bound; the count is on the device (n_recv)
+        else:
+            n, S = n_max, 0
+        f = self._fast_state(n)
+        cap_u = min(n, f['cap_u'])
+        counts_out = torch.zeros(K, 2, dtype=torch.int64, device=self.dev)
+        cnt_ptr = [counts_out[k].data_ptr() for k in range(K)]
+        u_ptr = [t.data_ptr() for t in f['u2']]
+        inv_ptr = [t.data_ptr() for t in f['inv2']]
+        ss_ptr = [t.data_ptr() for t in f['scr_s2']]
+        ss_len = f['scr_s2'][0].numel()
+        su_ptr, su_len = f['scr_u'].data_ptr(), f['scr_u'].numel()
+        pool_ptr = self.pool.data_ptr()
+
+        trace = bool(getattr(self, 'trace', False))               # timing events at the stage boundaries (diagnostics)
+        mkev = lambda: torch.cuda.Event(enable_timing=trace)
+        ev_x, ev_d, ev_i, ev_done = ([mkev() for _ in range(K)] for _ in range(4))
+        ev_begin = {q: [mkev() for _ in range(K)] for q in 'xdis'} if trace else None
+        ev_start = mkev(); ev_start.record(comp)
+        for q in st:
+            q.wait_event(ev_start)
+
+        def exchange(k):
+            ids, grads = batches[k]
+            b, nk = k & 1, ids.numel()
+            if k >= 2:
+                xs.wait_event(ev_i[k - 2])                        # this parity's receive buffers have been consumed
+            if k >= S:
+                xs.wait_event(ev_done[k - S])                     # nobody enters the barrier while it still reads slot k mod S
+            if trace:
+                ev_begin['x'][k].record(xs)
+            _lib.check(L.srm2_route_plan(ids.data_ptr(), nk, W, counts_ptr, scr_ptr, scr_len, xss), 'route_plan')
+            _lib.check(L.srm2_route_publish(counts_ptr, P['p_cmat'][b], self.rank, W, xss), 'route_publish')
+            self._barrier(xss)                                    # count matrices complete, receive buffers and slot free
+            if grads.data_ptr() != slot_ptr[k % S]:
+                with torch.cuda.stream(xs):
+                    self.grad_slot(k)[:nk].copy_(grads, non_blocking=True)
+            _lib.check(L.srm2_route_dispatch_ids(ids.data_ptr(), nk, W, self.rank, cmat_ptr[b], P['p_lid'][b], P['p_payload'][b], cap,
+                                                 nrecv_ptr[k & 3], err_ptr, scr_ptr, scr_len, xss), 'route_dispatch_ids')
+            self._barrier(xss)                                    # every name has arrived, every slot is filled
+            ev_x[k].record(xs)
+
+        def dedup(k):
+            b = k & 1
+            if pull:
+                ds.wait_event(ev_x[k])
+            if k >= 2:
+                ds.wait_event(ev_done[k - 2])                     # the unique rows of this parity have been consumed
+            if trace:
+                ev_begin['d'][k].record(ds)
+            ids_ptr, n_dev = (rl_ptr[b], nrecv_ptr[k & 3]) if pull else (batches[k][0].data_ptr(), 0)
+            _lib.check(L.srm2_unique_inverse_nd_i64(ids_ptr, n, n_dev, f['n_rows'], u_ptr[b], f['cap_u'], inv_ptr[b], cnt_ptr[k],
+                                                    su_ptr, su_len, dss), 'unique_inverse')
+            ev_d[k].record(ds)
+
+        def index(k):
+            b = k & 1
+            ix.wait_event(ev_d[k])
+            if k >= 2:
+                ix.wait_event(ev_done[k - 2])                     # this parity's descriptors have been consumed
+            if trace:
+                ev_begin['i'][k].record(ix)
+            src, n_dev = (rs_ptr[b], nrecv_ptr[k & 3]) if pull else (0, 0)
+            _lib.check(L.srm2_reduce_adam_index(u_ptr[b], src, inv_ptr[b], n, n_dev, D, -1, cnt_ptr[k], cap_u, ss_ptr[b], ss_len, ixs),
+                       'reduce_adam_index')
+            ev_i[k].record(ix)
+
+        def sums(k):
+            b = k & 1
+            comp.wait_event(ev_i[k])
+            if trace:
+                ev_begin['s'][k].record(comp)
+            sc = ops._scalars(*self.hyper, first_step + k)
+            if self._stage_events:
+                L.srm2_stage_events(self._stage_events[k][0].cuda_event, self._stage_events[k][1].cuda_event)
+            if pull:
+                rc = L.srm2_reduce_adam_apply_f32(pool_ptr, u_ptr[b], 0, P['p_gbuf'][k % S], W, n, nrecv_ptr[k & 3], D, -1, cnt_ptr[k], cap_u, sc,
+                                                  ss_ptr[b], ss_len, ms)
+            else:
+                rc = L.srm2_reduce_adam_apply_f32(pool_ptr, u_ptr[b], batches[k][1].data_ptr(), 0, 1, n, 0, D, -1, cnt_ptr[k], cap_u, sc,
+                                                  ss_ptr[b], ss_len, ms)
+            _lib.check(rc, 'reduce_adam_apply')
+            ev_done[k].record(comp)
+
+        # prologue, then every iteration enqueues one step of every stage, the oldest first (a stage only waits for events
+        # that have been recorded by then)
+        for k in range(min(2, K)):
+            if pull:
+                exchange(k)
+        for k in range(min(2, K)):
+            dedup(k)
+        index(0)
+        if pull and K > 2:
+            exchange(2)
+        out = []
+        for k in range(K):
+            sums(k)
+            out.append(counts_out[k])
+            if k + 1 < K:
+                index(k + 1)
+            if k + 2 < K:
+                dedup(k + 2)
+            if pull and k + 3 < K:
+                exchange(k + 3)
+        if self._stage_events:
+            L.srm2_stage_events(None, None)
+        for q in st:
+            comp.wait_stream(q)
+        if pull:
+            self._barrier(ms)                                     # no rank returns while a peer may still read its slots
+            self._check_exchange()
+            nr = int(P['n_recv4'][(K - 1) & 3].item())
+        else:
+            nr = n
+        if trace:      # microseconds since the start: (begin, end) of exchange, dedup, index, sums per step
+            torch.cuda.synchronize(self.dev)
+            us = lambda e: ev_start.elapsed_time(e) * 1e3
+            ends = {'x': ev_x, 'd': ev_d, 'i': ev_i, 's': ev_done}
+            self.trace_result = [tuple((us(ev_begin[q][k]), us(ends[q][k])) for q in ('xdis' if pull else 'dis')) for k in range(K)]
         self.last_local_lookups = nr
         self.last_local_lookups_total += nr * K
         return out

@@ -251,6 +251,36 @@ int srm2_route_dispatch(const int64_t* ids, const float* grad, int64_t n, int64_
                         int64_t* n_recv, uint32_t* err, int use_tma, void* scratch, size_t scratch_bytes, srm2_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------------
+ * Pull form of the same exchange (no counterpart in the reference): the gradient rows stay in the buffer of the rank
+ * that produced them (peer-accessible memory) and only the names of the lookups travel.  The owner's fused
+ * segment-reduce + Adam reads each row from its source over NVLink while it sums, so the rows cross the link once and
+ * are never written to or re-read from the owner's memory.
+ *   srm2_route_plan, srm2_route_publish, -- barrier --   as above
+ *   srm2_route_dispatch_ids   local ids -> peer_lid[d] [cap] int64 and codes (rank << 24) | position -> peer_src[d] [cap]
+ *                             uint32 of each owner d, same offsets, n_recv and err as srm2_route_dispatch; n < 2^24.
+ *   -- barrier --             every name has arrived
+ *   srm2_unique_inverse_nd_i64 on the received ids, then
+ *   srm2_reduce_adam_pull_f32 like srm2_reduce_adam_nd_f32 with order SRM2_ORDER_RUNS, except that lookup i's gradient
+ *                             row is row (src_code[i] & 0xffffff) of peer_grad[src_code[i] >> 24] (host array of `world`
+ *                             device pointers, 16-byte aligned, row stride D floats).
+ *   -- barrier --             before any rank overwrites a gradient buffer that peers may still be reading
+ */
+/* Stream-ordered barrier across the ranks' GPUs for the "-- barrier --" marks above (no counterpart in the reference;
+ * any collective on the stream serves as well, this one is a single one-warp kernel).  peer_tickets: host array of
+ * `world` device pointers, entry r = rank r's array of 16 uint64 in peer-visible memory, zero before the first use.
+ * `ticket` must grow by one with every barrier and be the same on every rank.  A rank whose peers do not arrive within
+ * timeout_ns sets bit 1 (value 2) of *err and carries on: the wait is bounded, the caller must check *err. */
+int srm2_peer_barrier(void* const* peer_tickets /* host */, int64_t rank, int64_t world, uint64_t ticket, uint32_t* err,
+                      int64_t timeout_ns, srm2_stream_t stream);
+int srm2_route_dispatch_ids(const int64_t* ids, int64_t n, int64_t world, int64_t rank, const int64_t* cmat,
+                            void* const* peer_lid /* host */, void* const* peer_src /* host */, int64_t cap, int64_t* n_recv,
+                            uint32_t* err, void* scratch, size_t scratch_bytes, srm2_stream_t stream);
+int srm2_reduce_adam_pull_f32(float* pool, const int64_t* slots, const float* const* peer_grad /* host */, int64_t world,
+                              const uint32_t* src_code, const int64_t* inv, int64_t n, const int64_t* n_dev, int64_t D,
+                              int64_t n_unique, const int64_t* n_unique_dev, int64_t max_unique, const float sc[8] /* host */,
+                              void* scratch, size_t scratch_bytes, srm2_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------------
  * Variants whose lookup count lives on the device (no counterpart in the reference): n is an upper bound that sizes
  * grids and scratch, the kernels process min(n, *n_dev) lookups.  They let a receive buffer of fixed capacity be
  * consumed without reading its fill level on the host (row-sharded exchange).  n_dev == NULL behaves like the plain
@@ -262,6 +292,27 @@ int srm2_unique_inverse_nd_i64(const int64_t* ids, int64_t n, const int64_t* n_d
 int srm2_reduce_adam_nd_f32(float* pool, const int64_t* slots, const float* grad, const int64_t* inv, int64_t n,
                             const int64_t* n_dev, int64_t D, int64_t n_unique, const int64_t* n_unique_dev, int64_t max_unique,
                             int order, const float sc[8] /* host */, void* scratch, size_t scratch_bytes, srm2_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * The fused segment-reduce + Adam in two halves (no counterpart in the reference).  Everything up to the run
+ * descriptors depends on the lookups' row indices only, not on the gradients: a training loop that knows the ids of
+ * the next batch ahead (data-loader prefetch) can run srm2_unique_inverse_* and srm2_reduce_adam_index for step s+1
+ * on a second stream while srm2_reduce_adam_apply_f32 of step s streams the gradient rows.  The halves communicate
+ * through `scratch` alone (same n, D, max_unique and scratch in both calls; order them with an event); use one scratch
+ * buffer per step in flight.  Order of summation: SRM2_ORDER_RUNS.  Precondition: every unique row has at least one
+ * lookup (as srm2_unique_inverse_* produces); a row without lookups is left unchanged by the split form.
+ *   srm2_reduce_adam_index      src_code == NULL: lookup i's gradient is row i of `grad` given to the apply call;
+ *                               src_code != NULL: pull form, see srm2_reduce_adam_pull_f32.
+ *   srm2_reduce_adam_apply_f32  exactly one of grad (local rows) and peer_grad (host array of `world` device pointers)
+ *                               is non-NULL and must match the index call.
+ */
+int srm2_reduce_adam_index(const int64_t* slots, const uint32_t* src_code, const int64_t* inv, int64_t n, const int64_t* n_dev,
+                           int64_t D, int64_t n_unique, const int64_t* n_unique_dev, int64_t max_unique, void* scratch,
+                           size_t scratch_bytes, srm2_stream_t stream);
+int srm2_reduce_adam_apply_f32(float* pool, const int64_t* slots, const float* grad, const float* const* peer_grad /* host */,
+                               int64_t world, int64_t n, const int64_t* n_dev, int64_t D, int64_t n_unique,
+                               const int64_t* n_unique_dev, int64_t max_unique, const float sc[8] /* host */, void* scratch,
+                               size_t scratch_bytes, srm2_stream_t stream);
 
 #ifdef __cplusplus
 }

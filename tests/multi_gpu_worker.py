@@ -44,17 +44,29 @@ def main():
     counts = eng2.run_steps(batches, 1)                  # the software-pipelined form must give the same shard
     eng3 = ShardedSparseAdam(total_rows, D, world, rank, dev, seed=42, bound=0.01, hyper=HYP, max_lookups_per_rank=batch * 26,
                              group=dist.group.WORLD)
-    p2p = eng3.enable_p2p(batch * 26)                    # exchange fused into the routing kernel (peer stores)
+    p2p = eng3.enable_p2p(batch * 26, pull=False)        # exchange fused into the routing kernel (peer stores)
     counts3 = eng3.run_steps(batches, 1)
+    # pull form: names travel, the owners read the gradient rows from the ranks that produced them.  Step 1's gradients
+    # are written into its slot beforehand (no copy), the others are copied in by run_steps.
+    eng4 = ShardedSparseAdam(total_rows, D, world, rank, dev, seed=42, bound=0.01, hyper=HYP, max_lookups_per_rank=batch * 26,
+                             group=dist.group.WORLD)
+    pull = eng4.enable_p2p(batch * 26, pull=True, grad_slots=4)
+    batches4 = list(batches)
+    if pull:
+        g0 = eng4.grad_slot(0)[:batches[0][1].shape[0]]
+        g0.copy_(batches[0][1])
+        batches4[0] = (batches[0][0], g0)
+    counts4 = eng4.run_steps(batches4, 1)
     torch.cuda.synchronize(dev)
     shard = eng.pool.cpu().numpy()
     ok = np.array_equal(shard.view(np.uint32), st[rank::world].view(np.uint32))
     ok = ok and torch.equal(eng.pool.view(torch.int32), eng2.pool.view(torch.int32)) and sum(int(c[0]) for c in counts) == rows_updated
     ok = ok and torch.equal(eng.pool.view(torch.int32), eng3.pool.view(torch.int32)) and sum(int(c[0]) for c in counts3) == rows_updated
+    ok = ok and torch.equal(eng.pool.view(torch.int32), eng4.pool.view(torch.int32)) and sum(int(c[0]) for c in counts4) == rows_updated
     flag = torch.tensor([int(ok), rows_updated], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
-        print(f'MULTI_GPU_RESULT ok={int(flag[0])} world={world} rows_updated_min={int(flag[1])} p2p={int(p2p)} '
+        print(f'MULTI_GPU_RESULT ok={int(flag[0])} world={world} rows_updated_min={int(flag[1])} p2p={int(p2p)} pull={int(pull)} '
               f'{getattr(eng3, "_peer_error", "")}', flush=True)
     dist.barrier()
     dist.destroy_process_group()

@@ -42,3 +42,111 @@ def test_engine_world1_vs_oracle(oracle):
         oracle.adam_rows(st, u, oracle.segment_reduce(grad, inv, len(u)), *HYP, step)
         assert int(c[0]) == len(u) and int(c[1]) == 0
     assert np.array_equal(eng.pool.cpu().numpy().view(np.uint32), st.view(np.uint32))
+
+
+@pytest.mark.parametrize('n,D,W', [(3000, 16, 2), (40000, 128, 4), (90000, 64, 3), (212992, 128, 8)])
+def test_pull_exchange_emulated_on_one_gpu(oracle, n, D, W):
+    """Pull form of the exchange with all W ranks' buffers on one device (kernels run one after another, nothing waits):
+    plan / publish / dispatch_ids for every rank, then every owner's dedup + srm2_reduce_adam_pull_f32 reading the
+    gradient rows where the ranks left them.  The W shards must equal the single-process oracle bit for bit."""
+    import ctypes as C
+    from elara_b200 import _lib, ops
+    from elara_b200.gpu_ops import init_rows
+    from elara_b200.sharded import local_rows
+    dev = torch.device('cuda:0')
+    L = _lib.lib()
+    R = 50_000
+    rng = np.random.default_rng(n + W)
+    p = np.arange(1, R + 1, dtype=np.float64) ** -1.1
+    perm0 = rng.permutation(R)
+    ids = [perm0[rng.choice(R, size=n, p=p / p.sum())].astype(np.int64) for _ in range(W)]
+    grads = [(rng.standard_normal((n, D)) * 10.0 ** rng.integers(-3, 4, size=(n, 1))).astype(np.float32) for _ in range(W)]
+    t_ids = [torch.from_numpy(x).to(dev) for x in ids]
+    t_grads = [torch.from_numpy(x).to(dev) for x in grads]
+    cap = 3 * n + 4096                      # the owner of the hottest rows receives well above the average
+    st = torch.cuda.current_stream(dev).cuda_stream
+    arr = lambda ts: (C.c_void_p * W)(*[t.data_ptr() for t in ts])
+    rlid = [torch.full((cap,), -1, dtype=torch.int64, device=dev) for _ in range(W)]
+    rsrc = [torch.zeros(cap, dtype=torch.int32, device=dev) for _ in range(W)]
+    cmat = [torch.zeros(W * W, dtype=torch.int64, device=dev) for _ in range(W)]
+    n_recv = torch.zeros(W, dtype=torch.int64, device=dev)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    nb = L.srm2_route_scratch_bytes(n, W)
+    scr = [torch.empty(nb, dtype=torch.uint8, device=dev) for _ in range(W)]
+    counts = torch.zeros(W, dtype=torch.int64, device=dev)
+    for r in range(W):
+        _lib.check(L.srm2_route_plan(t_ids[r].data_ptr(), n, W, counts.data_ptr(), scr[r].data_ptr(), nb, st), 'plan')
+        _lib.check(L.srm2_route_publish(counts.data_ptr(), arr(cmat), r, W, st), 'publish')
+    for r in range(W):
+        _lib.check(L.srm2_route_dispatch_ids(t_ids[r].data_ptr(), n, W, r, cmat[r].data_ptr(), arr(rlid), arr(rsrc), cap,
+                                             n_recv[r:].data_ptr(), err.data_ptr(), scr[r].data_ptr(), nb, st), 'dispatch_ids')
+    assert int(err.item()) == 0
+    # single-process expectation
+    all_ids = np.concatenate(ids); all_grads = np.concatenate(grads)
+    state = oracle.init_rows(np.arange(R), D, 7, 0.01)
+    u, inv = oracle.unique_inverse(all_ids)
+    oracle.adam_rows(state, u, oracle.segment_reduce(all_grads, inv, len(u), chunk=oracle.SEGMENT_CHUNK), *HYP, 3)
+    sc = ops._scalars(*HYP, 3)
+    for d in range(W):
+        nl = local_rows(R, W, d)
+        assert int(n_recv[d]) == sum(int((x % W == d).sum()) for x in ids)
+        pool = init_rows(torch.arange(nl, device=dev) * W + d, D, 7, 0.01)
+        uq = torch.empty(min(cap, nl), dtype=torch.int64, device=dev); iv = torch.empty(cap, dtype=torch.int64, device=dev)
+        cnt = torch.zeros(2, dtype=torch.int64, device=dev)
+        su = torch.empty(L.srm2_unique_scratch_bytes(nl), dtype=torch.uint8, device=dev)
+        ss = torch.empty(L.srm2_segment_scratch_bytes(cap, uq.numel(), D), dtype=torch.uint8, device=dev)
+        _lib.check(L.srm2_unique_inverse_nd_i64(rlid[d].data_ptr(), cap, n_recv[d:].data_ptr(), nl, uq.data_ptr(), uq.numel(), iv.data_ptr(),
+                                                cnt.data_ptr(), su.data_ptr(), su.numel(), st), 'unique')
+        _lib.check(L.srm2_reduce_adam_pull_f32(pool.data_ptr(), uq.data_ptr(), arr(t_grads), W, rsrc[d].data_ptr(), iv.data_ptr(), cap,
+                                               n_recv[d:].data_ptr(), D, -1, cnt.data_ptr(), uq.numel(), sc, ss.data_ptr(), ss.numel(), st),
+                   'reduce_adam_pull')
+        assert np.array_equal(pool.cpu().numpy().view(np.uint32), state[d::W].view(np.uint32)), d
+
+
+def test_engine_world1_pipelined_equals_step_by_step(oracle):
+    """run_steps at world size 1 (index half of step s+1 on a side stream while the sum half of step s runs) against
+    step() on a second engine and against the oracle."""
+    from elara_b200 import synth
+    from elara_b200.sharded import ShardedSparseAdam
+    dev = torch.device('cuda:0')
+    R, D, batch = 300_000, 128, 1024
+    sizes, offs = synth.table_sizes(R, 26, lo=4, hi=100_000, seed=5)
+    mk = lambda: ShardedSparseAdam(R, D, 1, 0, dev, seed=42, bound=0.01, hyper=HYP, max_lookups_per_rank=batch * 26)
+    eng, ref = mk(), mk()
+    st = oracle.init_rows(np.arange(R), D, 42, 0.01)
+    batches = []
+    for step in range(1, 8):
+        ids = synth.zipf_lookups(sizes, offs, batch, 1.1, 11, step)
+        grad = synth.normal_f32((len(ids), D), 1e-3, 11, step)
+        batches.append((torch.from_numpy(ids).to(dev), torch.from_numpy(grad).to(dev)))
+        u, inv = oracle.unique_inverse(ids)
+        oracle.adam_rows(st, u, oracle.segment_reduce(grad, inv, len(u)), *HYP, step)
+        ref.step(*batches[-1], step)
+    counts = eng.run_steps(batches[:4], 1) + eng.run_steps(batches[4:], 5)
+    torch.cuda.synchronize()
+    assert [int(c[0]) for c in counts] == [len(np.unique(i.cpu().numpy())) for i, _ in batches]
+    assert torch.equal(eng.pool.view(torch.int32), ref.pool.view(torch.int32))
+    assert np.array_equal(eng.pool.cpu().numpy().view(np.uint32), st.view(np.uint32))
+
+
+def test_peer_barrier_wait_is_bounded():
+    """The barrier kernel of the exchange gives up after its time limit and reports it: here `rank 1` never arrives (its
+    ticket array is a buffer that nothing writes), so rank 0 flags status 2 after 2 ms and the context stays usable; a
+    second barrier whose tickets are already there passes without a flag."""
+    import ctypes as C
+    from elara_b200 import _lib
+    dev = torch.device('cuda:0')
+    L = _lib.lib()
+    mine = torch.zeros(16, dtype=torch.int64, device=dev)
+    other = torch.zeros(16, dtype=torch.int64, device=dev)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    arr = (C.c_void_p * 2)(mine.data_ptr(), other.data_ptr())
+    st = torch.cuda.current_stream(dev).cuda_stream
+    _lib.check(L.srm2_peer_barrier(arr, 0, 2, 1, err.data_ptr(), 2_000_000, st), 'barrier')
+    torch.cuda.synchronize()
+    assert int(err.item()) == 2
+    assert int(other[0]) == 1 and int(mine[0]) == 1            # its own tickets were delivered
+    err.zero_(); mine[1] = 2                                    # "rank 1" has arrived at barrier 2
+    _lib.check(L.srm2_peer_barrier(arr, 0, 2, 2, err.data_ptr(), 2_000_000, st), 'barrier')
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
