@@ -392,7 +392,7 @@ srm2_segment_runsum_kernel(ReduceArgs a) {
 //  - the copy and add loops run `len` times (len is uniform over the group) instead of ten predicated times;
 //  - descriptors are fetched two items ahead and positions one item ahead, so neither is waited for.
 template <bool FUSED, bool PEER>
-__global__ void __launch_bounds__(kRunThreads)
+__global__ void __launch_bounds__(kRunThreads, 4)
 srm2_segment_runsum_wide_kernel(ReduceArgs a) {
   extern __shared__ __align__(128) float4 stage[];                 // [kRunStageVecs][kRunThreads]
   uint32_t* s_long = reinterpret_cast<uint32_t*>(stage + kRunStageVecs * kRunThreads);   // behind the staging slots, so
@@ -405,20 +405,48 @@ srm2_segment_runsum_wide_kernel(ReduceArgs a) {
   const unsigned gmask = a.lpr >= 32 ? 0xffffffffu : (((1u << a.lpr) - 1u) << (lane & ~(a.lpr - 1)));
   const int gleader = a.lpr >= 32 ? 0 : (lane & ~(a.lpr - 1));
   const int gl = lane - gleader;                    // lane within the group
-  const int64_t stride = (int64_t)gridDim.x * kRunThreads;
+  const int64_t step = (int64_t)gridDim.x * kRunThreads;         // grid-stride: even waves whatever the number of runs
   int64_t t = (int64_t)blockIdx.x * kRunThreads + threadIdx.x;
+  const int64_t end = items;
   const int j4 = (int)(t & (a.lpr - 1));
   auto run_of = [&](int64_t tt) { return tt >> a.shift; };
+  auto load_desc = [&](int64_t tt) -> uint4 { return tt < end ? __ldg(a.run_desc + run_of(tt)) : make_uint4(0u, 0u, 0u, 0u); };
   auto load_pos = [&](const uint4& d, int64_t c) -> uint32_t {   // position gl of run c, for runs of more than one lookup
     const int len = (int)(d.y & 0xffu);
     return (len > 1 && gl < len) ? __ldg(a.run_pos + c * kRun + gl) : 0u;
   };
-  uint4 d0 = make_uint4(0u, 0u, 0u, 0u), d1 = d0, d2 = d0;
-  uint32_t p0 = 0, p1 = 0;
-  if (t < items) d0 = __ldg(a.run_desc + run_of(t));
-  if (t + stride < items) d1 = __ldg(a.run_desc + run_of(t + stride));
-  if (t < items) p0 = load_pos(d0, run_of(t));
-  for (; t < items; t += stride) {
+  auto lone = [](const uint4& d) { return d.y == 1u; };          // a row with a single lookup: one run of length one
+  // descriptors of this item and the next two; positions of this item
+  uint4 d0 = load_desc(t), d1 = load_desc(t + step), d2 = load_desc(t + 2 * step);
+  uint32_t p0 = t < end ? load_pos(d0, run_of(t)) : 0u, p1 = 0;
+  while (t < end) {
+    if (FUSED && lone(d0) && lone(d1) && lone(d2)) {
+      // ---- three single-lookup rows at once: 3 x (gradient row, w, m, v) = 12 of the 13 slots, 192 bytes in flight ----
+      float* b0 = a.pool + (int64_t)((uint64_t)d0.z | ((uint64_t)d0.w << 32)) * (3 * (int64_t)a.D) + j4 * 4;
+      float* b1 = a.pool + (int64_t)((uint64_t)d1.z | ((uint64_t)d1.w << 32)) * (3 * (int64_t)a.D) + j4 * 4;
+      float* b2 = a.pool + (int64_t)((uint64_t)d2.z | ((uint64_t)d2.w << 32)) * (3 * (int64_t)a.D) + j4 * 4;
+      cp_async16(mine, grad_row<PEER>(a, d0.x) + j4 * 4);
+      cp_async16(mine + 4 * kRunThreads, grad_row<PEER>(a, d1.x) + j4 * 4);
+      cp_async16(mine + 8 * kRunThreads, grad_row<PEER>(a, d2.x) + j4 * 4);
+      cp_async16(mine + 1 * kRunThreads, b0); cp_async16(mine + 2 * kRunThreads, b0 + a.D); cp_async16(mine + 3 * kRunThreads, b0 + 2 * a.D);
+      cp_async16(mine + 5 * kRunThreads, b1); cp_async16(mine + 6 * kRunThreads, b1 + a.D); cp_async16(mine + 7 * kRunThreads, b1 + 2 * a.D);
+      cp_async16(mine + 9 * kRunThreads, b2); cp_async16(mine + 10 * kRunThreads, b2 + a.D); cp_async16(mine + 11 * kRunThreads, b2 + 2 * a.D);
+      cp_async_commit();
+      t += 3 * step;
+      d0 = load_desc(t); d1 = load_desc(t + step); d2 = load_desc(t + 2 * step);
+      cp_async_wait<0>();
+      const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int e = 0; e < 3; ++e) {
+        float* b = e == 0 ? b0 : (e == 1 ? b1 : b2);
+        const float4 g = add4(zero, add4(zero, mine[(4 * e) * kRunThreads]));     // the run sum from +0, then the row sum from +0
+        float4 w = mine[(4 * e + 1) * kRunThreads], m = mine[(4 * e + 2) * kRunThreads], v = mine[(4 * e + 3) * kRunThreads];
+        adam_vec4(w, m, v, g, a.sc);
+        *reinterpret_cast<float4*>(b) = w; *reinterpret_cast<float4*>(b + a.D) = m; *reinterpret_cast<float4*>(b + 2 * a.D) = v;
+      }
+      if (t < end) p0 = load_pos(d0, run_of(t));
+      continue;
+    }
     const uint4 d = d0;
     const int len = (int)(d.y & 0xffu);
     const bool multi = (d.y & kMultiBit) != 0;
@@ -443,13 +471,14 @@ srm2_segment_runsum_wide_kernel(ReduceArgs a) {
       }
     }
     cp_async_commit();
-    // ---- next items: descriptor two ahead, positions one ahead ----
-    if (t + 2 * stride < items) d2 = __ldg(a.run_desc + run_of(t + 2 * stride));
-    if (t + stride < items) p1 = load_pos(d1, run_of(t + stride));
+    // ---- next items: descriptor three ahead, positions one ahead ----
+    const uint4 d3 = load_desc(t + 3 * step);
+    if (t + step < end) p1 = load_pos(d1, run_of(t + step));
     cp_async_wait<0>();
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int q = 0; q < len; ++q) acc = add4(acc, mine[q * kRunThreads]);
-    d0 = d1; d1 = d2; p0 = p1;
+    d0 = d1; d1 = d2; d2 = d3; p0 = p1;
+    t += step;
     if (!multi) {
       const float4 g = add4(make_float4(0.f, 0.f, 0.f, 0.f), acc);
       if (FUSED) {

@@ -76,10 +76,9 @@ class ShardedSparseAdam:
             f = dict(n=n_max, n_rows=n_rows, cap_u=cap_u, u=mk(cap_u, torch.int64), inv=mk(n_max, torch.int64),
                      scr_u=mk(L.srm2_unique_scratch_bytes(n_rows), torch.uint8),
                      scr_s=mk(L.srm2_segment_scratch_bytes(n_max, cap_u, self.D), torch.uint8))
-            # second set for the pipelined forms: the index half of step s+1 runs while the sum half of step s reads its own
-            f['u2'] = [f['u'], mk(cap_u, torch.int64)]
-            f['inv2'] = [f['inv'], mk(n_max, torch.int64)]
-            f['scr_s2'] = [f['scr_s'], mk(L.srm2_segment_scratch_bytes(n_max, cap_u, self.D), torch.uint8)]
+            # three sets for the staged form: dedup of step s+2, index half of step s+1 and sum half of step s each work on
+            # their own (allocated on first use)
+            f['u2'], f['inv2'], f['scr_s2'] = [f['u']], [f['inv']], [f['scr_s']]
             self._fast = f
         return f
 
@@ -240,10 +239,11 @@ class ShardedSparseAdam:
             W, D = self.world, self.D
             n_max = int(max_lookups_per_rank)
             cap = int(n_max * slack) + 4096
-            rlid = symm.empty(2 * cap, dtype=torch.int64, device=self.dev)
-            cmat = symm.empty(2 * W * W, dtype=torch.int64, device=self.dev)
+            nrb = 4 if pull else 2                       # receive buffers (pull: small, and the exchange runs three steps ahead)
+            rlid = symm.empty(nrb * cap, dtype=torch.int64, device=self.dev)
+            cmat = symm.empty(nrb * W * W, dtype=torch.int64, device=self.dev)
             if pull:
-                payload = symm.empty(2 * cap, dtype=torch.int32, device=self.dev)              # source codes
+                payload = symm.empty(nrb * cap, dtype=torch.int32, device=self.dev)            # source codes
                 gbuf = symm.empty(grad_slots * n_max * D, dtype=torch.float32, device=self.dev)
             else:
                 payload = symm.empty(2 * cap * D, dtype=torch.float32, device=self.dev)        # gradient rows
@@ -253,11 +253,11 @@ class ShardedSparseAdam:
             h = [symm.rendezvous(t, self.group) for t in ts]
             arr = lambda ptrs: (C.c_void_p * W)(*[int(x) for x in ptrs])
             pbytes = 4 if pull else D * 4
-            peer = dict(cap=cap, n_max=n_max, pull=bool(pull), rlid=rlid, payload=payload, cmat=cmat, gbuf=gbuf, sig=sig, handles=h, ticket=0,
+            peer = dict(cap=cap, n_max=n_max, pull=bool(pull), nrb=nrb, rlid=rlid, payload=payload, cmat=cmat, gbuf=gbuf, sig=sig, handles=h, ticket=0,
                         p_sig=arr([h[3].buffer_ptrs[r] for r in range(W)]),
-                        p_lid=[arr([h[0].buffer_ptrs[r] + b * cap * 8 for r in range(W)]) for b in range(2)],
-                        p_payload=[arr([h[1].buffer_ptrs[r] + b * cap * pbytes for r in range(W)]) for b in range(2)],
-                        p_cmat=[arr([h[2].buffer_ptrs[r] + b * W * W * 8 for r in range(W)]) for b in range(2)],
+                        p_lid=[arr([h[0].buffer_ptrs[r] + b * cap * 8 for r in range(W)]) for b in range(nrb)],
+                        p_payload=[arr([h[1].buffer_ptrs[r] + b * cap * pbytes for r in range(W)]) for b in range(nrb)],
+                        p_cmat=[arr([h[2].buffer_ptrs[r] + b * W * W * 8 for r in range(W)]) for b in range(nrb)],
                         counts=torch.zeros(W, dtype=torch.int64, device=self.dev), n_recv=torch.zeros(2, dtype=torch.int64, device=self.dev),
                         err=torch.zeros(1, dtype=torch.int32, device=self.dev), bar=torch.zeros(1, device=self.dev),
                         comm=torch.cuda.Stream(self.dev, priority=-1))   # routing must not queue behind the shard update
@@ -368,8 +368,8 @@ class ShardedSparseAdam:
     # world > 1: step k's rows live in gradient slot k mod grad_slots of every rank; a batch whose gradients are not
     # already that slot is copied into it between the two barriers of its exchange (every rank has finished the sums of
     # the step that used the slot before: each rank waits for them before it enters the first barrier).
-    # Buffers: receive buffers, inverse, unique rows and reduce scratch exist twice (step parity); each stage waits for
-    # the last reader of what it overwrites.  Results are identical to calling step() in order.
+    # Buffers: receive buffers exist four times, inverse, unique rows and reduce scratch three times; each stage
+    # waits for the last reader of what it overwrites.  Results are identical to calling step() in order.
     def _run_steps_staged(self, batches, first_step):
         P, W, D = getattr(self, '_peer', None), self.world, self.D
         pull = W > 1
@@ -390,17 +390,21 @@ class ShardedSparseAdam:
             scr_ptr, scr_len = scr.data_ptr(), scr.numel()
             counts_ptr, err_ptr = P['counts'].data_ptr(), P['err'].data_ptr()
             if 'n_recv4' not in P:
-                P['n_recv4'] = torch.zeros(4, dtype=torch.int64, device=self.dev)
-            cmat_ptr = [P['cmat'][b * W * W:].data_ptr() for b in range(2)]
-            nrecv_ptr = [P['n_recv4'][q:].data_ptr() for q in range(4)]
-            rl_ptr = [P['rlid'][b * cap:].data_ptr() for b in range(2)]
-            rs_ptr = [P['payload'][b * cap:].data_ptr() for b in range(2)]
+                P['n_recv4'] = torch.zeros(8, dtype=torch.int64, device=self.dev)
+            NRB = P['nrb']
+            cmat_ptr = [P['cmat'][b * W * W:].data_ptr() for b in range(NRB)]
+            nrecv_ptr = [P['n_recv4'][q:].data_ptr() for q in range(8)]
+            rl_ptr = [P['rlid'][b * cap:].data_ptr() for b in range(NRB)]
+            rs_ptr = [P['payload'][b * cap:].data_ptr() for b in range(NRB)]
             slot_ptr = [self.grad_slot(q).data_ptr() for q in range(S)]
             n = cap                                                   # bound; the count is on the device (n_recv)
         else:
-            n, S = n_max, 0
+            n, S, NRB = n_max, 0, 1
         f = self._fast_state(n)
         cap_u = min(n, f['cap_u'])
+        NB = 3                                                        # buffer sets = stages that hold one (dedup, index, sums)
+        while len(f['u2']) < NB:
+            f['u2'].append(torch.empty_like(f['u'])); f['inv2'].append(torch.empty_like(f['inv'])); f['scr_s2'].append(torch.empty_like(f['scr_s']))
         counts_out = torch.zeros(K, 2, dtype=torch.int64, device=self.dev)
         cnt_ptr = [counts_out[k].data_ptr() for k in range(K)]
         u_ptr = [t.data_ptr() for t in f['u2']]
@@ -411,6 +415,52 @@ class ShardedSparseAdam:
         pool_ptr = self.pool.data_ptr()
 
         trace = bool(getattr(self, 'trace', False))               # timing events at the stage boundaries (diagnostics)
+        if not trace and not getattr(self, 'host_loop', False):
+            # the same loop inside the library (srm2_staged_steps): a step is ~20 launches, and issuing them from Python takes
+            # longer than running them
+            import ctypes as C
+            vp = lambda xs: (C.c_void_p * len(xs))(*[int(x) for x in xs])
+            ring = getattr(self, '_event_ring', None)
+            if ring is None:
+                ring = self._event_ring = [torch.cuda.Event() for _ in range(64)]
+                for e in ring:
+                    e.record(comp)                                # materialise the handles
+            A = _lib.Staged()
+            A.K, A.first_step, A.n, A.D, A.n_rows, A.cap_u = K, first_step, n, D, f['n_rows'], f['cap_u']
+            A.lr, A.b1, A.b2, A.eps = self.hyper
+            A.pool, A.counts_out = pool_ptr, counts_out.data_ptr()
+            keep = [vp([i.data_ptr() for i, _ in batches]), vp([g.data_ptr() for _, g in batches]),
+                    (C.c_int64 * K)(*[i.numel() for i, _ in batches]), vp([xss, dss, ixs, ms]), vp([e.cuda_event for e in ring])]
+            A.ids, A.grads, A.n_k, A.streams, A.events = (C.cast(x, C.c_void_p) for x in keep)
+            for q in range(3):
+                A.u[q], A.inv[q], A.scr_s[q] = u_ptr[q], inv_ptr[q], ss_ptr[q]
+            A.scr_s_bytes, A.scr_u, A.scr_u_bytes = ss_len, su_ptr, su_len
+            if self._stage_events:
+                keep.append(vp([e.cuda_event for pair in self._stage_events for e in pair]))
+                A.stage_events = C.cast(keep[-1], C.c_void_p)
+            A.world, A.rank = W, self.rank
+            if pull:
+                tk = C.c_int64(P['ticket'])
+                flat = lambda lists: vp([int(x) for arr_ in lists for x in arr_])
+                keep += [vp(cmat_ptr), vp(rl_ptr), vp(rs_ptr), flat(P['p_cmat']), flat(P['p_lid']), flat(P['p_payload']), vp(slot_ptr),
+                         flat(P['p_gbuf']), tk]
+                A.cap, A.n_recv_bufs, A.n_slots, A.timeout_ns = cap, NRB, S, self.barrier_timeout_ns
+                A.route_scr, A.route_scr_bytes, A.counts, A.err, A.n_recv = scr_ptr, scr_len, counts_ptr, err_ptr, P['n_recv4'].data_ptr()
+                (A.cmat, A.recv_lid, A.recv_src, A.peer_cmat, A.peer_lid, A.peer_src, A.slot, A.peer_slot) = (C.cast(x, C.c_void_p) for x in keep[-9:-1])
+                A.peer_tickets = C.cast(P['p_sig'], C.c_void_p)
+                A.ticket = C.cast(C.pointer(tk), C.c_void_p)
+            rc = L.srm2_staged_steps(C.byref(A))
+            if pull:
+                P['ticket'] = tk.value
+            _lib.check(rc, 'staged_steps')
+            if pull:
+                self._check_exchange()
+                nr = int(P['n_recv4'][(K - 1) & 7].item())
+            else:
+                nr = n
+            self.last_local_lookups = nr
+            self.last_local_lookups_total += nr * K
+            return [counts_out[k] for k in range(K)]
         mkev = lambda: torch.cuda.Event(enable_timing=trace)
         ev_x, ev_d, ev_i, ev_done = ([mkev() for _ in range(K)] for _ in range(4))
         ev_begin = {q: [mkev() for _ in range(K)] for q in 'xdis'} if trace else None
@@ -420,9 +470,9 @@ class ShardedSparseAdam:
 
         def exchange(k):
             ids, grads = batches[k]
-            b, nk = k & 1, ids.numel()
-            if k >= 2:
-                xs.wait_event(ev_i[k - 2])                        # this parity's receive buffers have been consumed
+            b, nk = k % NRB, ids.numel()
+            if k >= NRB:
+                xs.wait_event(ev_i[k - NRB])                      # these receive buffers have been consumed
             if k >= S:
                 xs.wait_event(ev_done[k - S])                     # nobody enters the barrier while it still reads slot k mod S
             if trace:
@@ -434,37 +484,35 @@ class ShardedSparseAdam:
                 with torch.cuda.stream(xs):
                     self.grad_slot(k)[:nk].copy_(grads, non_blocking=True)
             _lib.check(L.srm2_route_dispatch_ids(ids.data_ptr(), nk, W, self.rank, cmat_ptr[b], P['p_lid'][b], P['p_payload'][b], cap,
-                                                 nrecv_ptr[k & 3], err_ptr, scr_ptr, scr_len, xss), 'route_dispatch_ids')
+                                                 nrecv_ptr[k & 7], err_ptr, scr_ptr, scr_len, xss), 'route_dispatch_ids')
             self._barrier(xss)                                    # every name has arrived, every slot is filled
             ev_x[k].record(xs)
 
         def dedup(k):
-            b = k & 1
+            b, q = k % NRB, k % NB
             if pull:
                 ds.wait_event(ev_x[k])
-            if k >= 2:
-                ds.wait_event(ev_done[k - 2])                     # the unique rows of this parity have been consumed
+            if k >= NB:
+                ds.wait_event(ev_done[k - NB])                    # this buffer set has been consumed
             if trace:
                 ev_begin['d'][k].record(ds)
-            ids_ptr, n_dev = (rl_ptr[b], nrecv_ptr[k & 3]) if pull else (batches[k][0].data_ptr(), 0)
-            _lib.check(L.srm2_unique_inverse_nd_i64(ids_ptr, n, n_dev, f['n_rows'], u_ptr[b], f['cap_u'], inv_ptr[b], cnt_ptr[k],
+            ids_ptr, n_dev = (rl_ptr[b], nrecv_ptr[k & 7]) if pull else (batches[k][0].data_ptr(), 0)
+            _lib.check(L.srm2_unique_inverse_nd_i64(ids_ptr, n, n_dev, f['n_rows'], u_ptr[q], f['cap_u'], inv_ptr[q], cnt_ptr[k],
                                                     su_ptr, su_len, dss), 'unique_inverse')
             ev_d[k].record(ds)
 
         def index(k):
-            b = k & 1
+            b, q = k % NRB, k % NB
             ix.wait_event(ev_d[k])
-            if k >= 2:
-                ix.wait_event(ev_done[k - 2])                     # this parity's descriptors have been consumed
             if trace:
                 ev_begin['i'][k].record(ix)
-            src, n_dev = (rs_ptr[b], nrecv_ptr[k & 3]) if pull else (0, 0)
-            _lib.check(L.srm2_reduce_adam_index(u_ptr[b], src, inv_ptr[b], n, n_dev, D, -1, cnt_ptr[k], cap_u, ss_ptr[b], ss_len, ixs),
+            src, n_dev = (rs_ptr[b], nrecv_ptr[k & 7]) if pull else (0, 0)
+            _lib.check(L.srm2_reduce_adam_index(u_ptr[q], src, inv_ptr[q], n, n_dev, D, -1, cnt_ptr[k], cap_u, ss_ptr[q], ss_len, ixs),
                        'reduce_adam_index')
             ev_i[k].record(ix)
 
         def sums(k):
-            b = k & 1
+            q = k % NB
             comp.wait_event(ev_i[k])
             if trace:
                 ev_begin['s'][k].record(comp)
@@ -472,11 +520,11 @@ class ShardedSparseAdam:
             if self._stage_events:
                 L.srm2_stage_events(self._stage_events[k][0].cuda_event, self._stage_events[k][1].cuda_event)
             if pull:
-                rc = L.srm2_reduce_adam_apply_f32(pool_ptr, u_ptr[b], 0, P['p_gbuf'][k % S], W, n, nrecv_ptr[k & 3], D, -1, cnt_ptr[k], cap_u, sc,
-                                                  ss_ptr[b], ss_len, ms)
+                rc = L.srm2_reduce_adam_apply_f32(pool_ptr, u_ptr[q], 0, P['p_gbuf'][k % S], W, n, nrecv_ptr[k & 7], D, -1, cnt_ptr[k], cap_u, sc,
+                                                  ss_ptr[q], ss_len, ms)
             else:
-                rc = L.srm2_reduce_adam_apply_f32(pool_ptr, u_ptr[b], batches[k][1].data_ptr(), 0, 1, n, 0, D, -1, cnt_ptr[k], cap_u, sc,
-                                                  ss_ptr[b], ss_len, ms)
+                rc = L.srm2_reduce_adam_apply_f32(pool_ptr, u_ptr[q], batches[k][1].data_ptr(), 0, 1, n, 0, D, -1, cnt_ptr[k], cap_u, sc,
+                                                  ss_ptr[q], ss_len, ms)
             _lib.check(rc, 'reduce_adam_apply')
             ev_done[k].record(comp)
 
@@ -507,7 +555,7 @@ class ShardedSparseAdam:
         if pull:
             self._barrier(ms)                                     # no rank returns while a peer may still read its slots
             self._check_exchange()
-            nr = int(P['n_recv4'][(K - 1) & 3].item())
+            nr = int(P['n_recv4'][(K - 1) & 7].item())
         else:
             nr = n
         if trace:      # microseconds since the start: (begin, end) of exchange, dedup, index, sums per step

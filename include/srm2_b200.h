@@ -314,6 +314,47 @@ int srm2_reduce_adam_apply_f32(float* pool, const int64_t* slots, const float* g
                                const int64_t* n_unique_dev, int64_t max_unique, const float sc[8] /* host */, void* scratch,
                                size_t scratch_bytes, srm2_stream_t stream);
 
+/* ---------------------------------------------------------------------------------------------------------
+ * A window of K steps as a pipeline of stages on four streams, enqueued by one call (no counterpart in the reference;
+ * the reference's driver is a Python loop).  It issues exactly the calls documented above, in this order per
+ * iteration k — sums(k), index(k+1), dedup(k+2), exchange(k+3) — with CUDA events between the stages:
+ *   exchange (world > 1)  srm2_route_plan, _publish, srm2_peer_barrier, [copy of the step's gradients into its slot],
+ *                         srm2_route_dispatch_ids, srm2_peer_barrier                       on streams[0]
+ *   dedup                 srm2_unique_inverse_nd_i64                                       on streams[1]
+ *   index                 srm2_reduce_adam_index                                           on streams[2]
+ *   sums                  srm2_reduce_adam_apply_f32 (local rows, or peer_grad at world>1) on streams[3], the caller's
+ * A host loop that makes these calls itself gives the same result; this entry point exists because at ~20 launches per
+ * step the host, not the GPU, bounds such a loop.  All members are 8 bytes wide.  Pointers marked (host) are host
+ * arrays; everything else is device memory.  Nothing is allocated or synchronised; the call returns when the window is
+ * enqueued, streams[0..2] have been joined into streams[3].
+ */
+typedef struct srm2_staged {
+  int64_t K, first_step, n, D, n_rows, cap_u;   /* n: lookups per step (world 1), capacity of a receive buffer (world > 1) */
+  double lr, b1, b2, eps;
+  float* pool;                                   /* [n_rows, 3, D] */
+  int64_t* counts_out;                           /* [K, 2]: unique rows, invalid ids per step */
+  const void* const* ids;                        /* (host) [K] int64 [n_k] */
+  const void* const* grads;                      /* (host) [K] float [n_k, D] */
+  const int64_t* n_k;                            /* (host) [K] lookups of each step; world 1: all equal n */
+  int64_t* u[3]; int64_t* inv[3]; void* scr_s[3];/* three buffer sets: unique rows [cap_u], inverse [n], reduce scratch */
+  int64_t scr_s_bytes; void* scr_u; int64_t scr_u_bytes;
+  void* const* streams;                          /* (host) [4] cudaStream_t */
+  void* const* events;                           /* (host) [64] cudaEvent_t without timing: 16 per stage */
+  void* const* stage_events;                     /* (host) [2K] or NULL: recorded around the sums of each step */
+  /* world > 1 (pull exchange); ignored at world 1 */
+  int64_t world, rank, cap, n_recv_bufs, n_slots, timeout_ns;
+  void* route_scr; int64_t route_scr_bytes; int64_t* counts; uint32_t* err; int64_t* n_recv;   /* n_recv: [8] */
+  int64_t* const* cmat;                          /* (host) [n_recv_bufs] this rank's count matrices */
+  int64_t* const* recv_lid;                      /* (host) [n_recv_bufs] this rank's receive buffers (ids) */
+  uint32_t* const* recv_src;                     /* (host) [n_recv_bufs] ... (codes) */
+  void* const* peer_cmat; void* const* peer_lid; void* const* peer_src;   /* (host) [n_recv_bufs * world] */
+  float* const* slot;                            /* (host) [n_slots] this rank's gradient slots */
+  const float* const* peer_slot;                 /* (host) [n_slots * world] */
+  void* const* peer_tickets;                     /* (host) [world] */
+  int64_t* ticket;                               /* (host) in/out: last ticket used */
+} srm2_staged;
+int srm2_staged_steps(const srm2_staged* a /* host */);
+
 #ifdef __cplusplus
 }
 #endif

@@ -57,12 +57,18 @@ def main():
         g0.copy_(batches[0][1])
         batches4[0] = (batches[0][0], g0)
     counts4 = eng4.run_steps(batches4, 1)
+    eng5 = ShardedSparseAdam(total_rows, D, world, rank, dev, seed=42, bound=0.01, hyper=HYP, max_lookups_per_rank=batch * 26,
+                             group=dist.group.WORLD)
+    eng5.enable_p2p(batch * 26, pull=True, grad_slots=5)
+    eng5.host_loop = True                                # the same stages issued from Python instead of srm2_staged_steps
+    counts5 = eng5.run_steps(batches[:2], 1) + eng5.run_steps(batches[2:], 3)
     torch.cuda.synchronize(dev)
     shard = eng.pool.cpu().numpy()
     ok = np.array_equal(shard.view(np.uint32), st[rank::world].view(np.uint32))
     ok = ok and torch.equal(eng.pool.view(torch.int32), eng2.pool.view(torch.int32)) and sum(int(c[0]) for c in counts) == rows_updated
     ok = ok and torch.equal(eng.pool.view(torch.int32), eng3.pool.view(torch.int32)) and sum(int(c[0]) for c in counts3) == rows_updated
     ok = ok and torch.equal(eng.pool.view(torch.int32), eng4.pool.view(torch.int32)) and sum(int(c[0]) for c in counts4) == rows_updated
+    ok = ok and torch.equal(eng.pool.view(torch.int32), eng5.pool.view(torch.int32)) and sum(int(c[0]) for c in counts5) == rows_updated
     flag = torch.tensor([int(ok), rows_updated], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:

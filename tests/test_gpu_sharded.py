@@ -123,9 +123,13 @@ def test_engine_world1_pipelined_equals_step_by_step(oracle):
         oracle.adam_rows(st, u, oracle.segment_reduce(grad, inv, len(u)), *HYP, step)
         ref.step(*batches[-1], step)
     counts = eng.run_steps(batches[:4], 1) + eng.run_steps(batches[4:], 5)
+    eng2 = mk(); eng2.host_loop = True                       # the same stages issued from Python instead of srm2_staged_steps
+    counts2 = eng2.run_steps(batches[:1], 1) + eng2.run_steps(batches[1:], 2)
     torch.cuda.synchronize()
     assert [int(c[0]) for c in counts] == [len(np.unique(i.cpu().numpy())) for i, _ in batches]
+    assert [int(c[0]) for c in counts2] == [int(c[0]) for c in counts]
     assert torch.equal(eng.pool.view(torch.int32), ref.pool.view(torch.int32))
+    assert torch.equal(eng2.pool.view(torch.int32), ref.pool.view(torch.int32))
     assert np.array_equal(eng.pool.cpu().numpy().view(np.uint32), st.view(np.uint32))
 
 
