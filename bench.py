@@ -458,8 +458,8 @@ def add_cpu_baseline(out, a):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
-    ap.add_argument('--steps', type=int, default=20)
-    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--steps', type=int, default=100)
+    ap.add_argument('--warmup', type=int, default=5)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--rows', type=int, default=0, help='rows per GPU (default: 33.8M at 1 GPU, 25M per GPU above)')
     ap.add_argument('--batch', type=int, default=8192, help='samples per GPU per step (x26 lookups)')

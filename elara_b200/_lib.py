@@ -42,7 +42,7 @@ SIGNATURES = {
     'srm2_route_dispatch': (C.c_int, [_vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _i32, _vp, _sz, _vp]),
     'srm2_unique_inverse_nd_i64': (C.c_int, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _sz, _vp]),
     'srm2_reduce_adam_nd_f32': (C.c_int, [_vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _vp, _i64, _i32, _f8, _vp, _sz, _vp]),
-    'srm2_reduce_adam_index': (C.c_int, [_vp, _vp, _vp, _i64, _vp, _i64, _i64, _vp, _i64, _vp, _sz, _vp]),
+    'srm2_reduce_adam_index': (C.c_int, [_vp, _vp, _vp, _i64, _vp, _i64, _i64, _vp, _i64, _i32, _vp, _sz, _vp]),
     'srm2_reduce_adam_apply_f32': (C.c_int, [_vp, _vp, _vp, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _f8, _vp, _sz, _vp]),
     'srm2_peer_barrier': (C.c_int, [_vp, _i64, _i64, C.c_uint64, _vp, _i64, _vp]),
     'srm2_staged_steps': (C.c_int, [_vp]),
@@ -57,7 +57,7 @@ class Staged(C.Structure):
     _fields_ = ([(k, C.c_int64) for k in ('K', 'first_step', 'n', 'D', 'n_rows', 'cap_u')] +
                 [(k, C.c_double) for k in ('lr', 'b1', 'b2', 'eps')] +
                 [(k, C.c_void_p) for k in ('pool', 'counts_out', 'ids', 'grads', 'n_k')] +
-                [('u', C.c_void_p * 3), ('inv', C.c_void_p * 3), ('scr_s', C.c_void_p * 3)] +
+                [('u', C.c_void_p * 4), ('inv', C.c_void_p * 4), ('scr_s', C.c_void_p * 4)] +
                 [('scr_s_bytes', C.c_int64), ('scr_u', C.c_void_p), ('scr_u_bytes', C.c_int64)] +
                 [(k, C.c_void_p) for k in ('streams', 'events', 'stage_events')] +
                 [(k, C.c_int64) for k in ('world', 'rank', 'cap', 'n_recv_bufs', 'n_slots', 'timeout_ns')] +

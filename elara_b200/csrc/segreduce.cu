@@ -698,25 +698,26 @@ static int launch_runsum(const ReduceArgs& a, bool wide, int grid, cudaStream_t 
 
 struct PullSource { const float* const* peer_grad; int world; const uint32_t* src_code; };   // pull mode (fused, runs order only)
 
-// phase: kIndexPhase = everything that depends on the lookups' row indices only (sort, boundaries, plan, descriptors);
-// kSumPhase = the kernels that read gradients and write rows.  The two halves of a split call communicate through the
-// scratch buffer alone, so they may run on different streams (ordered by an event), and the index half of the next
-// step may run while the sum half of this one is still streaming.
-constexpr int kIndexPhase = 1, kSumPhase = 2, kBothPhases = 3;
+// phase bits: kSortPhase (sort, boundaries) and kDescrPhase (plan, run descriptors) together are the index half —
+// everything that depends on the lookups' row indices only; kSumPhase = the kernels that read gradients and write rows.
+// The parts of a split call communicate through the scratch buffer alone, so they may run on different streams (ordered
+// by events), and the index work of later steps may run while the sum half of this one is still streaming.
+constexpr int kSortPhase = 1, kSumPhase = 2, kDescrPhase = 4, kIndexPhase = kSortPhase | kDescrPhase, kAllPhases = 7;
 
 static int segment_pipeline(bool fused, int order, const float* grad, const int64_t* inv, int64_t n, const int64_t* n_dev, int64_t D, int64_t nu_host,
                             const int64_t* nu_dev, int64_t cap, float* out, float* pool, const int64_t* slots,
                             const float* sc, void* scratch, size_t scratch_bytes, cudaStream_t st, const PullSource* pull = nullptr,
-                            int phase = kBothPhases) {
+                            int phase = kAllPhases) {
   if (n < 0 || D <= 0 || cap < 0 || (nu_host < 0 && nu_dev == nullptr) || order < 0 || order > 2) return SRM2_ERR_ARG;
   if (nu_dev == nullptr) cap = nu_host;
   if (cap == 0) return SRM2_OK;
-  const bool index_phase = (phase & kIndexPhase) != 0, sum_phase = (phase & kSumPhase) != 0;
-  if (n > 0 && ((sum_phase && grad == nullptr && pull == nullptr) || (index_phase && inv == nullptr))) return SRM2_ERR_ARG;
-  if (phase != kBothPhases && (!fused || order != SRM2_ORDER_RUNS)) return SRM2_ERR_ARG;
+  const bool sort_phase = (phase & kSortPhase) != 0, descr_phase = (phase & kDescrPhase) != 0, sum_phase = (phase & kSumPhase) != 0;
+  const bool index_phase = sort_phase || descr_phase;
+  if (n > 0 && ((sum_phase && grad == nullptr && pull == nullptr) || (sort_phase && inv == nullptr))) return SRM2_ERR_ARG;
+  if (phase != kAllPhases && (!fused || order != SRM2_ORDER_RUNS)) return SRM2_ERR_ARG;
   if (pull) {
     if (!fused || order != SRM2_ORDER_RUNS || pull->world < 1 || pull->world > kMaxGradPeers || (sum_phase && pull->peer_grad == nullptr) ||
-        (index_phase && pull->src_code == nullptr))
+        (descr_phase && pull->src_code == nullptr))
       return SRM2_ERR_ARG;
     for (int r = 0; sum_phase && r < pull->world; ++r)
       if (pull->peer_grad[r] == nullptr || !aligned16(pull->peer_grad[r])) return SRM2_ERR_ARG;
@@ -734,10 +735,10 @@ static int segment_pipeline(bool fused, int order, const float* grad, const int6
   int launches = 0;
 
   // empty ranges for rows that no lookup names; counters (incl. the finished-CTA count) start at zero
-  if (index_phase && note_cuda(cudaMemsetAsync(s.zero, 0, s.zero_bytes, st))) return SRM2_ERR_CUDA;
+  if (sort_phase && note_cuda(cudaMemsetAsync(s.zero, 0, s.zero_bytes, st))) return SRM2_ERR_CUDA;
   // 1. sort (key = inv, value = position), 2. boundaries
-  const uint32_t *skey = nullptr, *spos = nullptr;
-  if (n > 0 && index_phase) {
+  const uint32_t *skey = (s.passes & 1) ? s.keyA : s.keyB, *spos = (s.passes & 1) ? s.valA : s.valB;   // where the last pass lands
+  if (n > 0 && sort_phase) {
     SortBuffers sb{s.keyA, s.valA, s.keyB, s.valB, s.hist, s.dtot, s.tiles};
     const uint32_t* hb = nullptr;
     const int rc = radix_sort_by_key(inv, n, n_dev, /*mod=*/0, cap, s.bits, s.passes, sb, &skey, &spos, &hb, &launches, st);
@@ -763,8 +764,9 @@ static int segment_pipeline(bool fused, int order, const float* grad, const int6
     return launch_status(launches + 1);
   }
   // 3. plan, 4. descriptors.  A split call leaves rows without lookups alone (its index half must not write rows).
-  if (index_phase) {
-    const int skip_empty = phase != kBothPhases;
+  if (sort_phase && !descr_phase && !sum_phase) return launch_status(launches);
+  if (descr_phase) {
+    const int skip_empty = phase != kAllPhases;
     if (fused)
       srm2_segment_plan_kernel<true><<<s.nblocks, kPlanThreads, 0, st>>>(a, s.run_off, s.mrun_off, s.mrow_off, s.bsum_r, s.bsum_m, s.bsum_f,
                                                                         s.counters, s.nblocks, skip_empty);
@@ -843,11 +845,13 @@ extern "C" int srm2_reduce_adam_pull_f32(float* pool, const int64_t* slots, cons
 }
 
 extern "C" int srm2_reduce_adam_index(const int64_t* slots, const uint32_t* src_code, const int64_t* inv, int64_t n, const int64_t* n_dev,
-                                      int64_t D, int64_t n_unique, const int64_t* n_unique_dev, int64_t max_unique, void* scratch,
+                                      int64_t D, int64_t n_unique, const int64_t* n_unique_dev, int64_t max_unique, int part, void* scratch,
                                       size_t scratch_bytes, srm2_stream_t stream) {
+  if (part < 0 || part > 2) return SRM2_ERR_ARG;
   const srm2::PullSource pull{nullptr, 1, src_code};
+  const int phase = part == SRM2_INDEX_SORT ? srm2::kSortPhase : (part == SRM2_INDEX_DESCRIPTORS ? srm2::kDescrPhase : srm2::kIndexPhase);
   return srm2::segment_pipeline(true, SRM2_ORDER_RUNS, nullptr, inv, n, n_dev, D, n_unique, n_unique_dev, max_unique, nullptr, nullptr, slots, nullptr,
-                                scratch, scratch_bytes, static_cast<cudaStream_t>(stream), src_code ? &pull : nullptr, srm2::kIndexPhase);
+                                scratch, scratch_bytes, static_cast<cudaStream_t>(stream), src_code ? &pull : nullptr, phase);
 }
 
 extern "C" int srm2_reduce_adam_apply_f32(float* pool, const int64_t* slots, const float* grad, const float* const* peer_grad, int64_t world,

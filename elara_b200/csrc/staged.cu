@@ -1,24 +1,24 @@
-// A window of optimizer steps enqueued as a pipeline of stages on four streams (see srm2_staged in the header).
+// A window of optimizer steps enqueued as a pipeline of stages on five streams (see srm2_staged in the header).
 // Pure host code: it makes the library's own calls and orders them with CUDA events.  Written in C++ because a step is
 // about twenty launches and an interpreted host loop needs longer to issue them than the GPU needs to run them.
 #include "common.cuh"
 
-static_assert(sizeof(srm2_staged) == 51 * 8, "srm2_staged: every member is 8 bytes wide");
+static_assert(sizeof(srm2_staged) == 54 * 8, "srm2_staged: every member is 8 bytes wide");
 
 namespace srm2 {
 namespace {
 
 constexpr int kRing = 16;          // events per stage; every dependency reaches back fewer steps than this
-constexpr int kSets = 3;           // buffer sets of dedup / index / sums
+constexpr int kSets = 4;           // buffer sets: dedup, sort, descriptors and sums each hold one
 
 struct Staged {
   const srm2_staged& a;
-  cudaStream_t xs, ds, ix, ms;
+  cudaStream_t xs, ds, so, ix, ms;
   bool pull;
   int rc = SRM2_OK;
   explicit Staged(const srm2_staged& s) : a(s), pull(s.world > 1) {
     xs = static_cast<cudaStream_t>(a.streams[0]); ds = static_cast<cudaStream_t>(a.streams[1]);
-    ix = static_cast<cudaStream_t>(a.streams[2]); ms = static_cast<cudaStream_t>(a.streams[3]);
+    so = static_cast<cudaStream_t>(a.streams[2]); ix = static_cast<cudaStream_t>(a.streams[3]); ms = static_cast<cudaStream_t>(a.streams[4]);
   }
   cudaEvent_t ev(int stage, int64_t k) const { return static_cast<cudaEvent_t>(a.events[stage * kRing + (int)(k % kRing)]); }
   bool ok() const { return rc == SRM2_OK; }
@@ -32,8 +32,8 @@ struct Staged {
   // stage 0: names of step k to their owners
   void exchange(int64_t k) {
     const int64_t R = a.n_recv_bufs, S = a.n_slots, W = a.world, b = k % R, nk = a.n_k[k];
-    if (k >= R) cuda(cudaStreamWaitEvent(xs, ev(2, k - R), 0));          // these receive buffers have been consumed
-    if (k >= S) cuda(cudaStreamWaitEvent(xs, ev(3, k - S), 0));          // nobody enters the barrier while it still reads the slot
+    if (k >= R) cuda(cudaStreamWaitEvent(xs, ev(3, k - R), 0));          // these receive buffers have been consumed
+    if (k >= S) cuda(cudaStreamWaitEvent(xs, ev(4, k - S), 0));          // nobody enters the barrier while it still reads the slot
     check(srm2_route_plan(static_cast<const int64_t*>(a.ids[k]), nk, W, a.counts, a.route_scr, (size_t)a.route_scr_bytes, xs));
     check(srm2_route_publish(a.counts, a.peer_cmat + b * W, a.rank, W, xs));
     barrier(xs);                                                          // count matrices complete, receive buffers and slot free
@@ -49,26 +49,27 @@ struct Staged {
   void dedup(int64_t k) {
     const int64_t q = k % kSets;
     if (pull) cuda(cudaStreamWaitEvent(ds, ev(0, k), 0));
-    if (k >= kSets) cuda(cudaStreamWaitEvent(ds, ev(3, k - kSets), 0));  // this buffer set has been consumed
+    if (k >= kSets) cuda(cudaStreamWaitEvent(ds, ev(4, k - kSets), 0));  // this buffer set has been consumed
     const int64_t* ids = pull ? a.recv_lid[k % a.n_recv_bufs] : static_cast<const int64_t*>(a.ids[k]);
     const int64_t* n_dev = pull ? a.n_recv + (k & 7) : nullptr;
     check(srm2_unique_inverse_nd_i64(ids, a.n, n_dev, a.n_rows, a.u[q], a.cap_u, a.inv[q], a.counts_out + 2 * k, a.scr_u, (size_t)a.scr_u_bytes, ds));
     cuda(cudaEventRecord(ev(1, k), ds));
   }
-  // stage 2
-  void index(int64_t k) {
+  // stages 2 and 3: the index half of the fused reduce in its two parts
+  void index(int64_t k, int part) {
     const int64_t q = k % kSets;
-    cuda(cudaStreamWaitEvent(ix, ev(1, k), 0));
+    cudaStream_t st = part == SRM2_INDEX_SORT ? so : ix;
+    cuda(cudaStreamWaitEvent(st, ev(part == SRM2_INDEX_SORT ? 1 : 2, k), 0));
     const uint32_t* src = pull ? a.recv_src[k % a.n_recv_bufs] : nullptr;
     const int64_t* n_dev = pull ? a.n_recv + (k & 7) : nullptr;
-    check(srm2_reduce_adam_index(a.u[q], src, a.inv[q], a.n, n_dev, a.D, -1, a.counts_out + 2 * k, a.cap_u < a.n ? a.cap_u : a.n, a.scr_s[q],
-                                 (size_t)a.scr_s_bytes, ix));
-    cuda(cudaEventRecord(ev(2, k), ix));
+    check(srm2_reduce_adam_index(a.u[q], src, a.inv[q], a.n, n_dev, a.D, -1, a.counts_out + 2 * k, a.cap_u < a.n ? a.cap_u : a.n, part, a.scr_s[q],
+                                 (size_t)a.scr_s_bytes, st));
+    cuda(cudaEventRecord(ev(part == SRM2_INDEX_SORT ? 2 : 3, k), st));
   }
-  // stage 3
+  // stage 4
   void sums(int64_t k) {
     const int64_t q = k % kSets;
-    cuda(cudaStreamWaitEvent(ms, ev(2, k), 0));
+    cuda(cudaStreamWaitEvent(ms, ev(3, k), 0));
     float sc[8];
     check(srm2_adam_scalars(a.lr, a.b1, a.b2, a.eps, a.first_step + k, sc));
     if (a.stage_events) srm2_stage_events(a.stage_events[2 * k], a.stage_events[2 * k + 1]);
@@ -79,32 +80,36 @@ struct Staged {
     else
       check(srm2_reduce_adam_apply_f32(a.pool, a.u[q], static_cast<const float*>(a.grads[k]), nullptr, 1, a.n, nullptr, a.D, -1, a.counts_out + 2 * k,
                                        cap_u, sc, a.scr_s[q], (size_t)a.scr_s_bytes, ms));
-    cuda(cudaEventRecord(ev(3, k), ms));
+    cuda(cudaEventRecord(ev(4, k), ms));
   }
 
   int run() {
     const int64_t K = a.K;
     // the side streams start behind what the caller's stream has enqueued so far
-    cudaEvent_t start = ev(3, kRing - 1);
+    cudaEvent_t start = ev(4, kRing - 1);
     cuda(cudaEventRecord(start, ms));
-    cuda(cudaStreamWaitEvent(xs, start, 0)); cuda(cudaStreamWaitEvent(ds, start, 0)); cuda(cudaStreamWaitEvent(ix, start, 0));
+    for (cudaStream_t st : {xs, ds, so, ix}) cuda(cudaStreamWaitEvent(st, start, 0));
     // prologue; then every iteration enqueues one step of every stage, the oldest first, so that a stage only ever waits
     // for events that have been recorded by then
-    for (int64_t k = 0; k < 3 && k < K && pull && ok(); ++k) exchange(k);
-    for (int64_t k = 0; k < 2 && k < K && ok(); ++k) dedup(k);
-    if (K > 0 && ok()) index(0);
+    for (int64_t k = 0; k < 4 && k < K && pull && ok(); ++k) exchange(k);
+    for (int64_t k = 0; k < 3 && k < K && ok(); ++k) dedup(k);
+    for (int64_t k = 0; k < 2 && k < K && ok(); ++k) index(k, SRM2_INDEX_SORT);
+    if (K > 0 && ok()) index(0, SRM2_INDEX_DESCRIPTORS);
     for (int64_t k = 0; k < K && ok(); ++k) {
       sums(k);
-      if (k + 1 < K && ok()) index(k + 1);
-      if (k + 2 < K && ok()) dedup(k + 2);
-      if (pull && k + 3 < K && ok()) exchange(k + 3);
+      if (k + 1 < K && ok()) index(k + 1, SRM2_INDEX_DESCRIPTORS);
+      if (k + 2 < K && ok()) index(k + 2, SRM2_INDEX_SORT);
+      if (k + 3 < K && ok()) dedup(k + 3);
+      if (pull && k + 4 < K && ok()) exchange(k + 4);
     }
     if (a.stage_events) srm2_stage_events(nullptr, nullptr);
     // join: what follows on the caller's stream sees the window complete
     if (K > 0) {
-      cudaEvent_t j0 = ev(0, (K - 1) + 1), j1 = ev(1, (K - 1) + 1), j2 = ev(2, (K - 1) + 1);   // ring entries nobody waits on any more
-      cudaEventRecord(j0, xs); cudaEventRecord(j1, ds); cudaEventRecord(j2, ix);
-      cudaStreamWaitEvent(ms, j0, 0); cudaStreamWaitEvent(ms, j1, 0); cudaStreamWaitEvent(ms, j2, 0);
+      int stage = 0;
+      for (cudaStream_t st : {xs, ds, so, ix}) {
+        cudaEvent_t j = ev(stage++, K);                                   // a ring entry nobody waits on any more
+        cudaEventRecord(j, st); cudaStreamWaitEvent(ms, j, 0);
+      }
     }
     if (pull && ok()) barrier(ms);                                        // no rank returns while a peer may still read its slots
     return rc;
@@ -119,7 +124,7 @@ extern "C" int srm2_staged_steps(const srm2_staged* a) {
   if (a == nullptr || a->K < 0 || a->n < 0 || a->D <= 0 || a->ids == nullptr || a->grads == nullptr || a->n_k == nullptr || a->streams == nullptr ||
       a->events == nullptr || a->pool == nullptr || a->counts_out == nullptr)
     return SRM2_ERR_ARG;
-  for (int q = 0; q < 3; ++q)
+  for (int q = 0; q < 4; ++q)
     if (a->u[q] == nullptr || a->inv[q] == nullptr || a->scr_s[q] == nullptr) return SRM2_ERR_ARG;
   if (a->world > 1) {
     if (a->world > 16 || a->rank < 0 || a->rank >= a->world || a->n_recv_bufs < 4 || a->n_recv_bufs >= 16 || a->n_slots < 4 || a->n_slots >= 16 ||

@@ -379,9 +379,9 @@ class ShardedSparseAdam:
         comp = torch.cuda.current_stream(self.dev)
         st = getattr(self, '_stage_streams', None)
         if st is None:
-            st = self._stage_streams = [torch.cuda.Stream(self.dev, priority=-1) for _ in range(3)]
-        xs, ds, ix = st
-        xss, dss, ixs, ms = xs.cuda_stream, ds.cuda_stream, ix.cuda_stream, comp.cuda_stream
+            st = self._stage_streams = [torch.cuda.Stream(self.dev, priority=-1) for _ in range(4)]
+        xs, ds, so, ix = st
+        xss, dss, sos, ixs, ms = xs.cuda_stream, ds.cuda_stream, so.cuda_stream, ix.cuda_stream, comp.cuda_stream
         if pull:
             if n_max > P['n_max']:
                 raise RuntimeError('more lookups than max_lookups_per_rank')
@@ -402,7 +402,7 @@ class ShardedSparseAdam:
             n, S, NRB = n_max, 0, 1
         f = self._fast_state(n)
         cap_u = min(n, f['cap_u'])
-        NB = 3                                                        # buffer sets = stages that hold one (dedup, index, sums)
+        NB = 4                                                        # buffer sets = stages that hold one (dedup, sort, descriptors, sums)
         while len(f['u2']) < NB:
             f['u2'].append(torch.empty_like(f['u'])); f['inv2'].append(torch.empty_like(f['inv'])); f['scr_s2'].append(torch.empty_like(f['scr_s']))
         counts_out = torch.zeros(K, 2, dtype=torch.int64, device=self.dev)
@@ -422,7 +422,7 @@ class ShardedSparseAdam:
             vp = lambda xs: (C.c_void_p * len(xs))(*[int(x) for x in xs])
             ring = getattr(self, '_event_ring', None)
             if ring is None:
-                ring = self._event_ring = [torch.cuda.Event() for _ in range(64)]
+                ring = self._event_ring = [torch.cuda.Event() for _ in range(80)]
                 for e in ring:
                     e.record(comp)                                # materialise the handles
             A = _lib.Staged()
@@ -430,9 +430,9 @@ class ShardedSparseAdam:
             A.lr, A.b1, A.b2, A.eps = self.hyper
             A.pool, A.counts_out = pool_ptr, counts_out.data_ptr()
             keep = [vp([i.data_ptr() for i, _ in batches]), vp([g.data_ptr() for _, g in batches]),
-                    (C.c_int64 * K)(*[i.numel() for i, _ in batches]), vp([xss, dss, ixs, ms]), vp([e.cuda_event for e in ring])]
+                    (C.c_int64 * K)(*[i.numel() for i, _ in batches]), vp([xss, dss, sos, ixs, ms]), vp([e.cuda_event for e in ring])]
             A.ids, A.grads, A.n_k, A.streams, A.events = (C.cast(x, C.c_void_p) for x in keep)
-            for q in range(3):
+            for q in range(4):
                 A.u[q], A.inv[q], A.scr_s[q] = u_ptr[q], inv_ptr[q], ss_ptr[q]
             A.scr_s_bytes, A.scr_u, A.scr_u_bytes = ss_len, su_ptr, su_len
             if self._stage_events:
@@ -507,7 +507,7 @@ class ShardedSparseAdam:
             if trace:
                 ev_begin['i'][k].record(ix)
             src, n_dev = (rs_ptr[b], nrecv_ptr[k & 7]) if pull else (0, 0)
-            _lib.check(L.srm2_reduce_adam_index(u_ptr[q], src, inv_ptr[q], n, n_dev, D, -1, cnt_ptr[k], cap_u, ss_ptr[q], ss_len, ixs),
+            _lib.check(L.srm2_reduce_adam_index(u_ptr[q], src, inv_ptr[q], n, n_dev, D, -1, cnt_ptr[k], cap_u, 0, ss_ptr[q], ss_len, ixs),
                        'reduce_adam_index')
             ev_i[k].record(ix)
 

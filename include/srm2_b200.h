@@ -303,11 +303,17 @@ int srm2_reduce_adam_nd_f32(float* pool, const int64_t* slots, const float* grad
  * lookup (as srm2_unique_inverse_* produces); a row without lookups is left unchanged by the split form.
  *   srm2_reduce_adam_index      src_code == NULL: lookup i's gradient is row i of `grad` given to the apply call;
  *                               src_code != NULL: pull form, see srm2_reduce_adam_pull_f32.
+ *                               part: SRM2_INDEX_ALL, or the two parts as separate calls (again on streams of their own):
+ *                               SRM2_INDEX_SORT (sort by unique row, segment boundaries; needs inv) then
+ *                               SRM2_INDEX_DESCRIPTORS (plan, run descriptors; needs slots and src_code).
  *   srm2_reduce_adam_apply_f32  exactly one of grad (local rows) and peer_grad (host array of `world` device pointers)
  *                               is non-NULL and must match the index call.
  */
+#define SRM2_INDEX_ALL 0
+#define SRM2_INDEX_SORT 1
+#define SRM2_INDEX_DESCRIPTORS 2
 int srm2_reduce_adam_index(const int64_t* slots, const uint32_t* src_code, const int64_t* inv, int64_t n, const int64_t* n_dev,
-                           int64_t D, int64_t n_unique, const int64_t* n_unique_dev, int64_t max_unique, void* scratch,
+                           int64_t D, int64_t n_unique, const int64_t* n_unique_dev, int64_t max_unique, int part, void* scratch,
                            size_t scratch_bytes, srm2_stream_t stream);
 int srm2_reduce_adam_apply_f32(float* pool, const int64_t* slots, const float* grad, const float* const* peer_grad /* host */,
                                int64_t world, int64_t n, const int64_t* n_dev, int64_t D, int64_t n_unique,
@@ -315,18 +321,19 @@ int srm2_reduce_adam_apply_f32(float* pool, const int64_t* slots, const float* g
                                size_t scratch_bytes, srm2_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------------
- * A window of K steps as a pipeline of stages on four streams, enqueued by one call (no counterpart in the reference;
+ * A window of K steps as a pipeline of stages on five streams, enqueued by one call (no counterpart in the reference;
  * the reference's driver is a Python loop).  It issues exactly the calls documented above, in this order per
- * iteration k — sums(k), index(k+1), dedup(k+2), exchange(k+3) — with CUDA events between the stages:
+ * iteration k — sums(k), descriptors(k+1), sort(k+2), dedup(k+3), exchange(k+4) — with CUDA events between the stages:
  *   exchange (world > 1)  srm2_route_plan, _publish, srm2_peer_barrier, [copy of the step's gradients into its slot],
  *                         srm2_route_dispatch_ids, srm2_peer_barrier                       on streams[0]
  *   dedup                 srm2_unique_inverse_nd_i64                                       on streams[1]
- *   index                 srm2_reduce_adam_index                                           on streams[2]
- *   sums                  srm2_reduce_adam_apply_f32 (local rows, or peer_grad at world>1) on streams[3], the caller's
+ *   sort                  srm2_reduce_adam_index(SRM2_INDEX_SORT)                          on streams[2]
+ *   descriptors           srm2_reduce_adam_index(SRM2_INDEX_DESCRIPTORS)                   on streams[3]
+ *   sums                  srm2_reduce_adam_apply_f32 (local rows, or peer_grad at world>1) on streams[4], the caller's
  * A host loop that makes these calls itself gives the same result; this entry point exists because at ~20 launches per
  * step the host, not the GPU, bounds such a loop.  All members are 8 bytes wide.  Pointers marked (host) are host
  * arrays; everything else is device memory.  Nothing is allocated or synchronised; the call returns when the window is
- * enqueued, streams[0..2] have been joined into streams[3].
+ * enqueued, streams[0..3] have been joined into streams[4].
  */
 typedef struct srm2_staged {
   int64_t K, first_step, n, D, n_rows, cap_u;   /* n: lookups per step (world 1), capacity of a receive buffer (world > 1) */
@@ -336,10 +343,10 @@ typedef struct srm2_staged {
   const void* const* ids;                        /* (host) [K] int64 [n_k] */
   const void* const* grads;                      /* (host) [K] float [n_k, D] */
   const int64_t* n_k;                            /* (host) [K] lookups of each step; world 1: all equal n */
-  int64_t* u[3]; int64_t* inv[3]; void* scr_s[3];/* three buffer sets: unique rows [cap_u], inverse [n], reduce scratch */
+  int64_t* u[4]; int64_t* inv[4]; void* scr_s[4];/* four buffer sets: unique rows [cap_u], inverse [n], reduce scratch */
   int64_t scr_s_bytes; void* scr_u; int64_t scr_u_bytes;
-  void* const* streams;                          /* (host) [4] cudaStream_t */
-  void* const* events;                           /* (host) [64] cudaEvent_t without timing: 16 per stage */
+  void* const* streams;                          /* (host) [5] cudaStream_t */
+  void* const* events;                           /* (host) [80] cudaEvent_t without timing: 16 per stage */
   void* const* stage_events;                     /* (host) [2K] or NULL: recorded around the sums of each step */
   /* world > 1 (pull exchange); ignored at world 1 */
   int64_t world, rank, cap, n_recv_bufs, n_slots, timeout_ns;
