@@ -287,7 +287,7 @@ def run_ours(a, world, rank, local_rank):
            'ms_per_step': ms / a.steps, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
            'config': config_dict(a, world, total_rows),
            'roofline': {'bound': 'hbm', 'achieved': achieved, 'peak': peak, 'unit': 'GB/s', 'frac': achieved / peak, 'traffic': traffic,
-                        'kernel': 'srm2_segment_runsum_kernel (fused run sums + Adam; multi-run rows finished in place)',
+                        'kernel': 'srm2_segment_runsum_wide_kernel (fused run sums + Adam; multi-run rows finished in place; N > 1: gradient rows read from their source rank over NVLink)',
                         'peak_source': f'{peak_kind} (MEASURED_PEAKS.json hbm_gbs)' if peak_kind == 'measured' else 'fallback 6650 GB/s',
                         'stage_us': float(np.mean(stage_ms)) * 1e3, 'algorithmic_bytes_per_launch': alg_bytes},
            'e2e': {'value': e_rows_all / (e_ms * 1e-3), 'unit': 'rows/s', 'h2d_bytes_per_step': int(n * 8 + n * D * 4) * world,
@@ -297,6 +297,12 @@ def run_ours(a, world, rank, local_rank):
     out['config']['pipeline'] = ('none: one call after another on one stream' if (world == 1 and a.no_pipeline) else
                                  'ids known one step ahead: dedup, sort and run descriptors of step s+1 run on a side stream while the run-sum + Adam '
                                  'kernel of step s streams the gradient rows')
+    if world > 1 and pull:
+        # the gradient rows of (world-1)/world of the lookups are read from peer memory by the same kernel
+        nv_bytes = lookups_stage * (world - 1) / world * D * 4
+        nv = nv_bytes / (float(np.mean(stage_ms)) * 1e-3) / 1e9
+        out['roofline']['nvlink'] = {'bytes_per_launch': nv_bytes, 'achieved': nv, 'peak': 657.0, 'unit': 'GB/s', 'frac': nv / 657.0,
+                                     'peak_source': 'peer reads with cp.async measured on this pool (own probe, 256 MiB, 2 GPUs)'}
     if world > 1:
         out['config']['exchange'] = ('pull: lookup names by peer stores, gradient rows read from their source rank by the fused reduce+Adam kernel (NVLink)'
                                      if pull else 'fused routing kernel: peer stores over NVLink' if p2p else 'NCCL all-to-all')

@@ -45,6 +45,8 @@ SIGNATURES = {
     'srm2_reduce_adam_index': (C.c_int, [_vp, _vp, _vp, _i64, _vp, _i64, _i64, _vp, _i64, _i32, _vp, _sz, _vp]),
     'srm2_reduce_adam_apply_f32': (C.c_int, [_vp, _vp, _vp, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _f8, _vp, _sz, _vp]),
     'srm2_peer_barrier': (C.c_int, [_vp, _i64, _i64, C.c_uint64, _vp, _i64, _vp]),
+    'srm2_assemble_f32': (C.c_int, [_vp, _i64, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, C.c_uint32, C.c_float, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                                    _i64, _i64, _vp, _i64, _vp, _vp, _i64, _vp, _vp, _i64, _vp]),
     'srm2_staged_steps': (C.c_int, [_vp]),
     'srm2_route_dispatch_ids': (C.c_int, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _sz, _vp]),
     'srm2_reduce_adam_pull_f32': (C.c_int, [_vp, _vp, _vp, _i64, _vp, _vp, _i64, _vp, _i64, _i64, _vp, _i64, _f8, _vp, _sz, _vp]),
@@ -82,6 +84,9 @@ def lib():
             f.restype, f.argtypes = res, args
         _lib = L
     return _lib
+
+
+SRM2_ERR_UNSUPPORTED = -2
 
 
 def check(status, what):

@@ -70,3 +70,41 @@ def replay_rows(rows, logs, offs, steps, cnt, D, K, seed, bound, table, out=None
                                                  _lib.stream_of(rows.device))
         _lib.check(st, 'replay_rows')
     return out
+
+
+def assemble(n, D, pool, hit_pos, hit_slot, N_pos, N_row, L_pos, L_row, logs, L_off, L_steps, L_cnt, K, seed, bound, table,
+             ff, F_pos, sw, S_pos):
+    """The working matrix of a step in one kernel (reference: the body of ELARAExecutor.assemble, srm2/elara.py:479-489).
+    Returns (W [n,D], fullN [n_N,3,D] or None, fullL [n_L,3,D] or None) — the reference returns W, (fullN, fullL, ff).
+    Index tensors are cuda int64; any of the five groups may be empty (pass empty tensors)."""
+    dev = pool.device
+    if not pool.is_cuda:
+        raise RuntimeError('pool must be a CUDA tensor: this library has no CPU path')
+    W = torch.empty(n, D, device=dev)
+    nh, nN, nL, nF, nS = hit_pos.numel(), N_row.numel(), L_row.numel(), F_pos.numel(), S_pos.numel()
+    fullN = torch.empty(nN, 3, D, device=dev) if nN else None
+    fullL = torch.empty(nL, 3, D, device=dev) if nL else None
+    for name, t, dt in (('hit_pos', hit_pos, torch.int64), ('hit_slot', hit_slot, torch.int64), ('N_pos', N_pos, torch.int64),
+                        ('N_row', N_row, torch.int64), ('L_pos', L_pos, torch.int64), ('L_row', L_row, torch.int64),
+                        ('L_off', L_off, torch.int64), ('L_steps', L_steps, torch.int32), ('L_cnt', L_cnt, torch.int32),
+                        ('F_pos', F_pos, torch.int64), ('S_pos', S_pos, torch.int64), ('logs', logs, torch.float32),
+                        ('ff', ff, torch.float32), ('sw', sw, torch.float32), ('pool', pool, torch.float32)):
+        if t.numel() and (t.dtype != dt or not t.is_contiguous() or t.device != dev):
+            raise RuntimeError(f'{name} must be a contiguous {dt} tensor on the device of pool')
+    if hit_slot.numel() != nh or N_pos.numel() != nN or L_pos.numel() != nL or (nL and (L_steps.numel() != nL * K or L_cnt.numel() != nL)):
+        raise RuntimeError('positions and sources of a group must have the same length')
+    p = lambda t: t.data_ptr() if t is not None and t.numel() else 0
+    with torch.cuda.device(dev):
+        st = _lib.lib().srm2_assemble_f32(W.data_ptr(), n, D, p(pool), p(hit_pos), p(hit_slot), nh, p(fullN), p(N_pos), p(N_row), nN,
+                                          _seed32(seed), float(bound), p(fullL), p(L_pos), p(L_row), p(logs), p(L_off), p(L_steps),
+                                          p(L_cnt), nL, K, table.t.data_ptr(), table.t.shape[0], p(ff), p(F_pos), nF, p(sw), p(S_pos), nS,
+                                          _lib.stream_of(dev))
+    if st == _lib.SRM2_ERR_UNSUPPORTED:      # odd D / K > 8 / unaligned views: the same result from the separate kernels
+        if nh: W.index_copy_(0, hit_pos, pool[:, 0].index_select(0, hit_slot))
+        if nN: init_rows(N_row, D, seed, bound, out=fullN); W.index_copy_(0, N_pos, fullN[:, 0])
+        if nL: replay_rows(L_row, logs, L_off, L_steps, L_cnt, D, K, seed, bound, table, out=fullL); W.index_copy_(0, L_pos, fullL[:, 0])
+        if nF: W.index_copy_(0, F_pos, ff[:, 0])
+        if nS: W.index_copy_(0, S_pos, sw)
+        return W, fullN, fullL
+    _lib.check(st, 'assemble')
+    return W, fullN, fullL

@@ -321,6 +321,26 @@ int srm2_reduce_adam_apply_f32(float* pool, const int64_t* slots, const float* g
                                size_t scratch_bytes, srm2_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------------
+ * Fused assemble.  Replaces the body of `ELARAExecutor.assemble` (srm2/elara.py:479-489: torch.empty, init_rows,
+ * replay_rows and ten index_select / index_copy_ calls) by one kernel.  W [n, D] receives one weight row per unique row of
+ * the step from five sources, each given as (positions in W, source):
+ *   resident rows      W[hit_pos[i]] = pool[hit_slot[i], 0]                      pool [C,3,D]
+ *   never-touched rows fullN[i] = init of N_row[i] (as srm2_init_rows_f32);      W[N_pos[i]] = fullN[i,0]
+ *   logged rows        fullL[i] = replay of L_row[i] (as srm2_replay_rows_f32);  W[L_pos[i]] = fullL[i,0]
+ *   staged full rows   W[F_pos[i]] = ff[i,0]                                      ff [n_F,3,D]
+ *   staged weights     W[S_pos[i]] = sw[i]                                        sw [n_S,D]
+ * Positions and rows are int64; L_steps [n_L,K] and L_cnt [n_L] int32.  fullN [n_N,3,D] and fullL [n_L,3,D] are outputs
+ * (the update step scatters them into the pool).  A position outside [0, n) is skipped.  D % 4 == 0, K <= 8 and 16-byte
+ * aligned float buffers; SRM2_ERR_UNSUPPORTED otherwise (use the separate calls then).
+ */
+int srm2_assemble_f32(float* W, int64_t n, int64_t D, const float* pool, const int64_t* hit_pos, const int64_t* hit_slot,
+                      int64_t n_hit, float* fullN, const int64_t* N_pos, const int64_t* N_row, int64_t n_N, uint32_t seed,
+                      float bound, float* fullL, const int64_t* L_pos, const int64_t* L_row, const float* logs,
+                      const int64_t* L_off, const int32_t* L_steps, const int32_t* L_cnt, int64_t n_L, int64_t K,
+                      const float* table, int64_t table_rows, const float* ff, const int64_t* F_pos, int64_t n_F,
+                      const float* sw, const int64_t* S_pos, int64_t n_S, srm2_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------------
  * A window of K steps as a pipeline of stages on five streams, enqueued by one call (no counterpart in the reference;
  * the reference's driver is a Python loop).  It issues exactly the calls documented above, in this order per
  * iteration k — sums(k), descriptors(k+1), sort(k+2), dedup(k+3), exchange(k+4) — with CUDA events between the stages:
