@@ -363,6 +363,36 @@ def kernel_figures(dev, peak):
     out['replay_262144x64_k3'] = fig(timed(lambda: replay_rows(t['rows'], t['logs'], t['offs'], t['steps'], t['cnt'], d, K, 1234, 0.01, table, out=o)),
                                      nbytes, n, 'rows')
     out['replay_262144x64_k3']['note'] = 'bound by fp32 issue (3 IEEE divisions + 1 square root per element and entry), not by HBM'
+    # fused assemble of a step's working matrix: 49,152 unique rows x 128 from a 1 M-row pool: 60 % resident, 10 % never touched,
+    # 20 % logged (1..3 gradients), 5 % staged full rows, 5 % staged weights; next to the same result from the separate calls
+    from elara_b200.gpu_ops import assemble
+    na, da = 49_152, 128
+    ga = np.random.default_rng(7)
+    cls = ga.choice(5, size=na, p=(.6, .1, .2, .05, .05))
+    pos = [torch.from_numpy(np.flatnonzero(cls == q).astype(np.int64)).to(dev) for q in range(5)]
+    cnts = [int(p_.numel()) for p_ in pos]
+    pool_a = torch.randn(1_000_000, 3, da, device=dev)
+    hit_slot = torch.from_numpy(ga.choice(1_000_000, size=cnts[0], replace=False).astype(np.int64)).to(dev)
+    N_row = torch.from_numpy(ga.choice(30_000_000, size=cnts[1], replace=False).astype(np.int64)).to(dev)
+    ca = synth.replay_case(cnts[2], 30_000_000, da, K, 50, 77)
+    ta = {k: torch.from_numpy(v).to(dev) for k, v in ca.items()}
+    ff = torch.randn(cnts[3], 3, da, device=dev); sw = torch.randn(cnts[4], da, device=dev)
+
+    def chain():
+        W = torch.empty(na, da, device=dev)
+        W.index_copy_(0, pos[0], pool_a[:, 0].index_select(0, hit_slot))
+        W.index_copy_(0, pos[1], init_rows(N_row, da, 1234, 0.01)[:, 0])
+        W.index_copy_(0, pos[2], replay_rows(ta['rows'], ta['logs'], ta['offs'], ta['steps'], ta['cnt'], da, K, 1234, 0.01, table)[:, 0])
+        W.index_copy_(0, pos[3], ff[:, 0]); W.index_copy_(0, pos[4], sw)
+        return W
+    fused = lambda: assemble(na, da, pool_a, pos[0], hit_slot, pos[1], N_row, pos[2], ta['rows'], ta['logs'], ta['offs'], ta['steps'], ta['cnt'], K,
+                             1234, 0.01, table, ff, pos[3], sw, pos[4])
+    same = torch.equal(fused()[0].view(torch.int32), chain().view(torch.int32))
+    ab = (na * (da * 4 + 8) + cnts[0] * (da * 4 + 8) + cnts[1] * (3 * da * 4 + 8) + cnts[2] * (3 * da * 4 + 24 + 4 * K) + ca['logs'].nbytes
+          + cnts[3] * da * 4 + cnts[4] * da * 4)
+    out['assemble_49152x128'] = fig(timed(fused), ab, na, 'rows')
+    out['assemble_49152x128'].update({'separate_calls_us': timed(chain), 'equal_to_separate_calls': bool(same),
+                                      'note': 'one launch instead of init_rows + replay_rows + ten index ops (srm2/elara.py:479-489)'})
     # dedup of one batch
     sizes, offs = synth.table_sizes(33_800_000, N_TABLES, seed=SEED)
     ids = torch.from_numpy(synth.zipf_lookups(sizes, offs, 8192, ALPHA, SEED, 1)).to(dev)
