@@ -170,13 +170,13 @@ def run_ours(a, world, rank, local_rank):
     bound = float(np.sqrt(1.0 / sizes.max()))
     eng = ShardedSparseAdam(total_rows, D, world, rank, dev, seed=SEED, bound=bound, hyper=HYP,
                             max_lookups_per_rank=n, group=dist.group.WORLD if world > 1 else None)
-    p2p = eng.enable_p2p(n, pull=(a.exchange == 'pull'), grad_slots=4) if world > 1 and a.exchange != 'nccl' else False
+    p2p = eng.enable_p2p(n, pull=(a.exchange == 'pull'), grad_slots=a.grad_slots) if world > 1 and a.exchange != 'nccl' else False
     pull = bool(p2p) and a.exchange == 'pull'
     nsteps = a.warmup + a.steps
     ids_np = [step_ids(sizes, offs, a.batch, world, rank, s + 1) for s in range(nsteps)]
     ids_dev = [torch.from_numpy(x).to(dev) for x in ids_np]
     gen = torch.Generator(device=dev).manual_seed(SEED + rank)
-    NBUF = 4
+    NBUF = a.grad_slots if world > 1 else 4
     if pull:       # the gradients are produced straight into the peer-visible slots the owners read from
         grads_dev = [eng.grad_slot(b)[:n] for b in range(NBUF)]
         for g in grads_dev:
@@ -501,6 +501,7 @@ def main():
     ap.add_argument('--batch', type=int, default=8192, help='samples per GPU per step (x26 lookups)')
     ap.add_argument('--exchange', default='pull', choices=['pull', 'push', 'nccl'],
                     help='N > 1: how routed lookups reach their owner (pull = rows read over NVLink by the reduce kernel)')
+    ap.add_argument('--grad-slots', type=int, default=8, help='N > 1: peer-visible gradient buffers per rank (pull exchange)')
     ap.add_argument('--no-pipeline', action='store_true', help='N = 1: one step after the other on one stream (no look-ahead on the ids)')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-kernels', action='store_true', help='skip the per-kernel figures (N = 1 only)')
