@@ -48,7 +48,9 @@ SIGNATURES = {
     'srm2_assemble_f32': (C.c_int, [_vp, _i64, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, C.c_uint32, C.c_float, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                     _i64, _i64, _vp, _i64, _vp, _vp, _i64, _vp, _vp, _i64, _vp]),
     'srm2_staged_steps': (C.c_int, [_vp]),
-    'srm2_route_dispatch_ids': (C.c_int, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _sz, _vp]),
+    'srm2_route_dispatch_ids': (C.c_int, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _vp, C.c_uint64, _i64, _vp, _sz, _vp]),
+    'srm2_route_publish_barrier': (C.c_int, [_vp, _vp, _vp, _i64, _i64, C.c_uint64, _vp, _i64, _vp]),
+    'srm2_route_plan_publish': (C.c_int, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, C.c_uint64, _vp, _i64, _vp, _sz, _vp]),
     'srm2_reduce_adam_pull_f32': (C.c_int, [_vp, _vp, _vp, _i64, _vp, _vp, _i64, _vp, _i64, _i64, _vp, _i64, _f8, _vp, _sz, _vp]),
 }
 
@@ -61,7 +63,7 @@ class Staged(C.Structure):
                 [(k, C.c_void_p) for k in ('pool', 'counts_out', 'ids', 'grads', 'n_k')] +
                 [('u', C.c_void_p * 4), ('inv', C.c_void_p * 4), ('scr_s', C.c_void_p * 4)] +
                 [('scr_s_bytes', C.c_int64), ('scr_u', C.c_void_p), ('scr_u_bytes', C.c_int64)] +
-                [(k, C.c_void_p) for k in ('streams', 'events', 'stage_events')] +
+                [(k, C.c_void_p) for k in ('streams', 'events', 'stage_events', 'trace_events')] +
                 [(k, C.c_int64) for k in ('world', 'rank', 'cap', 'n_recv_bufs', 'n_slots', 'timeout_ns')] +
                 [('route_scr', C.c_void_p), ('route_scr_bytes', C.c_int64), ('counts', C.c_void_p), ('err', C.c_void_p), ('n_recv', C.c_void_p)] +
                 [(k, C.c_void_p) for k in ('cmat', 'recv_lid', 'recv_src', 'peer_cmat', 'peer_lid', 'peer_src', 'slot', 'peer_slot',

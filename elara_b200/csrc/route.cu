@@ -50,7 +50,8 @@ static size_t route_layout(int64_t n, int64_t world, char* base, SortBuffers* sb
   size_t off = 0;
   auto take = [&](size_t bytes) { size_t o = off; off = align_up_r(off + bytes, 256); return o; };
   const size_t nn = (size_t)(n > 0 ? n : 1);
-  const size_t o_ka = take(nn * 4), o_va = take(nn * 4), o_h = take(sort_hist_words(tiles, bits) * 4), o_dt = take(sort_dtot_words(tiles, bits, 1) * 4);
+  const size_t o_ka = take(nn * 4), o_va = take(nn * 4), o_h = take(sort_hist_words(tiles, bits) * 4),
+               o_dt = take(sort_dtot_words(tiles, bits, 1) * 4 + 64);      // + the finished-CTA counter of the fused barrier
   if (sb) {
     auto u = [&](size_t o) { return reinterpret_cast<uint32_t*>(base + o); };
     sb->keyA = u(o_ka); sb->valA = u(o_va); sb->keyB = nullptr; sb->valB = nullptr; sb->hist = u(o_h); sb->dtot = u(o_dt); sb->tiles = tiles;
@@ -84,7 +85,7 @@ extern "C" int srm2_route_by_owner(const int64_t* ids, const float* grad, int64_
   const uint32_t *skey = nullptr, *perm = nullptr;
   int launches = 0;
   const uint32_t* hb = nullptr;
-  if (note_cuda(cudaMemsetAsync(sb.dtot, 0, sort_dtot_words(sb.tiles, route_bits(world), 1) * 4, st))) return SRM2_ERR_CUDA;
+  if (note_cuda(cudaMemsetAsync(sb.dtot, 0, sort_dtot_words(sb.tiles, route_bits(world), 1) * 4 + 64, st))) return SRM2_ERR_CUDA;
   const int rc = radix_sort_by_key(ids, n, nullptr, (int)world, 0, route_bits(world), 1, sb, &skey, &perm, &hb, &launches, st);
   if (rc != SRM2_OK) return rc;
   srm2_route_counts_kernel<<<(unsigned)((world + 255) / 256), 256, 0, st>>>(sb.hist, hb, sb.tiles, (int)world, n, out_counts);
@@ -111,6 +112,31 @@ namespace srm2 {
 
 constexpr int kMaxPeers = 16;
 struct PeerPtrs { void* p[kMaxPeers]; };
+
+// Lane r < world of one warp: arrive at rank r, then wait for rank r.  Callers make their earlier stores visible first
+// (__threadfence_system by every writing thread, then a warp or CTA barrier).
+__device__ __forceinline__ void peer_barrier_lane(const PeerPtrs& sig, int rank, int r, unsigned long long ticket, uint32_t* __restrict__ err,
+                                                  long long timeout_ns) {
+  unsigned long long* dst = static_cast<unsigned long long*>(sig.p[r]) + rank;
+  __threadfence_system();
+  asm volatile("st.release.sys.global.u64 [%0], %1;\n" ::"l"(dst), "l"(ticket) : "memory");
+  const unsigned long long* src = static_cast<const unsigned long long*>(sig.p[rank]) + r;
+  long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t0));
+  for (uint32_t it = 0; it < (1u << 27); ++it) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];\n" : "=l"(v) : "l"(src) : "memory");
+    if (v >= ticket) return;
+    if ((it & 15u) == 15u) {
+      long long t1;
+      asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t1));
+      if (t1 - t0 > timeout_ns) break;
+    }
+    __nanosleep(40);
+  }
+  atomicOr(err, 2u);
+}
+
 
 __global__ void srm2_route_publish_kernel(const int64_t* __restrict__ counts, PeerPtrs cmat, int rank, int world) {
   const int d = threadIdx.x;
@@ -312,8 +338,10 @@ srm2_route_dispatch_tma_kernel(const int64_t* __restrict__ ids, const float* __r
 __global__ void __launch_bounds__(256)
 srm2_route_dispatch_ids_kernel(const int64_t* __restrict__ ids, const uint32_t* __restrict__ perm, const uint32_t* __restrict__ owner_sorted,
                                int64_t n, int world, int rank, const int64_t* __restrict__ cmat, PeerPtrs lid_peers, PeerPtrs src_peers,
-                               int64_t cap, int64_t* __restrict__ n_recv, uint32_t* __restrict__ err) {
+                               int64_t cap, int64_t* __restrict__ n_recv, uint32_t* __restrict__ err, PeerPtrs sig, unsigned long long ticket,
+                               long long timeout_ns, uint32_t* __restrict__ done) {
   __shared__ int64_t s_start[kMaxPeers], s_base[kMaxPeers];
+  __shared__ bool s_last;
   if (threadIdx.x < world) {
     const int d = threadIdx.x;
     int64_t start = 0, base = 0;
@@ -338,6 +366,13 @@ srm2_route_dispatch_ids_kernel(const int64_t* __restrict__ ids, const uint32_t* 
     static_cast<int64_t*>(lid_peers.p[d])[r] = id < 0 ? -1 : id / world;
     static_cast<uint32_t*>(src_peers.p[d])[r] = ((uint32_t)rank << 24) | p;
   }
+  if (ticket == 0) return;
+  // the barrier behind the names, by the last CTA to finish: no extra launch, no extra NVLink round trip in the stream
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(done, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (s_last && (int)threadIdx.x < world) peer_barrier_lane(sig, rank, (int)threadIdx.x, ticket, err, timeout_ns);
 }
 
 // ---- barrier across the ranks' GPUs ------------------------------------------------------------------------------------
@@ -349,47 +384,95 @@ srm2_route_dispatch_ids_kernel(const int64_t* __restrict__ ids, const uint32_t* 
 // arrives costs the others the time limit, never the GPU.
 __global__ void srm2_peer_barrier_kernel(PeerPtrs sig, int rank, int world, unsigned long long ticket, uint32_t* __restrict__ err,
                                          long long timeout_ns) {
-  const int r = threadIdx.x;
-  if (r >= world) return;
-  unsigned long long* dst = static_cast<unsigned long long*>(sig.p[r]) + rank;
-  __threadfence_system();
-  asm volatile("st.release.sys.global.u64 [%0], %1;\n" ::"l"(dst), "l"(ticket) : "memory");
-  const unsigned long long* src = static_cast<const unsigned long long*>(sig.p[rank]) + r;
-  long long t0;
-  asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t0));
-  for (uint32_t it = 0; it < (1u << 27); ++it) {
-    unsigned long long v;
-    asm volatile("ld.acquire.sys.global.u64 %0, [%1];\n" : "=l"(v) : "l"(src) : "memory");
-    if (v >= ticket) return;
-    if ((it & 15u) == 15u) {
-      long long t1;
-      asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t1));
-      if (t1 - t0 > timeout_ns) break;
+  if ((int)threadIdx.x < world) peer_barrier_lane(sig, rank, (int)threadIdx.x, ticket, err, timeout_ns);
+}
+
+// counts + publish + barrier in one one-warp kernel (the tail of the plan): lane d takes owner d's count from the sort
+// pass, keeps it in counts[d], stores it into row `rank` of every rank's count matrix, and the warp then goes through the
+// barrier — three dependent launches, two of them bound by an NVLink round trip, become one.
+__global__ void srm2_route_publish_barrier_kernel(const uint32_t* __restrict__ hist, const uint32_t* __restrict__ dtot, int tiles, int64_t n,
+                                                  int64_t* __restrict__ counts, PeerPtrs cmat, PeerPtrs sig, int rank, int world,
+                                                  unsigned long long ticket, uint32_t* __restrict__ err, long long timeout_ns) {
+  const int d = threadIdx.x;
+  if (d < world) {
+    int64_t c = 0;
+    if (n > 0) {
+      if (dtot) c = dtot[d];
+      else c = ((d + 1 < world) ? (int64_t)hist[(int64_t)(d + 1) * tiles] : n) - (int64_t)hist[(int64_t)d * tiles];
     }
-    __nanosleep(40);
+    counts[d] = c;
+    for (int r = 0; r < world; ++r) static_cast<int64_t*>(cmat.p[r])[rank * world + d] = c;
+    __threadfence_system();
   }
-  atomicOr(err, 2u);
+  __syncwarp();
+  if (d < world) peer_barrier_lane(sig, rank, d, ticket, err, timeout_ns);
+}
+
+}  // namespace srm2
+
+namespace srm2 {
+struct PublishArgs { void* const* peer_cmat; void* const* peer_tickets; int64_t rank; uint64_t ticket; uint32_t* err; int64_t timeout_ns; };
+
+// The plan; with `pub` its last kernel also publishes the counts and goes through the barrier.
+static int route_plan_impl(const int64_t* ids, int64_t n, int64_t world, int64_t* out_counts, void* scratch, size_t scratch_bytes,
+                           cudaStream_t st, const PublishArgs* pub) {
+  if (n < 0 || world < 1 || out_counts == nullptr || (n > 0 && ids == nullptr)) return SRM2_ERR_ARG;
+  if (world > kMaxPeers || n >= ((int64_t)1 << 31)) return SRM2_ERR_UNSUPPORTED;
+  if (scratch == nullptr || !aligned16(scratch) || scratch_bytes < route_layout(n, world, nullptr, nullptr)) return SRM2_ERR_SCRATCH;
+  PeerPtrs pc{}, ps{};
+  if (pub) {
+    if (pub->peer_cmat == nullptr || pub->peer_tickets == nullptr || pub->err == nullptr || pub->rank < 0 || pub->rank >= world ||
+        pub->ticket == 0 || pub->timeout_ns <= 0)
+      return SRM2_ERR_ARG;
+    for (int r = 0; r < world; ++r) {
+      if (pub->peer_cmat[r] == nullptr || pub->peer_tickets[r] == nullptr) return SRM2_ERR_ARG;
+      pc.p[r] = pub->peer_cmat[r]; ps.p[r] = pub->peer_tickets[r];
+    }
+  }
+  SortBuffers sb;
+  route_layout(n, world, static_cast<char*>(scratch), &sb);
+  int launches = 0;
+  const uint32_t *skey = nullptr, *perm = nullptr, *dt = nullptr;
+  // digit totals and the finished-CTA counter of the fused barrier start at zero
+  if (note_cuda(cudaMemsetAsync(sb.dtot, 0, sort_dtot_words(sb.tiles, route_bits(world), 1) * 4 + 64, st))) return SRM2_ERR_CUDA;
+  if (n > 0) {
+    const int rc = radix_sort_by_key(ids, n, nullptr, (int)world, 0, route_bits(world), 1, sb, &skey, &perm, &dt, &launches, st);
+    if (rc != SRM2_OK) return rc;
+  }
+  if (pub)
+    srm2_route_publish_barrier_kernel<<<1, 32, 0, st>>>(sb.hist, dt, sb.tiles, n, out_counts, pc, ps, (int)pub->rank, (int)world,
+                                                       (unsigned long long)pub->ticket, pub->err, (long long)pub->timeout_ns);
+  else if (n > 0)
+    srm2_route_counts_kernel<<<(unsigned)((world + 255) / 256), 256, 0, st>>>(sb.hist, dt, sb.tiles, (int)world, n, out_counts);
+  else if (note_cuda(cudaMemsetAsync(out_counts, 0, (size_t)world * 8, st)))
+    return SRM2_ERR_CUDA;
+  return launch_status(launches + 1);
+}
+// The same with the counts already in memory (a plan that ran earlier, possibly on another stream).
+__global__ void srm2_route_publish_counts_barrier_kernel(const int64_t* __restrict__ counts, PeerPtrs cmat, PeerPtrs sig, int rank, int world,
+                                                         unsigned long long ticket, uint32_t* __restrict__ err, long long timeout_ns) {
+  const int d = threadIdx.x;
+  if (d < world) {
+    const int64_t c = counts[d];
+    for (int r = 0; r < world; ++r) static_cast<int64_t*>(cmat.p[r])[rank * world + d] = c;
+    __threadfence_system();
+  }
+  __syncwarp();
+  if (d < world) peer_barrier_lane(sig, rank, d, ticket, err, timeout_ns);
 }
 
 }  // namespace srm2
 
 extern "C" int srm2_route_plan(const int64_t* ids, int64_t n, int64_t world, int64_t* out_counts, void* scratch,
                                size_t scratch_bytes, srm2_stream_t stream) {
-  using namespace srm2;
-  if (n < 0 || world < 1 || out_counts == nullptr || (n > 0 && ids == nullptr)) return SRM2_ERR_ARG;
-  if (world > kMaxPeers || n >= ((int64_t)1 << 31)) return SRM2_ERR_UNSUPPORTED;
-  if (scratch == nullptr || !aligned16(scratch) || scratch_bytes < route_layout(n, world, nullptr, nullptr)) return SRM2_ERR_SCRATCH;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (n == 0) return note_cuda(cudaMemsetAsync(out_counts, 0, (size_t)world * 8, st));
-  SortBuffers sb;
-  route_layout(n, world, static_cast<char*>(scratch), &sb);
-  int launches = 0;
-  const uint32_t *skey = nullptr, *perm = nullptr, *dt = nullptr;
-  if (note_cuda(cudaMemsetAsync(sb.dtot, 0, sort_dtot_words(sb.tiles, route_bits(world), 1) * 4, st))) return SRM2_ERR_CUDA;
-  const int rc = radix_sort_by_key(ids, n, nullptr, (int)world, 0, route_bits(world), 1, sb, &skey, &perm, &dt, &launches, st);
-  if (rc != SRM2_OK) return rc;
-  srm2_route_counts_kernel<<<(unsigned)((world + 255) / 256), 256, 0, st>>>(sb.hist, dt, sb.tiles, (int)world, n, out_counts);
-  return launch_status(launches + 1);
+  return srm2::route_plan_impl(ids, n, world, out_counts, scratch, scratch_bytes, static_cast<cudaStream_t>(stream), nullptr);
+}
+
+extern "C" int srm2_route_plan_publish(const int64_t* ids, int64_t n, int64_t world, int64_t rank, int64_t* out_counts,
+                                       void* const* peer_cmat, void* const* peer_tickets, uint64_t ticket, uint32_t* err,
+                                       int64_t timeout_ns, void* scratch, size_t scratch_bytes, srm2_stream_t stream) {
+  const srm2::PublishArgs pub{peer_cmat, peer_tickets, rank, ticket, err, timeout_ns};
+  return srm2::route_plan_impl(ids, n, world, out_counts, scratch, scratch_bytes, static_cast<cudaStream_t>(stream), &pub);
 }
 
 extern "C" int srm2_route_publish(const int64_t* counts, void* const* peer_cmat, int64_t rank, int64_t world, srm2_stream_t stream) {
@@ -444,24 +527,28 @@ extern "C" int srm2_route_dispatch(const int64_t* ids, const float* grad, int64_
 
 extern "C" int srm2_route_dispatch_ids(const int64_t* ids, int64_t n, int64_t world, int64_t rank, const int64_t* cmat,
                                        void* const* peer_lid, void* const* peer_src, int64_t cap, int64_t* n_recv, uint32_t* err,
-                                       void* scratch, size_t scratch_bytes, srm2_stream_t stream) {
+                                       void* const* peer_tickets, uint64_t ticket, int64_t timeout_ns, void* scratch,
+                                       size_t scratch_bytes, srm2_stream_t stream) {
   using namespace srm2;
   if (n < 0 || world < 1 || world > kMaxPeers || rank < 0 || rank >= world || cap < 0) return SRM2_ERR_ARG;
   if (cmat == nullptr || peer_lid == nullptr || peer_src == nullptr || n_recv == nullptr || err == nullptr) return SRM2_ERR_ARG;
   if (n > 0 && ids == nullptr) return SRM2_ERR_ARG;
   if (n >= ((int64_t)1 << 24)) return SRM2_ERR_UNSUPPORTED;          // the position field of the code
   if (scratch == nullptr || !aligned16(scratch) || scratch_bytes < route_layout(n, world, nullptr, nullptr)) return SRM2_ERR_SCRATCH;
-  PeerPtrs pl{}, ps{};
+  if (peer_tickets == nullptr) ticket = 0;
+  if (ticket != 0 && timeout_ns <= 0) return SRM2_ERR_ARG;
+  PeerPtrs pl{}, ps{}, pt{};
   for (int r = 0; r < world; ++r) {
-    if (peer_lid[r] == nullptr || peer_src[r] == nullptr) return SRM2_ERR_ARG;
-    pl.p[r] = peer_lid[r]; ps.p[r] = peer_src[r];
+    if (peer_lid[r] == nullptr || peer_src[r] == nullptr || (ticket != 0 && peer_tickets[r] == nullptr)) return SRM2_ERR_ARG;
+    pl.p[r] = peer_lid[r]; ps.p[r] = peer_src[r]; pt.p[r] = ticket != 0 ? peer_tickets[r] : nullptr;
   }
   SortBuffers sb;
   route_layout(n, world, static_cast<char*>(scratch), &sb);     // keyA / valA hold the owners and the permutation of srm2_route_plan
   int grid = (int)((n + 255) / 256 < (int64_t)kSMs * 4 ? (n + 255) / 256 : (int64_t)kSMs * 4);
   if (grid < 1) grid = 1;
+  uint32_t* done = sb.dtot + sort_dtot_words(sb.tiles, route_bits(world), 1);      // zeroed by the plan
   srm2_route_dispatch_ids_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(ids, sb.valA, sb.keyA, n, (int)world, (int)rank, cmat, pl, ps, cap,
-                                                                                     n_recv, err);
+                                                                                     n_recv, err, pt, (unsigned long long)ticket, (long long)timeout_ns, done);
   return launch_status(1);
 }
 
@@ -475,5 +562,21 @@ extern "C" int srm2_peer_barrier(void* const* peer_tickets, int64_t rank, int64_
     pp.p[r] = peer_tickets[r];
   }
   srm2_peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pp, (int)rank, (int)world, (unsigned long long)ticket, err, (long long)timeout_ns);
+  return launch_status(1);
+}
+
+extern "C" int srm2_route_publish_barrier(const int64_t* counts, void* const* peer_cmat, void* const* peer_tickets, int64_t rank, int64_t world,
+                                          uint64_t ticket, uint32_t* err, int64_t timeout_ns, srm2_stream_t stream) {
+  using namespace srm2;
+  if (counts == nullptr || peer_cmat == nullptr || peer_tickets == nullptr || err == nullptr || world < 1 || world > kMaxPeers || rank < 0 ||
+      rank >= world || ticket == 0 || timeout_ns <= 0)
+    return SRM2_ERR_ARG;
+  PeerPtrs pc{}, ps{};
+  for (int r = 0; r < world; ++r) {
+    if (peer_cmat[r] == nullptr || peer_tickets[r] == nullptr) return SRM2_ERR_ARG;
+    pc.p[r] = peer_cmat[r]; ps.p[r] = peer_tickets[r];
+  }
+  srm2_route_publish_counts_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(counts, pc, ps, (int)rank, (int)world,
+                                                                                           (unsigned long long)ticket, err, (long long)timeout_ns);
   return launch_status(1);
 }

@@ -698,7 +698,7 @@ static int launch_runsum(const ReduceArgs& a, bool wide, int grid, cudaStream_t 
 
 struct PullSource { const float* const* peer_grad; int world; const uint32_t* src_code; };   // pull mode (fused, runs order only)
 
-// phase bits: kSortPhase (sort, boundaries) and kDescrPhase (plan, run descriptors) together are the index half —
+// phase bits: kSortPhase (radix passes) and kDescrPhase (boundaries, plan, run descriptors) together are the index half —
 // everything that depends on the lookups' row indices only; kSumPhase = the kernels that read gradients and write rows.
 // The parts of a split call communicate through the scratch buffer alone, so they may run on different streams (ordered
 // by events), and the index work of later steps may run while the sum half of this one is still streaming.
@@ -743,6 +743,8 @@ static int segment_pipeline(bool fused, int order, const float* grad, const int6
     const uint32_t* hb = nullptr;
     const int rc = radix_sort_by_key(inv, n, n_dev, /*mod=*/0, cap, s.bits, s.passes, sb, &skey, &spos, &hb, &launches, st);
     if (rc != SRM2_OK) return rc;
+  }
+  if (n > 0 && descr_phase) {
     srm2_segment_bounds_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(skey, n, n_dev, s.seg_start, s.seg_end, cap);
     ++launches;
   }

@@ -3,7 +3,7 @@
 // about twenty launches and an interpreted host loop needs longer to issue them than the GPU needs to run them.
 #include "common.cuh"
 
-static_assert(sizeof(srm2_staged) == 54 * 8, "srm2_staged: every member is 8 bytes wide");
+static_assert(sizeof(srm2_staged) == 55 * 8, "srm2_staged: every member is 8 bytes wide");
 
 namespace srm2 {
 namespace {
@@ -22,6 +22,9 @@ struct Staged {
   }
   cudaEvent_t ev(int stage, int64_t k) const { return static_cast<cudaEvent_t>(a.events[stage * kRing + (int)(k % kRing)]); }
   bool ok() const { return rc == SRM2_OK; }
+  void trace(int64_t k, int stage, int end, cudaStream_t st) {
+    if (a.trace_events) cuda(cudaEventRecord(static_cast<cudaEvent_t>(a.trace_events[k * 10 + stage * 2 + end]), st));
+  }
   void check(int r) { if (rc == SRM2_OK && r != SRM2_OK) rc = r; }
   void cuda(cudaError_t e) { if (rc == SRM2_OK && note_cuda(e)) rc = SRM2_ERR_CUDA; }
   void barrier(cudaStream_t st) {
@@ -29,20 +32,32 @@ struct Staged {
     check(srm2_peer_barrier(a.peer_tickets, a.rank, a.world, (uint64_t)*a.ticket, a.err, a.timeout_ns, st));
   }
 
+  // stage 5 (world > 1): the routing plan of step k — local work, on the descriptor stream, which has room.  Two scratch sets:
+  // the names stage of step k-2 was the last reader of this one.
+  char* route_set(int64_t k) const { return static_cast<char*>(a.route_scr) + (k & 1) * a.route_scr_bytes; }
+  void plan(int64_t k) {
+    if (k >= 2) cuda(cudaStreamWaitEvent(ix, ev(0, k - 2), 0));
+    check(srm2_route_plan(static_cast<const int64_t*>(a.ids[k]), a.n_k[k], a.world, a.counts + (k & 1) * a.world, route_set(k), (size_t)a.route_scr_bytes, ix));
+    cuda(cudaEventRecord(ev(5, k), ix));
+  }
   // stage 0: names of step k to their owners
   void exchange(int64_t k) {
     const int64_t R = a.n_recv_bufs, S = a.n_slots, W = a.world, b = k % R, nk = a.n_k[k];
+    cuda(cudaStreamWaitEvent(xs, ev(5, k), 0));
     if (k >= R) cuda(cudaStreamWaitEvent(xs, ev(3, k - R), 0));          // these receive buffers have been consumed
     if (k >= S) cuda(cudaStreamWaitEvent(xs, ev(4, k - S), 0));          // nobody enters the barrier while it still reads the slot
-    check(srm2_route_plan(static_cast<const int64_t*>(a.ids[k]), nk, W, a.counts, a.route_scr, (size_t)a.route_scr_bytes, xs));
-    check(srm2_route_publish(a.counts, a.peer_cmat + b * W, a.rank, W, xs));
-    barrier(xs);                                                          // count matrices complete, receive buffers and slot free
+    trace(k, 0, 0, xs);
+    // counts to every rank and the first barrier in one kernel: count matrices complete, receive buffers and slot free
+    *a.ticket += 1;
+    check(srm2_route_publish_barrier(a.counts + (k & 1) * W, a.peer_cmat + b * W, a.peer_tickets, a.rank, W, (uint64_t)*a.ticket, a.err, a.timeout_ns, xs));
     float* slot = a.slot[k % S];
     if (a.grads[k] != slot && nk > 0)
       cuda(cudaMemcpyAsync(slot, a.grads[k], (size_t)nk * a.D * 4, cudaMemcpyDeviceToDevice, xs));
+    // names to their owners; the last CTA is the second barrier: every name has arrived, every slot is filled
+    *a.ticket += 1;
     check(srm2_route_dispatch_ids(static_cast<const int64_t*>(a.ids[k]), nk, W, a.rank, a.cmat[b], a.peer_lid + b * W, a.peer_src + b * W, a.cap,
-                                  a.n_recv + (k & 7), a.err, a.route_scr, (size_t)a.route_scr_bytes, xs));
-    barrier(xs);                                                          // every name has arrived, every slot is filled
+                                  a.n_recv + (k & 7), a.err, a.peer_tickets, (uint64_t)*a.ticket, a.timeout_ns, route_set(k), (size_t)a.route_scr_bytes, xs));
+    trace(k, 0, 1, xs);
     cuda(cudaEventRecord(ev(0, k), xs));
   }
   // stage 1
@@ -50,9 +65,11 @@ struct Staged {
     const int64_t q = k % kSets;
     if (pull) cuda(cudaStreamWaitEvent(ds, ev(0, k), 0));
     if (k >= kSets) cuda(cudaStreamWaitEvent(ds, ev(4, k - kSets), 0));  // this buffer set has been consumed
+    trace(k, 1, 0, ds);
     const int64_t* ids = pull ? a.recv_lid[k % a.n_recv_bufs] : static_cast<const int64_t*>(a.ids[k]);
     const int64_t* n_dev = pull ? a.n_recv + (k & 7) : nullptr;
     check(srm2_unique_inverse_nd_i64(ids, a.n, n_dev, a.n_rows, a.u[q], a.cap_u, a.inv[q], a.counts_out + 2 * k, a.scr_u, (size_t)a.scr_u_bytes, ds));
+    trace(k, 1, 1, ds);
     cuda(cudaEventRecord(ev(1, k), ds));
   }
   // stages 2 and 3: the index half of the fused reduce in its two parts
@@ -60,16 +77,19 @@ struct Staged {
     const int64_t q = k % kSets;
     cudaStream_t st = part == SRM2_INDEX_SORT ? so : ix;
     cuda(cudaStreamWaitEvent(st, ev(part == SRM2_INDEX_SORT ? 1 : 2, k), 0));
+    trace(k, part == SRM2_INDEX_SORT ? 2 : 3, 0, st);
     const uint32_t* src = pull ? a.recv_src[k % a.n_recv_bufs] : nullptr;
     const int64_t* n_dev = pull ? a.n_recv + (k & 7) : nullptr;
     check(srm2_reduce_adam_index(a.u[q], src, a.inv[q], a.n, n_dev, a.D, -1, a.counts_out + 2 * k, a.cap_u < a.n ? a.cap_u : a.n, part, a.scr_s[q],
                                  (size_t)a.scr_s_bytes, st));
+    trace(k, part == SRM2_INDEX_SORT ? 2 : 3, 1, st);
     cuda(cudaEventRecord(ev(part == SRM2_INDEX_SORT ? 2 : 3, k), st));
   }
   // stage 4
   void sums(int64_t k) {
     const int64_t q = k % kSets;
     cuda(cudaStreamWaitEvent(ms, ev(3, k), 0));
+    trace(k, 4, 0, ms);
     float sc[8];
     check(srm2_adam_scalars(a.lr, a.b1, a.b2, a.eps, a.first_step + k, sc));
     if (a.stage_events) srm2_stage_events(a.stage_events[2 * k], a.stage_events[2 * k + 1]);
@@ -80,6 +100,7 @@ struct Staged {
     else
       check(srm2_reduce_adam_apply_f32(a.pool, a.u[q], static_cast<const float*>(a.grads[k]), nullptr, 1, a.n, nullptr, a.D, -1, a.counts_out + 2 * k,
                                        cap_u, sc, a.scr_s[q], (size_t)a.scr_s_bytes, ms));
+    trace(k, 4, 1, ms);
     cuda(cudaEventRecord(ev(4, k), ms));
   }
 
@@ -91,7 +112,11 @@ struct Staged {
     for (cudaStream_t st : {xs, ds, so, ix}) cuda(cudaStreamWaitEvent(st, start, 0));
     // prologue; then every iteration enqueues one step of every stage, the oldest first, so that a stage only ever waits
     // for events that have been recorded by then
-    for (int64_t k = 0; k < 4 && k < K && pull && ok(); ++k) exchange(k);
+    for (int64_t k = 0; k < 5 && k < K && pull && ok(); ++k) {           // plan(k) overwrites what exchange(k-2) read
+      plan(k);
+      if (k >= 1 && k - 1 < 4) exchange(k - 1);
+    }
+    if (pull && K <= 4 && K >= 1 && ok()) exchange(K - 1);               // short windows: the last exchange of the prologue
     for (int64_t k = 0; k < 3 && k < K && ok(); ++k) dedup(k);
     for (int64_t k = 0; k < 2 && k < K && ok(); ++k) index(k, SRM2_INDEX_SORT);
     if (K > 0 && ok()) index(0, SRM2_INDEX_DESCRIPTORS);
@@ -101,6 +126,7 @@ struct Staged {
       if (k + 2 < K && ok()) index(k + 2, SRM2_INDEX_SORT);
       if (k + 3 < K && ok()) dedup(k + 3);
       if (pull && k + 4 < K && ok()) exchange(k + 4);
+      if (pull && k + 5 < K && ok()) plan(k + 5);
     }
     if (a.stage_events) srm2_stage_events(nullptr, nullptr);
     // join: what follows on the caller's stream sees the window complete

@@ -386,11 +386,13 @@ class ShardedSparseAdam:
             if n_max > P['n_max']:
                 raise RuntimeError('more lookups than max_lookups_per_rank')
             cap, S = P['cap'], P['slots']
-            scr = ops._scratch(self.dev, L.srm2_route_scratch_bytes(n_max, W), 'route')
-            scr_ptr, scr_len = scr.data_ptr(), scr.numel()
-            counts_ptr, err_ptr = P['counts'].data_ptr(), P['err'].data_ptr()
+            scr_len = (L.srm2_route_scratch_bytes(n_max, W) + 255) // 256 * 256
+            scr = ops._scratch(self.dev, 2 * scr_len, 'route')        # two sets: the plan runs a step ahead of the names
+            scr_ptr = scr.data_ptr()
             if 'n_recv4' not in P:
                 P['n_recv4'] = torch.zeros(8, dtype=torch.int64, device=self.dev)
+                P['counts2'] = torch.zeros(2 * W, dtype=torch.int64, device=self.dev)
+            counts_ptr, err_ptr = P['counts2'].data_ptr(), P['err'].data_ptr()
             NRB = P['nrb']
             cmat_ptr = [P['cmat'][b * W * W:].data_ptr() for b in range(NRB)]
             nrecv_ptr = [P['n_recv4'][q:].data_ptr() for q in range(8)]
@@ -415,14 +417,14 @@ class ShardedSparseAdam:
         pool_ptr = self.pool.data_ptr()
 
         trace = bool(getattr(self, 'trace', False))               # timing events at the stage boundaries (diagnostics)
-        if not trace and not getattr(self, 'host_loop', False):
+        if not getattr(self, 'host_loop', False):
             # the same loop inside the library (srm2_staged_steps): a step is ~20 launches, and issuing them from Python takes
             # longer than running them
             import ctypes as C
             vp = lambda xs: (C.c_void_p * len(xs))(*[int(x) for x in xs])
             ring = getattr(self, '_event_ring', None)
             if ring is None:
-                ring = self._event_ring = [torch.cuda.Event() for _ in range(80)]
+                ring = self._event_ring = [torch.cuda.Event() for _ in range(96)]
                 for e in ring:
                     e.record(comp)                                # materialise the handles
             A = _lib.Staged()
@@ -438,6 +440,14 @@ class ShardedSparseAdam:
             if self._stage_events:
                 keep.append(vp([e.cuda_event for pair in self._stage_events for e in pair]))
                 A.stage_events = C.cast(keep[-1], C.c_void_p)
+            if trace:
+                tev = [torch.cuda.Event(enable_timing=True) for _ in range(K * 10)]
+                t0ev = torch.cuda.Event(enable_timing=True)
+                for e in tev:
+                    e.record(comp)
+                t0ev.record(comp)
+                keep.append(vp([e.cuda_event for e in tev]))
+                A.trace_events = C.cast(keep[-1], C.c_void_p)
             A.world, A.rank = W, self.rank
             if pull:
                 tk = C.c_int64(P['ticket'])
@@ -458,6 +468,11 @@ class ShardedSparseAdam:
                 nr = int(P['n_recv4'][(K - 1) & 7].item())
             else:
                 nr = n
+            if trace:      # microseconds since the start: (begin, end) of exchange, dedup, sort, descriptors, sums per step
+                torch.cuda.synchronize(self.dev)
+                first = 0 if pull else 1
+                self.trace_result = [tuple((t0ev.elapsed_time(tev[k * 10 + 2 * q]) * 1e3, t0ev.elapsed_time(tev[k * 10 + 2 * q + 1]) * 1e3)
+                                           for q in range(first, 5)) for k in range(K)]
             self.last_local_lookups = nr
             self.last_local_lookups_total += nr * K
             return [counts_out[k] for k in range(K)]
@@ -484,7 +499,7 @@ class ShardedSparseAdam:
                 with torch.cuda.stream(xs):
                     self.grad_slot(k)[:nk].copy_(grads, non_blocking=True)
             _lib.check(L.srm2_route_dispatch_ids(ids.data_ptr(), nk, W, self.rank, cmat_ptr[b], P['p_lid'][b], P['p_payload'][b], cap,
-                                                 nrecv_ptr[k & 7], err_ptr, scr_ptr, scr_len, xss), 'route_dispatch_ids')
+                                                 nrecv_ptr[k & 7], err_ptr, 0, 0, 0, scr_ptr, scr_len, xss), 'route_dispatch_ids')
             self._barrier(xss)                                    # every name has arrived, every slot is filled
             ev_x[k].record(xs)
 

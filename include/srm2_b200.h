@@ -274,7 +274,19 @@ int srm2_peer_barrier(void* const* peer_tickets /* host */, int64_t rank, int64_
                       int64_t timeout_ns, srm2_stream_t stream);
 int srm2_route_dispatch_ids(const int64_t* ids, int64_t n, int64_t world, int64_t rank, const int64_t* cmat,
                             void* const* peer_lid /* host */, void* const* peer_src /* host */, int64_t cap, int64_t* n_recv,
-                            uint32_t* err, void* scratch, size_t scratch_bytes, srm2_stream_t stream);
+                            uint32_t* err, void* const* peer_tickets /* host or NULL */, uint64_t ticket, int64_t timeout_ns,
+                            void* scratch, size_t scratch_bytes, srm2_stream_t stream);
+/* The two barriers of the exchange folded into its kernels (fewer launches, fewer NVLink round trips in the stream):
+ *   srm2_route_plan_publish  = srm2_route_plan + srm2_route_publish + srm2_peer_barrier(ticket): the plan's last kernel
+ *                              stores the counts into every rank's matrix and goes through the barrier;
+ *   srm2_route_dispatch_ids with peer_tickets != NULL and ticket != 0: the last CTA to finish goes through the barrier
+ *                              (srm2_peer_barrier semantics, same bounded wait and status bit). */
+/*   srm2_route_publish_barrier = srm2_route_publish + srm2_peer_barrier for counts of a plan that ran earlier. */
+int srm2_route_publish_barrier(const int64_t* counts, void* const* peer_cmat /* host */, void* const* peer_tickets /* host */,
+                               int64_t rank, int64_t world, uint64_t ticket, uint32_t* err, int64_t timeout_ns, srm2_stream_t stream);
+int srm2_route_plan_publish(const int64_t* ids, int64_t n, int64_t world, int64_t rank, int64_t* out_counts,
+                            void* const* peer_cmat /* host */, void* const* peer_tickets /* host */, uint64_t ticket, uint32_t* err,
+                            int64_t timeout_ns, void* scratch, size_t scratch_bytes, srm2_stream_t stream);
 int srm2_reduce_adam_pull_f32(float* pool, const int64_t* slots, const float* const* peer_grad /* host */, int64_t world,
                               const uint32_t* src_code, const int64_t* inv, int64_t n, const int64_t* n_dev, int64_t D,
                               int64_t n_unique, const int64_t* n_unique_dev, int64_t max_unique, const float sc[8] /* host */,
@@ -304,8 +316,8 @@ int srm2_reduce_adam_nd_f32(float* pool, const int64_t* slots, const float* grad
  *   srm2_reduce_adam_index      src_code == NULL: lookup i's gradient is row i of `grad` given to the apply call;
  *                               src_code != NULL: pull form, see srm2_reduce_adam_pull_f32.
  *                               part: SRM2_INDEX_ALL, or the two parts as separate calls (again on streams of their own):
- *                               SRM2_INDEX_SORT (sort by unique row, segment boundaries; needs inv) then
- *                               SRM2_INDEX_DESCRIPTORS (plan, run descriptors; needs slots and src_code).
+ *                               SRM2_INDEX_SORT (sort by unique row; needs inv) then
+ *                               SRM2_INDEX_DESCRIPTORS (segment boundaries, plan, run descriptors; needs slots and src_code).
  *   srm2_reduce_adam_apply_f32  exactly one of grad (local rows) and peer_grad (host array of `world` device pointers)
  *                               is non-NULL and must match the index call.
  */
@@ -343,9 +355,10 @@ int srm2_assemble_f32(float* W, int64_t n, int64_t D, const float* pool, const i
 /* ---------------------------------------------------------------------------------------------------------
  * A window of K steps as a pipeline of stages on five streams, enqueued by one call (no counterpart in the reference;
  * the reference's driver is a Python loop).  It issues exactly the calls documented above, in this order per
- * iteration k — sums(k), descriptors(k+1), sort(k+2), dedup(k+3), exchange(k+4) — with CUDA events between the stages:
- *   exchange (world > 1)  srm2_route_plan, _publish, srm2_peer_barrier, [copy of the step's gradients into its slot],
- *                         srm2_route_dispatch_ids, srm2_peer_barrier                       on streams[0]
+ * iteration k — sums(k), descriptors(k+1), sort(k+2), dedup(k+3), exchange(k+4), plan(k+5) — with CUDA events between:
+ *   plan (world > 1)      srm2_route_plan                                                  on streams[3] (it has room there)
+ *   exchange (world > 1)  srm2_route_publish_barrier, [copy of the step's gradients into its slot],
+ *                         srm2_route_dispatch_ids with the barrier in its last CTA         on streams[0]
  *   dedup                 srm2_unique_inverse_nd_i64                                       on streams[1]
  *   sort                  srm2_reduce_adam_index(SRM2_INDEX_SORT)                          on streams[2]
  *   descriptors           srm2_reduce_adam_index(SRM2_INDEX_DESCRIPTORS)                   on streams[3]
@@ -366,11 +379,14 @@ typedef struct srm2_staged {
   int64_t* u[4]; int64_t* inv[4]; void* scr_s[4];/* four buffer sets: unique rows [cap_u], inverse [n], reduce scratch */
   int64_t scr_s_bytes; void* scr_u; int64_t scr_u_bytes;
   void* const* streams;                          /* (host) [5] cudaStream_t */
-  void* const* events;                           /* (host) [80] cudaEvent_t without timing: 16 per stage */
+  void* const* events;                           /* (host) [96] cudaEvent_t without timing: 16 per stage */
   void* const* stage_events;                     /* (host) [2K] or NULL: recorded around the sums of each step */
+  void* const* trace_events;                     /* (host) [K * 10] or NULL: cudaEvent_t with timing, (begin, end) of the five
+                                                    stages of every step, step-major (diagnostics) */
   /* world > 1 (pull exchange); ignored at world 1 */
   int64_t world, rank, cap, n_recv_bufs, n_slots, timeout_ns;
-  void* route_scr; int64_t route_scr_bytes; int64_t* counts; uint32_t* err; int64_t* n_recv;   /* n_recv: [8] */
+  void* route_scr; int64_t route_scr_bytes; int64_t* counts; uint32_t* err; int64_t* n_recv;   /* two route scratch sets of
+                                                    route_scr_bytes each, counts [2, world], n_recv [8] */
   int64_t* const* cmat;                          /* (host) [n_recv_bufs] this rank's count matrices */
   int64_t* const* recv_lid;                      /* (host) [n_recv_bufs] this rank's receive buffers (ids) */
   uint32_t* const* recv_src;                     /* (host) [n_recv_bufs] ... (codes) */

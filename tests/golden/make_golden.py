@@ -3,7 +3,7 @@
 Run in a container that has the reference checkout (read-only) and the compiled reference sources
 (`python oracle/build_ref.py`):
 
-    python tests/golden/make_golden.py [--ref /root/reference]
+    python tests/golden/make_golden.py [--ref <checkout of the reference>]
 
 What produces each file:
   adam_*.npz       the reference's C++ cpu_adam / adam_scalars (srm2/csrc/srm2_cpu.cpp) AND its Triton

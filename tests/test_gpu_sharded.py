@@ -79,7 +79,7 @@ def test_pull_exchange_emulated_on_one_gpu(oracle, n, D, W):
         _lib.check(L.srm2_route_publish(counts.data_ptr(), arr(cmat), r, W, st), 'publish')
     for r in range(W):
         _lib.check(L.srm2_route_dispatch_ids(t_ids[r].data_ptr(), n, W, r, cmat[r].data_ptr(), arr(rlid), arr(rsrc), cap,
-                                             n_recv[r:].data_ptr(), err.data_ptr(), scr[r].data_ptr(), nb, st), 'dispatch_ids')
+                                             n_recv[r:].data_ptr(), err.data_ptr(), 0, 0, 0, scr[r].data_ptr(), nb, st), 'dispatch_ids')
     assert int(err.item()) == 0
     # single-process expectation
     all_ids = np.concatenate(ids); all_grads = np.concatenate(grads)
