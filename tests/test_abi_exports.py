@@ -47,3 +47,18 @@ def test_no_cpu_path():
         gpu_ops.init_rows(torch.arange(3), 8, 1, 0.01)
     with pytest.raises(AttributeError):
         ops.ext().cpu_adam
+
+
+def test_struct_layouts_match_the_header(tmp_path):
+    """The ctypes mirrors of the header's structs have the size and member offsets a C compiler gives them."""
+    import subprocess
+    from elara_b200 import _lib
+    src = tmp_path / 'layout.c'
+    src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "srm2_b200.h"\n'
+                   'int main(void) { printf("%zu %zu %zu %zu %zu\\n", sizeof(srm2_staged), offsetof(srm2_staged, pool), offsetof(srm2_staged, u),\n'
+                   '                        offsetof(srm2_staged, world), offsetof(srm2_staged, ticket)); return 0; }\n')
+    exe = tmp_path / 'layout'
+    subprocess.check_call(['gcc', '-I', str(ROOT / 'include'), '-o', str(exe), str(src)])
+    size, o_pool, o_u, o_world, o_ticket = map(int, subprocess.check_output([str(exe)]).split())
+    S = _lib.Staged
+    assert (ctypes.sizeof(S), S.pool.offset, S.u.offset, S.world.offset, S.ticket.offset) == (size, o_pool, o_u, o_world, o_ticket)
