@@ -4,11 +4,18 @@ No counterpart in the reference (it is single-GPU); this is the multi-GPU form o
 (srm2/train.py:352 unique, :429 segment-reduce, srm2/ops.py:59-67 Adam) for the row-sharded benchmark configuration.
 
 Per step and rank:
-  1. route    stable grouping of this rank's lookups by owner (row_id mod world) + gather of their gradient rows
-  2. exchange NCCL all-to-all over NVLink: lookup counts, then local row ids and gradient rows
+  1. route    stable grouping of this rank's lookups by owner (row_id mod world)
+  2. exchange one of three forms, chosen by enable_p2p():
+              pull (default)  only the names of the lookups (local row id, source rank and position) are stored into the
+                              owners' receive buffers over NVLink; the owner's fused reduce + Adam kernel then reads every
+                              gradient row from the rank that produced it
+              push            the routing kernel stores ids and gradient rows into the owners' receive buffers
+              NCCL            all-to-all of counts, ids and gathered gradient rows (no peer access needed)
   3. update   dedup -> segment-reduce -> Adam on the local shard (fused, runs-of-10 order)
+run_steps() takes a window of steps whose ids are known ahead and runs it as a pipeline of stages on separate streams
+(see _run_steps_staged); step() is the plain one-step form.
 Bitwise equality with a single process: ranks hold consecutive slices of the global batch, the grouping is stable and
-the all-to-all concatenates in rank order, so an owner sees the lookups of a row in ascending global position — the
+every owner receives its lookups in rank order, so it sees the lookups of a row in ascending global position — the
 order the single-process segment-reduce uses — and it sees all of them, so the runs of 10 are cut identically.
 """
 import torch
@@ -390,12 +397,12 @@ class ShardedSparseAdam:
             scr = ops._scratch(self.dev, 2 * scr_len, 'route')        # two sets: the plan runs a step ahead of the names
             scr_ptr = scr.data_ptr()
             if 'n_recv4' not in P:
-                P['n_recv4'] = torch.zeros(8, dtype=torch.int64, device=self.dev)
+                P['n_recv_ring'] = torch.zeros(8, dtype=torch.int64, device=self.dev)
                 P['counts2'] = torch.zeros(2 * W, dtype=torch.int64, device=self.dev)
             counts_ptr, err_ptr = P['counts2'].data_ptr(), P['err'].data_ptr()
             NRB = P['nrb']
             cmat_ptr = [P['cmat'][b * W * W:].data_ptr() for b in range(NRB)]
-            nrecv_ptr = [P['n_recv4'][q:].data_ptr() for q in range(8)]
+            nrecv_ptr = [P['n_recv_ring'][q:].data_ptr() for q in range(8)]
             rl_ptr = [P['rlid'][b * cap:].data_ptr() for b in range(NRB)]
             rs_ptr = [P['payload'][b * cap:].data_ptr() for b in range(NRB)]
             slot_ptr = [self.grad_slot(q).data_ptr() for q in range(S)]
@@ -455,7 +462,7 @@ class ShardedSparseAdam:
                 keep += [vp(cmat_ptr), vp(rl_ptr), vp(rs_ptr), flat(P['p_cmat']), flat(P['p_lid']), flat(P['p_payload']), vp(slot_ptr),
                          flat(P['p_gbuf']), tk]
                 A.cap, A.n_recv_bufs, A.n_slots, A.timeout_ns = cap, NRB, S, self.barrier_timeout_ns
-                A.route_scr, A.route_scr_bytes, A.counts, A.err, A.n_recv = scr_ptr, scr_len, counts_ptr, err_ptr, P['n_recv4'].data_ptr()
+                A.route_scr, A.route_scr_bytes, A.counts, A.err, A.n_recv = scr_ptr, scr_len, counts_ptr, err_ptr, P['n_recv_ring'].data_ptr()
                 (A.cmat, A.recv_lid, A.recv_src, A.peer_cmat, A.peer_lid, A.peer_src, A.slot, A.peer_slot) = (C.cast(x, C.c_void_p) for x in keep[-9:-1])
                 A.peer_tickets = C.cast(P['p_sig'], C.c_void_p)
                 A.ticket = C.cast(C.pointer(tk), C.c_void_p)
@@ -465,7 +472,7 @@ class ShardedSparseAdam:
             _lib.check(rc, 'staged_steps')
             if pull:
                 self._check_exchange()
-                nr = int(P['n_recv4'][(K - 1) & 7].item())
+                nr = int(P['n_recv_ring'][(K - 1) & 7].item())
             else:
                 nr = n
             if trace:      # microseconds since the start: (begin, end) of exchange, dedup, sort, descriptors, sums per step
@@ -570,7 +577,7 @@ class ShardedSparseAdam:
         if pull:
             self._barrier(ms)                                     # no rank returns while a peer may still read its slots
             self._check_exchange()
-            nr = int(P['n_recv4'][(K - 1) & 7].item())
+            nr = int(P['n_recv_ring'][(K - 1) & 7].item())
         else:
             nr = n
         if trace:      # microseconds since the start: (begin, end) of exchange, dedup, index, sums per step
