@@ -353,6 +353,24 @@ int srm2_assemble_f32(float* W, int64_t n, int64_t D, const float* pool, const i
                       const float* sw, const int64_t* S_pos, int64_t n_S, srm2_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------------
+ * Classification and class partition of a step's unique rows.  Replaces, inside `ELARAPlanner.plan`, the expressions of
+ * srm2/elara.py:214-219 (pool slot, hit, look-ahead membership, admission), :229-239 (code, table threshold, the
+ * 10-way class of srm2/elara.py:32), :243 (class counts) and :258 (order = stable argsort of the class).
+ *   u [n] int64 ascending unique row ids in [0, R);  slot_of, last_seen int32 [R];  code int8 [R];  kthr int8 [T];
+ *   toff int64 [T] ascending table offsets;  u_next / n_next (host arrays): up to 8 ascending look-ahead id lists
+ *   ttl != 0: admit = !hit && last_seen[row] > s, else admit = !hit && in_next;  use_admit != 0: `admit` is an input
+ *   (the reference's second classify() after un-admissions, srm2/elara.py:256);  want_T: the planner's st_mode == 'T'
+ * Outputs: sl int32 [n], in_next / admit bool bytes [n], c int8 [n] (code of each row), cls int8 [n], counts int64 [11]
+ * (classes 0..9; [10] = row ids outside [0, R), classified as C_S without reading anything), order int64 [n].
+ */
+size_t srm2_plan_scratch_bytes(int64_t n);
+int srm2_plan_classify(const int64_t* u, int64_t n, int64_t R, const int32_t* slot_of, const int32_t* last_seen, const int8_t* code,
+                       const int8_t* kthr, const int64_t* toff, int64_t T, const int64_t* const* u_next /* host */,
+                       const int64_t* n_next /* host */, int64_t n_lists, int64_t s, int64_t K, int ttl, int want_T, int use_admit,
+                       int32_t* sl, uint8_t* in_next, uint8_t* admit, int8_t* c, int8_t* cls, int64_t* counts, int64_t* order,
+                       void* scratch, size_t scratch_bytes, srm2_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------------
  * A window of K steps as a pipeline of stages on five streams, enqueued by one call (no counterpart in the reference;
  * the reference's driver is a Python loop).  It issues exactly the calls documented above, in this order per
  * iteration k — sums(k), descriptors(k+1), sort(k+2), dedup(k+3), exchange(k+4), plan(k+5) — with CUDA events between:

@@ -264,3 +264,40 @@ def ref_dir():
         p = HERE / '_ref' / 'srm2_elara_dir.so'
         _REF['dir'] = _load_ext(p, 'srm2_elara_dir') if p.exists() else None
     return _REF['dir']
+
+
+# ------------------------------------------------------------------------------------------------------------
+# Classification and class partition of ELARAPlanner.plan (srm2/elara.py:214-219, 229-239, 243, 258), NumPy restatement.
+C_HIT, C_NADM, C_NAPP, C_NCMP, C_LADM, C_LAPP, C_LCMP, C_FADM, C_FNADM, C_S = range(10)      # srm2/elara.py:32
+
+
+def plan_classify(u, u_nexts, slot_of, last_seen, code, kthr, toff, s, K, ttl, want_T, admit=None):
+    """-> dict(sl, in_next, admit, c, cls, counts[10], order).  `admit` given: classification only (the reference's second
+    call of classify() after un-admissions, srm2/elara.py:256)."""
+    u = np.asarray(u, np.int64)
+    n = u.shape[0]
+    sl = slot_of[u]; hit = sl >= 0                                              # :214
+    in_next = np.zeros(n, bool)
+    for un in u_nexts:                                                          # :216-218
+        j = np.minimum(np.searchsorted(un, u), len(un) - 1)
+        in_next |= un[j] == u
+    if admit is None:
+        admit = ~hit & ((last_seen[u] > s) if ttl else in_next)                 # :219
+    c = code[u]; thr = kthr[np.searchsorted(toff, u, side='right') - 1]         # :229, table_of :167-168
+    isN = c == 0; isL = (c >= 1) & (c <= K); app = c < thr                      # :230
+    wantT = np.full(n, bool(want_T))
+    cls = np.full(n, C_S, np.int8)                                              # :235-239
+    cls = np.where(~isN & ~isL & (admit | wantT), np.where(admit, C_FADM, C_FNADM), cls)
+    cls = np.where(isL, np.where(admit, C_LADM, np.where(app, C_LAPP, C_LCMP)), cls)
+    cls = np.where(isN, np.where(admit, C_NADM, np.where(app, C_NAPP, C_NCMP)), cls)
+    cls = np.where(hit, C_HIT, cls).astype(np.int8)
+    counts = np.bincount(cls.astype(np.int64), minlength=10).astype(np.int64)   # :243
+    order = np.argsort(cls, kind='stable').astype(np.int64)                     # :258
+    return dict(sl=sl.astype(np.int32), in_next=in_next, admit=admit, c=c.astype(np.int8), cls=cls, counts=counts, order=order)
+
+
+def plan_positions(r):
+    """hit_pos, N_pos, L_pos, F_pos, S_pos as the reference slices them out of `order` (srm2/elara.py:259-266)."""
+    b = np.concatenate([[0], np.cumsum(r['counts'])])
+    rng = lambda lo, hi: r['order'][b[lo]:b[hi + 1]]
+    return dict(hit_pos=rng(C_HIT, C_HIT), N_pos=rng(C_NADM, C_NCMP), L_pos=rng(C_LADM, C_LCMP), F_pos=rng(C_FADM, C_FNADM), S_pos=rng(C_S, C_S))

@@ -161,3 +161,30 @@ def test_oracle_vs_compiled_reference(oracle):
             oracle.adam_rows(st, rows, grad, 1e-3, 0.9, 0.999, 1e-8, step, nthreads=4)
             E.cpu_adam(ref, torch.from_numpy(rows), torch.from_numpy(grad), 1e-3, 0.9, 0.999, 1e-8, step, 8)
         assert eq_bits(st, ref.numpy())
+
+
+def plan_golden_steps(golden_dir, name):
+    g = np.load(golden_dir / f'{name}.npz')
+    for s in range(1, int(g['steps']) + 1):
+        if int(g[f's{s}_overflow']):
+            continue
+        nexts = [g[f's{s}_next{q}'] for q in range(int(g[f's{s}_n_next']))]
+        yield g, s, nexts
+
+
+@pytest.mark.parametrize('name', ['plan_ttl_T', 'plan_carry_S'])
+def test_plan_classify_oracle_vs_reference_planner(oracle, golden_dir, name):
+    """The NumPy restatement of the planner's classification reproduces the position lists the reference's own
+    ELARAPlanner.plan returned (tests/golden/make_plan_golden.py)."""
+    seen = set()
+    for g, s, nexts in plan_golden_steps(golden_dir, name):
+        r = oracle.plan_classify(g[f's{s}_u'], nexts, g[f's{s}_slot_of'], g[f's{s}_last_seen'], g[f's{s}_code'], g['kthr'], g['toff'], s,
+                                 int(g['K']), int(g['ttl']), int(g['want_T']))
+        pos = oracle.plan_positions(r)
+        for k, v in pos.items():
+            assert np.array_equal(v, g[f's{s}_{k}']), (name, s, k)
+        assert np.array_equal(r['sl'][pos['hit_pos']].astype(np.int64), g[f's{s}_hit_slot'])
+        assert np.array_equal(r['c'][pos['L_pos']].astype(np.int32), g[f's{s}_L_cnt'])
+        assert int(r['counts'][oracle.C_NADM]) == int(g[f's{s}_N_n_adm']) and int(r['counts'][oracle.C_LADM]) == int(g[f's{s}_L_n_adm'])
+        seen |= set(np.flatnonzero(r['counts']).tolist())
+    assert len(seen) >= 8          # the traces exercise nearly every class
