@@ -393,6 +393,42 @@ def kernel_figures(dev, peak):
     out['assemble_49152x128'] = fig(timed(fused), ab, na, 'rows')
     out['assemble_49152x128'].update({'separate_calls_us': timed(chain), 'equal_to_separate_calls': bool(same),
                                       'note': 'one launch instead of init_rows + replay_rows + ten index ops (srm2/elara.py:479-489)'})
+    # planner classification + class partition of one step: 49,152 unique rows of a 33.8 M-row directory, two look-ahead lists,
+    # next to the same result from library ops (searchsorted / where / bincount / stable argsort, as the reference's plan() does)
+    from elara_b200.planner import plan_classify
+    gp = np.random.default_rng(11)
+    Rp, Cp, Kp = 33_800_000, 8_000_000, 3
+    psizes, poffs = synth.table_sizes(Rp, N_TABLES, seed=SEED)
+    toff_t = torch.from_numpy(poffs).to(dev)
+    kthr_t = torch.full((N_TABLES,), 3, dtype=torch.int8, device=dev)
+    code_t = torch.from_numpy(gp.choice(np.arange(5), size=Rp, p=(.5, .15, .1, .05, .2)).astype(np.int8)).to(dev)
+    slot_t = torch.full((Rp,), -1, dtype=torch.int32, device=dev)
+    slot_t[torch.from_numpy(gp.choice(Rp, size=Cp, replace=False)).to(dev)] = torch.arange(Cp, dtype=torch.int32, device=dev)
+    seen_t = torch.from_numpy(gp.integers(-1, 60, size=Rp).astype(np.int32)).to(dev)
+    up = [torch.from_numpy(np.unique(synth.zipf_lookups(psizes, poffs, 8192, ALPHA, SEED, 50 + q))).to(dev) for q in range(3)]
+
+    def plan_chain():
+        u_ = up[0]
+        sl = slot_t[u_]; hit = sl >= 0
+        in_next = torch.zeros(u_.numel(), dtype=torch.bool, device=dev)
+        for un in up[1:]:
+            in_next |= un[torch.searchsorted(un, u_).clamp(max=un.numel() - 1)] == u_
+        admit = ~hit & (seen_t[u_] > 30)
+        c = code_t[u_]; thr = kthr_t[torch.searchsorted(toff_t, u_, right=True) - 1]
+        isN = c == 0; isL = (c >= 1) & (c <= Kp); app = c < thr
+        cls = torch.full_like(c, 9)
+        cls = torch.where(~isN & ~isL, torch.where(admit, 7, 8).to(torch.int8), cls)
+        cls = torch.where(isL, torch.where(admit, 4, torch.where(app, 5, 6)).to(torch.int8), cls)
+        cls = torch.where(isN, torch.where(admit, 1, torch.where(app, 2, 3)).to(torch.int8), cls)
+        cls = torch.where(hit, torch.zeros_like(cls), cls)
+        return cls, torch.bincount(cls.long(), minlength=10), torch.argsort(cls, stable=True)
+    fusedp = lambda: plan_classify(up[0], up[1:], slot_t, seen_t, code_t, kthr_t, toff_t, 30, Kp, True, True)
+    rp, cp = fusedp(), plan_chain()
+    out['plan_classify_%d_rows' % up[0].numel()] = {
+        'us': timed(fusedp), 'library_op_chain_us': timed(plan_chain), 'kernel_launches': 4,
+        'equal_to_op_chain': bool(torch.equal(rp.cls, cp[0]) and torch.equal(rp.counts, cp[1]) and torch.equal(rp.order, cp[2])),
+        'note': 'classification + counts + stable class partition of a step (srm2/elara.py:214-258); latency-bound integer work'}
+    del code_t, slot_t, seen_t
     # dedup of one batch
     sizes, offs = synth.table_sizes(33_800_000, N_TABLES, seed=SEED)
     ids = torch.from_numpy(synth.zipf_lookups(sizes, offs, 8192, ALPHA, SEED, 1)).to(dev)
