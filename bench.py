@@ -403,7 +403,8 @@ def kernel_figures(dev, peak):
     kthr_t = torch.full((N_TABLES,), 3, dtype=torch.int8, device=dev)
     code_t = torch.from_numpy(gp.choice(np.arange(5), size=Rp, p=(.5, .15, .1, .05, .2)).astype(np.int8)).to(dev)
     slot_t = torch.full((Rp,), -1, dtype=torch.int32, device=dev)
-    slot_t[torch.from_numpy(gp.choice(Rp, size=Cp, replace=False)).to(dev)] = torch.arange(Cp, dtype=torch.int32, device=dev)
+    slot_row_t = torch.from_numpy(gp.choice(Rp, size=Cp, replace=False).astype(np.int64)).to(dev)      # row held by each pool slot
+    slot_t[slot_row_t] = torch.arange(Cp, dtype=torch.int32, device=dev)
     seen_t = torch.from_numpy(gp.integers(-1, 60, size=Rp).astype(np.int32)).to(dev)
     up = [torch.from_numpy(np.unique(synth.zipf_lookups(psizes, poffs, 8192, ALPHA, SEED, 50 + q))).to(dev) for q in range(3)]
 
@@ -428,7 +429,27 @@ def kernel_figures(dev, peak):
         'us': timed(fusedp), 'library_op_chain_us': timed(plan_chain), 'kernel_launches': 4,
         'equal_to_op_chain': bool(torch.equal(rp.cls, cp[0]) and torch.equal(rp.counts, cp[1]) and torch.equal(rp.order, cp[2])),
         'note': 'classification + counts + stable class partition of a step (srm2/elara.py:214-258); latency-bound integer work'}
-    del code_t, slot_t, seen_t
+    # eviction candidates of the same step: 131,072 dynamic slots of the 8 M-slot pool
+    from elara_b200.planner import evict_candidates
+    nd = 131_072
+    pinned_t = torch.zeros(Cp, dtype=torch.bool, device=dev); pinned_t[:Cp - nd] = True
+    dyn_t = (Cp - nd + torch.randperm(nd, device=dev)).to(torch.int64)
+
+    def evict_chain():
+        protect = pinned_t.clone()
+        for un in up[1:]:
+            sn = slot_t[un].long()
+            m = torch.zeros(Cp, dtype=torch.int32, device=dev); m.scatter_add_(0, sn.clamp(min=0), (sn >= 0).to(torch.int32)); protect |= m > 0
+        e = ~protect[dyn_t] & (seen_t[slot_row_t[dyn_t]] <= 30)
+        o = torch.argsort((~e).to(torch.int8), stable=True)
+        return e.sum(), dyn_t[o]
+    fusede = lambda: evict_candidates(up[1:], slot_t, pinned_t, dyn_t, slot_row_t, seen_t, 30, True)
+    re_, ce = fusede(), evict_chain()
+    out['plan_evict_candidates_%d_slots' % nd] = {
+        'us': timed(fusede), 'library_op_chain_us': timed(evict_chain),
+        'equal_to_op_chain': bool(int(re_.n_exp.item()) == int(ce[0].item()) and torch.equal(re_.parted, ce[1])),
+        'note': 'protected slots, expired dynamic slots and their stable split (srm2/elara.py:220-228, 245-246)'}
+    del code_t, slot_t, seen_t, slot_row_t, pinned_t
     # dedup of one batch
     sizes, offs = synth.table_sizes(33_800_000, N_TABLES, seed=SEED)
     ids = torch.from_numpy(synth.zipf_lookups(sizes, offs, 8192, ALPHA, SEED, 1)).to(dev)

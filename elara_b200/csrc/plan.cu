@@ -95,6 +95,49 @@ static size_t plan_layout(int64_t n, char* base, SortBuffers* sb, int64_t** key6
   return off;
 }
 
+// ---- eviction candidates (srm2/elara.py:220-228, 245-246) --------------------------------------------------------------
+// protect = pinned | (slots named by the look-ahead lists); a dynamic slot expires when it is not protected (TTL mode: and
+// its row was last seen at or before step s); the dynamic slots are then split, in order, into expired | kept.
+__global__ void __launch_bounds__(256)
+srm2_plan_protect_kernel(NextLists nx, int64_t total, const int32_t* __restrict__ slot_of, int64_t R, uint8_t* __restrict__ protect, int64_t C) {
+  int64_t t = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (t >= total) return;
+  int q = 0;
+  while (q < nx.count - 1 && t >= nx.n[q]) { t -= nx.n[q]; ++q; }
+  const int64_t r = nx.p[q][t];
+  if (r < 0 || r >= R) return;
+  const int32_t sn = slot_of[r];
+  if (sn >= 0 && sn < C) protect[sn] = 1;                 // every writer stores the same value
+}
+
+__global__ void __launch_bounds__(256)
+srm2_plan_expired_kernel(const int64_t* __restrict__ dyn_slots, int64_t nd, const uint8_t* __restrict__ protect, int64_t C,
+                         const int64_t* __restrict__ slot_row, const int32_t* __restrict__ last_seen, int64_t R, int64_t s, int ttl,
+                         uint8_t* __restrict__ exp_out, int64_t* __restrict__ key_out) {
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= nd) return;
+  const int64_t sl = dyn_slots[i];
+  bool e = false;
+  if (sl >= 0 && sl < C) {
+    e = protect[sl] == 0;
+    if (ttl) {
+      int64_t row = slot_row[sl];
+      if (row < 0) row += R;                               // the reference's negative index wraps
+      e = e && row >= 0 && row < R && (int64_t)last_seen[row] <= s;
+    }
+  }
+  exp_out[i] = e; key_out[i] = e ? 0 : 1;                  // expired slots first, order kept inside both groups
+}
+
+// parted[i] = dyn_slots[order[i]]; n_exp = number of keys 0 (digit total, or the scanned start of digit 1)
+__global__ void __launch_bounds__(256)
+srm2_plan_split_kernel(const int64_t* __restrict__ dyn_slots, const uint32_t* __restrict__ spos, int64_t nd, const uint32_t* __restrict__ dtot,
+                       const uint32_t* __restrict__ hist, int tiles, int64_t* __restrict__ parted, int64_t* __restrict__ n_exp) {
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i == 0) *n_exp = dtot ? (int64_t)dtot[0] : (int64_t)hist[tiles];
+  if (i < nd) parted[i] = dyn_slots[spos[i]];
+}
+
 }  // namespace srm2
 
 extern "C" size_t srm2_plan_scratch_bytes(int64_t n) { return n < 0 ? 0 : srm2::plan_layout(n, nullptr, nullptr, nullptr); }
@@ -133,4 +176,45 @@ extern "C" int srm2_plan_classify(const int64_t* u, int64_t n, int64_t R, const 
   if (rc != SRM2_OK) return rc;
   srm2_plan_order_kernel<<<blocks, 256, 0, st>>>(spos, n, order);
   return launch_status(launches + 1);
+}
+
+extern "C" int srm2_plan_evict_candidates(const int64_t* const* u_next, const int64_t* n_next, int64_t n_lists, const int32_t* slot_of, int64_t R,
+                                          const uint8_t* pinned, int64_t C, const int64_t* dyn_slots, int64_t nd, const int64_t* slot_row,
+                                          const int32_t* last_seen, int64_t s, int ttl, uint8_t* protect, uint8_t* exp, int64_t* n_exp,
+                                          int64_t* parted, void* scratch, size_t scratch_bytes, srm2_stream_t stream) {
+  using namespace srm2;
+  if (n_lists < 0 || n_lists > kMaxNext || R < 0 || C < 0 || nd < 0 || n_exp == nullptr || (n_lists > 0 && (u_next == nullptr || n_next == nullptr)))
+    return SRM2_ERR_ARG;
+  if (C > 0 && (pinned == nullptr || protect == nullptr)) return SRM2_ERR_ARG;
+  if (nd > 0 && (dyn_slots == nullptr || slot_row == nullptr || exp == nullptr || parted == nullptr || (ttl && last_seen == nullptr))) return SRM2_ERR_ARG;
+  if (nd >= ((int64_t)1 << 31)) return SRM2_ERR_UNSUPPORTED;
+  if (scratch == nullptr || !aligned16(scratch) || scratch_bytes < plan_layout(nd, nullptr, nullptr, nullptr)) return SRM2_ERR_SCRATCH;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  NextLists nx{};
+  int64_t total = 0;
+  for (int q = 0; q < (int)n_lists; ++q) {
+    if (n_next[q] < 0 || (n_next[q] > 0 && (u_next[q] == nullptr || slot_of == nullptr))) return SRM2_ERR_ARG;
+    if (n_next[q] == 0) continue;
+    nx.p[nx.count] = u_next[q]; nx.n[nx.count] = n_next[q]; ++nx.count; total += n_next[q];
+  }
+  int launches = 0;
+  if (C > 0 && note_cuda(cudaMemcpyAsync(protect, pinned, (size_t)C, cudaMemcpyDeviceToDevice, st))) return SRM2_ERR_CUDA;
+  if (total > 0 && C > 0) {
+    srm2_plan_protect_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(nx, total, slot_of, R, protect, C);
+    ++launches;
+  }
+  if (nd == 0) {
+    if (note_cuda(cudaMemsetAsync(n_exp, 0, 8, st))) return SRM2_ERR_CUDA;
+    return launch_status(launches);
+  }
+  SortBuffers sb; int64_t* key64 = nullptr;
+  plan_layout(nd, static_cast<char*>(scratch), &sb, &key64);
+  if (note_cuda(cudaMemsetAsync(sb.dtot, 0, sort_dtot_words(sb.tiles, kPlanBits, 1) * 4, st))) return SRM2_ERR_CUDA;
+  const unsigned blocks = (unsigned)((nd + 255) / 256);
+  srm2_plan_expired_kernel<<<blocks, 256, 0, st>>>(dyn_slots, nd, protect, C, slot_row, last_seen, R, s, ttl, exp, key64);
+  const uint32_t *skey = nullptr, *spos = nullptr, *dt = nullptr;
+  const int rc = radix_sort_by_key(key64, nd, nullptr, 0, 2, 1, 1, sb, &skey, &spos, &dt, &launches, st);
+  if (rc != SRM2_OK) return rc;
+  srm2_plan_split_kernel<<<blocks, 256, 0, st>>>(dyn_slots, spos, nd, dt, sb.hist, sb.tiles, parted, n_exp);
+  return launch_status(launches + 2);
 }

@@ -53,3 +53,35 @@ def plan_classify(u, u_nexts, slot_of, last_seen, code, kthr, toff, s, K, ttl, w
                                   order.data_ptr(), scr.data_ptr(), scr.numel(), _lib.stream_of(dev))
     _lib.check(st, 'plan_classify')
     return SimpleNamespace(sl=sl, in_next=in_next, admit=adm, c=c, cls=cls, counts=counts[:10], bad_rows=counts[10:], order=order)
+
+
+def evict_candidates(u_nexts, slot_of, pinned, dyn_slots, slot_row, last_seen, s, ttl):
+    """Eviction candidates of a step (reference: srm2/elara.py:220-228, 245-246).  Returns a namespace of cuda tensors:
+    protect bool [C], exp bool [len(dyn_slots)], n_exp int64 [1] (on the device: the reference reads it with the class counts
+    in its one host sync), parted int64: ev_slot = parted[:n_exp], keep_dyn = parted[n_exp:]."""
+    if not slot_of.is_cuda:
+        raise RuntimeError('slot_of must be a CUDA tensor: this library has no CPU path')
+    dev = slot_of.device
+    if len(u_nexts) > 8:
+        raise RuntimeError('at most 8 look-ahead lists')
+    for name, t, dt in (('slot_of', slot_of, torch.int32), ('pinned', pinned, torch.bool), ('dyn_slots', dyn_slots, torch.int64),
+                        ('slot_row', slot_row, torch.int64), ('last_seen', last_seen, torch.int32),
+                        *[(f'u_nexts[{q}]', t, torch.int64) for q, t in enumerate(u_nexts)]):
+        if t.dtype != dt or not t.is_contiguous() or t.device != dev:
+            raise RuntimeError(f'{name} must be a contiguous {dt} tensor on the device of slot_of')
+    L = _lib.lib()
+    Cn, nd = pinned.numel(), dyn_slots.numel()
+    protect = torch.empty(Cn, dtype=torch.bool, device=dev)
+    exp = torch.empty(nd, dtype=torch.bool, device=dev)
+    n_exp = torch.empty(1, dtype=torch.int64, device=dev)
+    parted = torch.empty(nd, dtype=torch.int64, device=dev)
+    scr = ops._scratch(dev, L.srm2_plan_scratch_bytes(nd), 'plan')
+    nl = len(u_nexts)
+    ptrs = (C.c_void_p * max(nl, 1))(*[t.data_ptr() for t in u_nexts])
+    lens = (C.c_int64 * max(nl, 1))(*[t.numel() for t in u_nexts])
+    with torch.cuda.device(dev):
+        st = L.srm2_plan_evict_candidates(ptrs, lens, nl, slot_of.data_ptr(), slot_of.numel(), pinned.data_ptr(), Cn, dyn_slots.data_ptr(), nd,
+                                          slot_row.data_ptr(), last_seen.data_ptr(), int(s), int(bool(ttl)), protect.data_ptr(), exp.data_ptr(),
+                                          n_exp.data_ptr(), parted.data_ptr(), scr.data_ptr(), scr.numel(), _lib.stream_of(dev))
+    _lib.check(st, 'plan_evict_candidates')
+    return SimpleNamespace(protect=protect, exp=exp, n_exp=n_exp, parted=parted)

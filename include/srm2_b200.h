@@ -363,12 +363,24 @@ int srm2_assemble_f32(float* W, int64_t n, int64_t D, const float* pool, const i
  * Outputs: sl int32 [n], in_next / admit bool bytes [n], c int8 [n] (code of each row), cls int8 [n], counts int64 [11]
  * (classes 0..9; [10] = row ids outside [0, R), classified as C_S without reading anything), order int64 [n].
  */
-size_t srm2_plan_scratch_bytes(int64_t n);
+size_t srm2_plan_scratch_bytes(int64_t n);   /* n = rows of srm2_plan_classify, or dynamic slots of srm2_plan_evict_candidates */
 int srm2_plan_classify(const int64_t* u, int64_t n, int64_t R, const int32_t* slot_of, const int32_t* last_seen, const int8_t* code,
                        const int8_t* kthr, const int64_t* toff, int64_t T, const int64_t* const* u_next /* host */,
                        const int64_t* n_next /* host */, int64_t n_lists, int64_t s, int64_t K, int ttl, int want_T, int use_admit,
                        int32_t* sl, uint8_t* in_next, uint8_t* admit, int8_t* c, int8_t* cls, int64_t* counts, int64_t* order,
                        void* scratch, size_t scratch_bytes, srm2_stream_t stream);
+
+/* Eviction candidates of a step.  Replaces, inside `ELARAPlanner.plan`, srm2/elara.py:220-228 and :245-246.
+ *   protect [C] bool bytes = pinned | (pool slots of the rows in the look-ahead lists);
+ *   exp [nd] = !protect[dyn_slots[i]] (ttl != 0: && last_seen[slot_row[dyn_slots[i]]] <= s);
+ *   parted [nd] int64 = the dynamic slots, expired ones first, order kept inside both groups; *n_exp (device int64) = their
+ *   number: ev_slot = parted[:n_exp], keep_dyn = parted[n_exp:].
+ * pinned [C] bool bytes, dyn_slots [nd] int64, slot_row [C] int64; indices out of range are skipped, not read. */
+int srm2_plan_evict_candidates(const int64_t* const* u_next /* host */, const int64_t* n_next /* host */, int64_t n_lists,
+                               const int32_t* slot_of, int64_t R, const uint8_t* pinned, int64_t C, const int64_t* dyn_slots,
+                               int64_t nd, const int64_t* slot_row, const int32_t* last_seen, int64_t s, int ttl,
+                               uint8_t* protect, uint8_t* exp, int64_t* n_exp, int64_t* parted, void* scratch, size_t scratch_bytes,
+                               srm2_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------------
  * A window of K steps as a pipeline of stages on five streams, enqueued by one call (no counterpart in the reference;

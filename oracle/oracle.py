@@ -301,3 +301,21 @@ def plan_positions(r):
     b = np.concatenate([[0], np.cumsum(r['counts'])])
     rng = lambda lo, hi: r['order'][b[lo]:b[hi + 1]]
     return dict(hit_pos=rng(C_HIT, C_HIT), N_pos=rng(C_NADM, C_NCMP), L_pos=rng(C_LADM, C_LCMP), F_pos=rng(C_FADM, C_FNADM), S_pos=rng(C_S, C_S))
+
+
+def plan_evict_candidates(u_nexts, slot_of, pinned, dyn_slots, slot_row, last_seen, s, ttl):
+    """Eviction candidates of a step (srm2/elara.py:220-228, 245-246): slots named by the look-ahead lists are protected;
+    a dynamic slot expires when it is not protected (TTL mode: and its row's last_seen <= s); the dynamic slots are split,
+    keeping their order, into the expired ones (ev_slot) and the rest (keep_dyn).
+    -> dict(protect bool [C], exp bool [len(dyn_slots)], n_exp, ev_slot, keep_dyn)."""
+    protect = pinned.copy()                                                        # :220
+    for un in u_nexts:                                                             # :221-223
+        sn = slot_of[un].astype(np.int64)
+        protect[sn[sn >= 0]] = True
+    dl = np.asarray(dyn_slots, np.int64)
+    exp = ~protect[dl]                                                             # :226
+    if ttl:
+        exp &= last_seen[slot_row[dl]] <= s                                        # :227-228
+    o = np.argsort(~exp, kind='stable')                                            # :245
+    n_exp = int(exp.sum())
+    return dict(protect=protect, exp=exp, n_exp=n_exp, ev_slot=dl[o[:n_exp]], keep_dyn=dl[o[n_exp:]])

@@ -1,7 +1,7 @@
 """Golden vectors for the classification / partition part of the reference's ELARAPlanner.plan (srm2/elara.py:209-271):
 the planner itself runs on CPU tensors (C++ directory compiled by oracle/build_ref.py); before every plan() call the
-state it reads (slot_of, last_seen, code) and its inputs (u, the look-ahead lists) are recorded, after it the position
-lists of the returned Plan.  Seeded synthetic ids; nothing here is taken from a dataset.
+state it reads (slot_of, last_seen, code, pinned, dyn_slots, slot_row) and its inputs (u, the look-ahead lists) are recorded, after it the position
+lists and eviction candidates of the returned Plan and the planner's new list of dynamic slots.  Seeded synthetic ids; nothing here is taken from a dataset.
 
     python tests/golden/make_plan_golden.py [--ref <checkout of the reference>]
 """
@@ -47,13 +47,16 @@ def gen_plan(elara, out, name, dyn, st_mode, kthr, steps=20, seed=5):
         save[f's{s}_n_next'] = np.array(len(nexts))
         for q, un in enumerate(nexts):
             save[f's{s}_next{q}'] = un.numpy()
-        for k in ('slot_of', 'last_seen', 'code'):
+        for k in ('slot_of', 'last_seen', 'code', 'pinned', 'dyn_slots', 'slot_row'):
             save[f's{s}_{k}'] = getattr(pl, k).numpy().copy()
         overflow0 = pl.stats.get('overflow', 0)
         p = pl.plan(s, U[s0], nexts)
         save[f's{s}_overflow'] = np.array(int(pl.stats.get('overflow', 0) != overflow0))   # un-admission ran: not the plain classification
         for k in ('hit_pos', 'hit_slot', 'N_pos', 'L_pos', 'F_pos', 'S_pos', 'L_cnt'):
             save[f's{s}_{k}'] = getattr(p, k).numpy()
+        save[f's{s}_ev_slot'] = p.ev_slot.numpy()                      # eviction candidates, and what stayed (head of the new list)
+        save[f's{s}_dyn_slots_after'] = pl.dyn_slots.numpy().copy()
+        save[f's{s}_preempt'] = np.array(int(pl.stats.get('preempt', 0)))
         for X in ('N', 'L'):
             save[f's{s}_{X}_n_adm'] = np.array(p.ix[X + '_adm'].numel())
     print(name, {k: v for k, v in pl.stats.items() if v})

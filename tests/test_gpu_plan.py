@@ -73,3 +73,48 @@ def test_plan_classify_counts_bad_rows(dev):
     z32 = np.full(10, -1, np.int32)
     got = run(dev, np.array([-5, 3, 10, 99], np.int64), [], z32, z32, np.zeros(10, np.int8), np.array([1], np.int8), np.array([0], np.int64), 1, 3, 1, 1)
     assert int(got['bad_rows'][0]) == 3 and got['cls'].tolist() == [9, 2, 9, 9] and int(got['counts'].sum()) == 1
+
+
+def run_ev(dev, nexts, slot_of, pinned, dyn_slots, slot_row, last_seen, s, ttl):
+    from elara_b200.planner import evict_candidates
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    r = evict_candidates([t(x) for x in nexts], t(slot_of), t(pinned), t(dyn_slots), t(slot_row), t(last_seen), s, ttl)
+    torch.cuda.synchronize()
+    n_exp = int(r.n_exp.item()); parted = r.parted.cpu().numpy()
+    return dict(protect=r.protect.cpu().numpy(), exp=r.exp.cpu().numpy(), n_exp=n_exp, ev_slot=parted[:n_exp], keep_dyn=parted[n_exp:])
+
+
+def same_ev(got, want):
+    assert got['n_exp'] == want['n_exp']
+    for k in ('protect', 'exp', 'ev_slot', 'keep_dyn'):
+        assert np.array_equal(got[k], want[k]), k
+
+
+@pytest.mark.parametrize('name', ['plan_ttl_T', 'plan_carry_S'])
+def test_evict_candidates_vs_reference_planner(dev, oracle, golden_dir, name):
+    from test_oracle_golden import plan_golden_steps
+    for g, s, nexts in plan_golden_steps(golden_dir, name):
+        a = (nexts, g[f's{s}_slot_of'], g[f's{s}_pinned'], g[f's{s}_dyn_slots'], g[f's{s}_slot_row'], g[f's{s}_last_seen'], s, int(g['ttl']))
+        got = run_ev(dev, *a)
+        same_ev(got, oracle.plan_evict_candidates(*a))
+        if s == 1 or int(g[f's{s}_preempt']) == int(g[f's{s - 1}_preempt']):
+            assert np.array_equal(got['ev_slot'], g[f's{s}_ev_slot']), (name, s)                 # the reference's own choice
+            assert np.array_equal(got['keep_dyn'], g[f's{s}_dyn_slots_after'][:len(got['keep_dyn'])]), (name, s)
+
+
+@pytest.mark.parametrize('nd,ttl,n_lists', [(131_072, 1, 2), (131_072, 0, 3), (5, 1, 0), (0, 1, 1), (2_000_000, 1, 2)])
+def test_evict_candidates_vs_oracle_large(dev, oracle, nd, ttl, n_lists):
+    rng = np.random.default_rng(nd + ttl + n_lists)
+    R, C = 4_000_000, max(2 * nd, 1000)
+    n0 = C - nd
+    slot_row = np.full(C, -1, np.int64); slot_of = np.full(R, -1, np.int32)
+    rows = rng.choice(R, size=C, replace=False).astype(np.int64)
+    slot_row[:] = rows; slot_of[rows] = np.arange(C, dtype=np.int32)
+    pinned = np.zeros(C, bool); pinned[:n0] = True
+    dyn_slots = (n0 + rng.permutation(nd)).astype(np.int64)
+    last_seen = rng.integers(-1, 60, size=R).astype(np.int32)
+    nexts = [np.sort(np.concatenate([rng.choice(rows, size=min(C, 20_000), replace=False), rng.choice(R, size=5000)])).astype(np.int64)
+             for _ in range(n_lists)]
+    nexts = [np.unique(x) for x in nexts]
+    a = (nexts, slot_of, pinned, dyn_slots, slot_row, last_seen, 30, ttl)
+    same_ev(run_ev(dev, *a), oracle.plan_evict_candidates(*a))

@@ -188,3 +188,18 @@ def test_plan_classify_oracle_vs_reference_planner(oracle, golden_dir, name):
         assert int(r['counts'][oracle.C_NADM]) == int(g[f's{s}_N_n_adm']) and int(r['counts'][oracle.C_LADM]) == int(g[f's{s}_L_n_adm'])
         seen |= set(np.flatnonzero(r['counts']).tolist())
     assert len(seen) >= 8          # the traces exercise nearly every class
+
+
+@pytest.mark.parametrize('name', ['plan_ttl_T', 'plan_carry_S'])
+def test_plan_evict_candidates_oracle_vs_reference_planner(oracle, golden_dir, name):
+    """Eviction candidates and surviving dynamic slots as the reference planner chose them (steps without preemption)."""
+    n_ev = 0
+    for g, s, nexts in plan_golden_steps(golden_dir, name):
+        if s > 1 and int(g[f's{s}_preempt']) != int(g[f's{s - 1}_preempt']):
+            continue
+        r = oracle.plan_evict_candidates(nexts, g[f's{s}_slot_of'], g[f's{s}_pinned'], g[f's{s}_dyn_slots'], g[f's{s}_slot_row'], g[f's{s}_last_seen'],
+                                         s, int(g['ttl']))
+        assert np.array_equal(r['ev_slot'], g[f's{s}_ev_slot']), (name, s)
+        assert np.array_equal(r['keep_dyn'], g[f's{s}_dyn_slots_after'][:len(r['keep_dyn'])]), (name, s)
+        n_ev += r['n_exp']
+    assert n_ev > 50
