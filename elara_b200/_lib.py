@@ -51,6 +51,9 @@ SIGNATURES = {
     'srm2_plan_classify': (C.c_int, [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp,
                                      _vp, _vp, _vp, _vp, _sz, _vp]),
     'srm2_plan_evict_candidates': (C.c_int, [_vp, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i32, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    'srm2_plan_pack_scratch_bytes': (_sz, [_i64, _i64]),
+    'srm2_plan_pack': (C.c_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _i64, _vp, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp,
+                                 _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     'srm2_staged_steps': (C.c_int, [_vp]),
     'srm2_route_dispatch_ids': (C.c_int, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _vp, C.c_uint64, _i64, _vp, _sz, _vp]),
     'srm2_route_publish_barrier': (C.c_int, [_vp, _vp, _vp, _i64, _i64, C.c_uint64, _vp, _i64, _vp]),

@@ -138,6 +138,70 @@ srm2_plan_split_kernel(const int64_t* __restrict__ dyn_slots, const uint32_t* __
   if (i < nd) parted[i] = dyn_slots[spos[i]];
 }
 
+// ---- packed eviction outputs and host work lists (srm2/elara.py:389-407) ------------------------------------------------
+// Two stable one-bit partitions (evicted rows going to M first; valid resident-history entries first) and one kernel
+// that writes every list of the plan's single device-to-host copy into one flat buffer.
+struct PackArgs {
+  const int64_t* ev_slot; const uint8_t* rep; const int64_t* evf_slots; const int64_t* evl_ids; const int64_t* ev_dyn; int64_t nev; int K;
+  const int32_t* loc; int64_t n_loc; const int64_t* F_row; int64_t nF; int64_t nFa; const int64_t* S_row; int64_t nS;
+  const int64_t* c_slots; int64_t nc; const int32_t* L_ids; int64_t nLK; const int64_t* a_ids; int64_t na;
+  const int64_t* mat_top; const int64_t* log_top; const int64_t* live;
+  const uint32_t* om; const uint32_t* ol; const unsigned long long* rep_sum;
+  int64_t* evM_slot; int64_t* evl_src; int64_t* flat;
+  int64_t end[9];                                   // exclusive ends of the item ranges: the 7 flat parts, evM_slot, evl_src
+};
+
+__global__ void __launch_bounds__(256)
+srm2_plan_pack_keys_kernel(const uint8_t* __restrict__ rep, int64_t nev, const int64_t* __restrict__ evl_ids, int64_t nevK,
+                           int64_t* __restrict__ key1, int64_t* __restrict__ key2, unsigned long long* __restrict__ rep_sum) {
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  const bool r = i < nev && rep[i] != 0;
+  if (i < nev) key1[i] = r ? 1 : 0;
+  if (i < nevK) key2[i] = evl_ids[i] < 0 ? 1 : 0;
+  const unsigned m = __ballot_sync(0xffffffffu, r);
+  if ((threadIdx.x & 31) == 0 && m) atomicAdd(rep_sum, (unsigned long long)__popc(m));
+}
+
+__device__ __forceinline__ int64_t loc_of(const PackArgs& a, int64_t row) {
+  if (row < 0) row += a.n_loc;                            // the reference's negative index wraps
+  return (row >= 0 && row < a.n_loc) ? (int64_t)a.loc[row] : -1;
+}
+
+__global__ void __launch_bounds__(256)
+srm2_plan_pack_kernel(PackArgs a) {
+  const int64_t t = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (t >= a.end[8]) return;
+  if (t < a.end[0]) { a.flat[t] = loc_of(a, a.S_row[t]); return; }
+  if (t < a.end[1]) { a.flat[t] = loc_of(a, a.F_row[t - a.end[0]]); return; }
+  if (t < a.end[2]) { a.flat[t] = (int64_t)a.L_ids[t - a.end[1]]; return; }
+  if (t < a.end[3]) { a.flat[t] = a.a_ids[t - a.end[2]]; return; }
+  if (t < a.end[4]) {                                      // W_slot: compactions, transient M updates, evictions
+    const int64_t i = t - a.end[3], nFn = a.nF - a.nFa;
+    int64_t v;
+    if (i < a.nc) v = a.c_slots[i];
+    else if (i < a.nc + nFn) v = loc_of(a, a.F_row[a.nFa + (i - a.nc)]);
+    else v = a.evf_slots[a.om[i - a.nc - nFn]];
+    a.flat[t] = v; return;
+  }
+  if (t < a.end[5]) { a.flat[t] = a.evl_ids[a.ol[t - a.end[4]]]; return; }
+  if (t < a.end[6]) {
+    const int q = (int)(t - a.end[5]);
+    a.flat[t] = q == 0 ? *a.mat_top : q == 1 ? *a.log_top : q == 2 ? *a.live : (int64_t)*a.rep_sum;
+    return;
+  }
+  if (t < a.end[7]) { const int64_t i = t - a.end[6]; a.evM_slot[i] = a.ev_slot[a.om[i]]; return; }
+  const int64_t j = t - a.end[7];
+  const uint32_t o = a.ol[j];
+  a.evl_src[j] = a.ev_dyn[o / (uint32_t)a.K] * a.K + (o % (uint32_t)a.K);
+}
+
+static size_t pack_layout(int64_t nev, int64_t K, size_t* o2, size_t* oc) {
+  const size_t l1 = plan_layout(nev, nullptr, nullptr, nullptr), l2 = plan_layout(nev * K, nullptr, nullptr, nullptr);
+  if (o2) *o2 = l1;
+  if (oc) *oc = l1 + l2;
+  return l1 + l2 + 256;
+}
+
 }  // namespace srm2
 
 extern "C" size_t srm2_plan_scratch_bytes(int64_t n) { return n < 0 ? 0 : srm2::plan_layout(n, nullptr, nullptr, nullptr); }
@@ -217,4 +281,58 @@ extern "C" int srm2_plan_evict_candidates(const int64_t* const* u_next, const in
   if (rc != SRM2_OK) return rc;
   srm2_plan_split_kernel<<<blocks, 256, 0, st>>>(dyn_slots, spos, nd, dt, sb.hist, sb.tiles, parted, n_exp);
   return launch_status(launches + 2);
+}
+
+extern "C" size_t srm2_plan_pack_scratch_bytes(int64_t nev, int64_t K) {
+  return (nev < 0 || K < 1) ? 0 : srm2::pack_layout(nev, K, nullptr, nullptr);
+}
+
+extern "C" int srm2_plan_pack(const int64_t* ev_slot, const uint8_t* rep, const int64_t* evf_slots, const int64_t* evl_ids, const int64_t* ev_dyn,
+                              int64_t nev, int64_t K, const int32_t* loc, int64_t n_loc, const int64_t* F_row, int64_t nF, int64_t nFa,
+                              const int64_t* S_row, int64_t nS, const int64_t* c_slots, int64_t nc, const int32_t* L_ids, int64_t nL,
+                              const int64_t* a_ids, int64_t na, const int64_t* mat_top, const int64_t* log_top, const int64_t* live,
+                              int64_t* evM_slot, int64_t* evl_src, int64_t* flat, void* scratch, size_t scratch_bytes, srm2_stream_t stream) {
+  using namespace srm2;
+  if (nev < 0 || K < 1 || K > 64 || n_loc < 0 || nF < 0 || nFa < 0 || nFa > nF || nS < 0 || nc < 0 || nL < 0 || na < 0 || flat == nullptr ||
+      mat_top == nullptr || log_top == nullptr || live == nullptr)
+    return SRM2_ERR_ARG;
+  if (nev > 0 && (ev_slot == nullptr || rep == nullptr || evf_slots == nullptr || evl_ids == nullptr || ev_dyn == nullptr || evM_slot == nullptr ||
+                  evl_src == nullptr))
+    return SRM2_ERR_ARG;
+  if ((nF > 0 && (F_row == nullptr || loc == nullptr)) || (nS > 0 && (S_row == nullptr || loc == nullptr)) || (nc > 0 && c_slots == nullptr) ||
+      (nL > 0 && L_ids == nullptr) || (na > 0 && a_ids == nullptr))
+    return SRM2_ERR_ARG;
+  if (nev * K >= ((int64_t)1 << 31)) return SRM2_ERR_UNSUPPORTED;
+  size_t o2 = 0, oc = 0;
+  if (scratch == nullptr || !aligned16(scratch) || scratch_bytes < pack_layout(nev, K, &o2, &oc)) return SRM2_ERR_SCRATCH;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  char* base = static_cast<char*>(scratch);
+  unsigned long long* rep_sum = reinterpret_cast<unsigned long long*>(base + oc);
+  if (note_cuda(cudaMemsetAsync(rep_sum, 0, 8, st))) return SRM2_ERR_CUDA;
+  int launches = 0;
+  const uint32_t *om = nullptr, *ol = nullptr;
+  if (nev > 0) {
+    SortBuffers sb1, sb2; int64_t *key1 = nullptr, *key2 = nullptr;
+    plan_layout(nev, base, &sb1, &key1);
+    plan_layout(nev * K, base + o2, &sb2, &key2);
+    if (note_cuda(cudaMemsetAsync(sb1.dtot, 0, sort_dtot_words(sb1.tiles, kPlanBits, 1) * 4, st))) return SRM2_ERR_CUDA;
+    if (note_cuda(cudaMemsetAsync(sb2.dtot, 0, sort_dtot_words(sb2.tiles, kPlanBits, 1) * 4, st))) return SRM2_ERR_CUDA;
+    srm2_plan_pack_keys_kernel<<<(unsigned)((nev * K + 255) / 256), 256, 0, st>>>(rep, nev, evl_ids, nev * K, key1, key2, rep_sum);
+    ++launches;
+    const uint32_t *sk = nullptr, *dt = nullptr;
+    int rc = radix_sort_by_key(key1, nev, nullptr, 0, 2, 1, 1, sb1, &sk, &om, &dt, &launches, st);
+    if (rc != SRM2_OK) return rc;
+    rc = radix_sort_by_key(key2, nev * K, nullptr, 0, 2, 1, 1, sb2, &sk, &ol, &dt, &launches, st);
+    if (rc != SRM2_OK) return rc;
+  }
+  PackArgs a{};
+  a.ev_slot = ev_slot; a.rep = rep; a.evf_slots = evf_slots; a.evl_ids = evl_ids; a.ev_dyn = ev_dyn; a.nev = nev; a.K = (int)K;
+  a.loc = loc; a.n_loc = n_loc; a.F_row = F_row; a.nF = nF; a.nFa = nFa; a.S_row = S_row; a.nS = nS; a.c_slots = c_slots; a.nc = nc;
+  a.L_ids = L_ids; a.nLK = nL * K; a.a_ids = a_ids; a.na = na; a.mat_top = mat_top; a.log_top = log_top; a.live = live;
+  a.om = om; a.ol = ol; a.rep_sum = rep_sum; a.evM_slot = evM_slot; a.evl_src = evl_src; a.flat = flat;
+  const int64_t sizes[9] = {nS, nF, nL * K, na, nc + (nF - nFa) + nev, nev * K, 4, nev, nev * K};
+  int64_t e = 0;
+  for (int q = 0; q < 9; ++q) { e += sizes[q]; a.end[q] = e; }
+  srm2_plan_pack_kernel<<<(unsigned)((e + 255) / 256), 256, 0, st>>>(a);
+  return launch_status(launches + 1);
 }

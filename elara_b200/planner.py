@@ -85,3 +85,34 @@ def evict_candidates(u_nexts, slot_of, pinned, dyn_slots, slot_row, last_seen, s
                                           n_exp.data_ptr(), parted.data_ptr(), scr.data_ptr(), scr.numel(), _lib.stream_of(dev))
     _lib.check(st, 'plan_evict_candidates')
     return SimpleNamespace(protect=protect, exp=exp, n_exp=n_exp, parted=parted)
+
+
+def pack(ev_slot, rep, evf_slots, evl_ids, ev_dyn, K, loc, F_row, S_row, nFa, c_slots, L_ids, a_ids, mat_top, log_top, live):
+    """Packed eviction outputs and host work lists of a plan (reference: srm2/elara.py:389-407).  Returns a namespace:
+    evM_slot, evl_src (cuda int64) and `flat` (cuda int64) with `parts`, the (name, length) list in emission order —
+    the reference copies exactly this buffer to the host in its one device-to-host copy and slices it there."""
+    dev = loc.device
+    if not loc.is_cuda:
+        raise RuntimeError('loc must be a CUDA tensor: this library has no CPU path')
+    nev, nF, nS, nc, nL, na = ev_slot.numel(), F_row.numel(), S_row.numel(), c_slots.numel(), L_ids.numel() // max(K, 1), a_ids.numel()
+    for name, t, dt in (('ev_slot', ev_slot, torch.int64), ('rep', rep, torch.bool), ('evf_slots', evf_slots, torch.int64),
+                        ('evl_ids', evl_ids, torch.int64), ('ev_dyn', ev_dyn, torch.int64), ('loc', loc, torch.int32), ('F_row', F_row, torch.int64),
+                        ('S_row', S_row, torch.int64), ('c_slots', c_slots, torch.int64), ('L_ids', L_ids, torch.int32), ('a_ids', a_ids, torch.int64),
+                        ('mat_top', mat_top, torch.int64), ('log_top', log_top, torch.int64), ('live', live, torch.int64)):
+        if t.numel() and (t.dtype != dt or not t.is_contiguous() or t.device != dev):
+            raise RuntimeError(f'{name} must be a contiguous {dt} tensor on the device of loc')
+    if rep.numel() != nev or evf_slots.numel() != nev or ev_dyn.numel() != nev or evl_ids.numel() != nev * K:
+        raise RuntimeError('rep, evf_slots, ev_dyn must be [nev] and evl_ids [nev, K]')
+    parts = [('S_slot', nS), ('F_slot', nF), ('L_ids', nL * K), ('A_ids', na), ('W_slot', nc + nF - int(nFa) + nev), ('EVL_ids', nev * K), ('tops', 4)]
+    L = _lib.lib()
+    evM_slot = torch.empty(nev, dtype=torch.int64, device=dev)
+    evl_src = torch.empty(nev * K, dtype=torch.int64, device=dev)
+    flat = torch.empty(sum(n for _, n in parts), dtype=torch.int64, device=dev)
+    scr = ops._scratch(dev, L.srm2_plan_pack_scratch_bytes(nev, K), 'plan_pack')
+    p = lambda t: t.data_ptr() if t.numel() else 0
+    with torch.cuda.device(dev):
+        st = L.srm2_plan_pack(p(ev_slot), p(rep), p(evf_slots), p(evl_ids), p(ev_dyn), nev, K, p(loc), loc.numel(), p(F_row), nF, int(nFa), p(S_row), nS,
+                              p(c_slots), nc, p(L_ids), nL, p(a_ids), na, mat_top.data_ptr(), log_top.data_ptr(), live.data_ptr(),
+                              p(evM_slot), p(evl_src), flat.data_ptr(), scr.data_ptr(), scr.numel(), _lib.stream_of(dev))
+    _lib.check(st, 'plan_pack')
+    return SimpleNamespace(evM_slot=evM_slot, evl_src=evl_src, flat=flat, parts=parts)

@@ -382,6 +382,22 @@ int srm2_plan_evict_candidates(const int64_t* const* u_next /* host */, const in
                                uint8_t* protect, uint8_t* exp, int64_t* n_exp, int64_t* parted, void* scratch, size_t scratch_bytes,
                                srm2_stream_t stream);
 
+/* Packed eviction outputs and host work lists of a plan.  Replaces, inside `ELARAPlanner.plan`, srm2/elara.py:389-407
+ * (two stable argsorts, the gathers behind them, loc lookups and the concatenation for the single device-to-host copy).
+ *   inputs: ev_slot [nev] int64 and the outputs of srm2_dir_a for them: rep [nev] bool bytes, evf_slots [nev], evl_ids
+ *   [nev,K], ev_dyn [nev] int64;  loc int32 [n_loc];  F_row [nF], S_row [nS] int64;  nFa = admitted rows at the head of F_row;
+ *   c_slots [nc], a_ids [na] int64 (srm2_dir_b);  L_ids int32 [nL,K] (srm2_dir_a);  mat_top, log_top, live: device int64.
+ *   outputs: evM_slot [nev] = ev_slot, rows going to M first;  evl_src [nev*K] = rows of the resident-history matrix, valid
+ *   entries first;  flat = S_slot [nS] | F_slot [nF] | L_ids [nL*K] | A_ids [na] | W_slot [nc + nF - nFa + nev] |
+ *   EVL_ids [nev*K] | tops [4] = (mat_top, log_top, live, number of rows going back to L), all int64.
+ */
+size_t srm2_plan_pack_scratch_bytes(int64_t nev, int64_t K);
+int srm2_plan_pack(const int64_t* ev_slot, const uint8_t* rep, const int64_t* evf_slots, const int64_t* evl_ids, const int64_t* ev_dyn,
+                   int64_t nev, int64_t K, const int32_t* loc, int64_t n_loc, const int64_t* F_row, int64_t nF, int64_t nFa,
+                   const int64_t* S_row, int64_t nS, const int64_t* c_slots, int64_t nc, const int32_t* L_ids, int64_t nL,
+                   const int64_t* a_ids, int64_t na, const int64_t* mat_top, const int64_t* log_top, const int64_t* live,
+                   int64_t* evM_slot, int64_t* evl_src, int64_t* flat, void* scratch, size_t scratch_bytes, srm2_stream_t stream);
+
 /* ---------------------------------------------------------------------------------------------------------
  * A window of K steps as a pipeline of stages on five streams, enqueued by one call (no counterpart in the reference;
  * the reference's driver is a Python loop).  It issues exactly the calls documented above, in this order per

@@ -319,3 +319,23 @@ def plan_evict_candidates(u_nexts, slot_of, pinned, dyn_slots, slot_row, last_se
     o = np.argsort(~exp, kind='stable')                                            # :245
     n_exp = int(exp.sum())
     return dict(protect=protect, exp=exp, n_exp=n_exp, ev_slot=dl[o[:n_exp]], keep_dyn=dl[o[n_exp:]])
+
+
+def plan_pack(ev_slot, rep, evf_slots, evl_ids, ev_dyn, K, loc, F_row, S_row, nFa, c_slots, L_ids, a_ids, tops3):
+    """Packed eviction outputs and host work lists of a plan (srm2/elara.py:389-407).
+    -> dict(evM_slot, evl_src, S_slot, F_slot, L_ids, A_ids, W_slot, EVL_ids, tops[4])."""
+    nev = len(ev_slot)
+    if nev:
+        om = np.argsort(rep.astype(np.int8), kind='stable')                     # rows going to M first (:393-394)
+        evM_slot = ev_slot[om]; evf = evf_slots[om]
+        flat = evl_ids.reshape(-1)
+        ol = np.argsort((flat < 0).astype(np.int8), kind='stable')              # valid history entries first (:395-397)
+        evl_src = (ev_dyn[:, None] * K + np.arange(K)[None, :]).reshape(-1)[ol]
+        evl = flat[ol]
+    else:
+        evM_slot = ev_slot; evf = evf_slots; evl_src = np.zeros(0, np.int64); evl = evl_ids.reshape(-1)
+    F_slot = loc[F_row].astype(np.int64); S_slot = loc[S_row].astype(np.int64)  # :401
+    W_slot = np.concatenate([c_slots, F_slot[nFa:], evf])                       # :402
+    tops = np.concatenate([np.asarray(tops3, np.int64), [int(rep.sum())]])      # :403
+    return dict(evM_slot=evM_slot, evl_src=evl_src, S_slot=S_slot, F_slot=F_slot, L_ids=L_ids.reshape(-1).astype(np.int64),
+                A_ids=a_ids.astype(np.int64), W_slot=W_slot, EVL_ids=evl.astype(np.int64), tops=tops)

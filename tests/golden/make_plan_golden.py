@@ -34,6 +34,16 @@ def gen_plan(elara, out, name, dyn, st_mode, kthr, steps=20, seed=5):
     pl = elara.ELARAPlanner(R, C, K, 'static', dyn, st_mode, static_rows, L, 'cpu', torch.from_numpy(toff),
                             torch.tensor(kthr, dtype=torch.int8), evict_logs=1, dir_impl='cpp')
     pl.code[static_rows] = pl.MAT
+    rec = {}
+    real = pl.dx
+
+    class Recorder:                                   # the directory calls inside plan(): their outputs feed the packing
+        def elara_dir_a(self, *a):
+            rec['a'] = real.elara_dir_a(*a); return rec['a']
+
+        def elara_dir_b(self, *a):
+            rec['b'] = real.elara_dir_b(*a); return rec['b']
+    pl.dx = Recorder()
     save = {'K': np.array(K), 'ttl': np.array(int(dyn == 'ttl')), 'want_T': np.array(int(st_mode == 'T')), 'steps': np.array(steps),
             'toff': toff, 'kthr': np.array(kthr, np.int8)}
     for j in range(min(steps, L + 1)):
@@ -57,6 +67,19 @@ def gen_plan(elara, out, name, dyn, st_mode, kthr, steps=20, seed=5):
         save[f's{s}_ev_slot'] = p.ev_slot.numpy()                      # eviction candidates, and what stayed (head of the new list)
         save[f's{s}_dyn_slots_after'] = pl.dyn_slots.numpy().copy()
         save[f's{s}_preempt'] = np.array(int(pl.stats.get('preempt', 0)))
+        # packing of the eviction outputs and host work lists (srm2/elara.py:389-407): inputs ...
+        for nm, t in zip(('L_steps', 'L_ids', 'hrec_dyn', 'hrec_j', 'ev_row', 'rep', 'evl_ids', 'evf_slots', 'ev_dyn'), rec['a']):
+            if nm in ('L_ids', 'rep', 'evl_ids', 'evf_slots', 'ev_dyn'):
+                save[f's{s}_pk_{nm}'] = t.numpy().copy()
+        save[f's{s}_pk_a_ids'] = rec['b'][0].numpy().copy(); save[f's{s}_pk_c_slots'] = rec['b'][1].numpy().copy()
+        save[f's{s}_pk_loc'] = pl.loc.numpy().copy()
+        save[f's{s}_pk_tops'] = np.array([int(pl.mat_top), int(pl.log_top), int(pl.live)], np.int64)
+        save[f's{s}_pk_F_row'] = p.F_row.numpy(); save[f's{s}_pk_S_row'] = p.S_row.numpy()
+        save[f's{s}_pk_nFa'] = np.array(p.ix['F_adm'].numel())
+        # ... and outputs
+        save[f's{s}_pk_evM_slot'] = p.evM_slot.numpy(); save[f's{s}_pk_evl_src'] = p.evl_src.numpy()
+        for k_ in ('S_slot', 'F_slot', 'L_ids', 'A_ids', 'W_slot', 'EVL_ids', 'tops'):
+            save[f's{s}_pk_cpu_{k_}'] = p.cpu[k_].numpy().copy()
         for X in ('N', 'L'):
             save[f's{s}_{X}_n_adm'] = np.array(p.ix[X + '_adm'].numel())
     print(name, {k: v for k, v in pl.stats.items() if v})

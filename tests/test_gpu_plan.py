@@ -118,3 +118,48 @@ def test_evict_candidates_vs_oracle_large(dev, oracle, nd, ttl, n_lists):
     nexts = [np.unique(x) for x in nexts]
     a = (nexts, slot_of, pinned, dyn_slots, slot_row, last_seen, 30, ttl)
     same_ev(run_ev(dev, *a), oracle.plan_evict_candidates(*a))
+
+
+def run_pack(dev, ev_slot, rep, evf_slots, evl_ids, ev_dyn, K, loc, F_row, S_row, nFa, c_slots, L_ids, a_ids, tops3):
+    from elara_b200.planner import pack
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    top = [torch.tensor([int(v)], dtype=torch.int64, device=dev) for v in tops3]
+    r = pack(t(ev_slot), t(rep), t(evf_slots), t(evl_ids), t(ev_dyn), K, t(loc), t(F_row), t(S_row), nFa, t(c_slots), t(L_ids), t(a_ids), *top)
+    torch.cuda.synchronize()
+    flat = r.flat.cpu().numpy(); out = dict(evM_slot=r.evM_slot.cpu().numpy(), evl_src=r.evl_src.cpu().numpy()); o = 0
+    for name, n in r.parts:
+        out[name] = flat[o:o + n]; o += n
+    assert o == len(flat)
+    return out
+
+
+@pytest.mark.parametrize('name', ['plan_ttl_T', 'plan_carry_S'])
+def test_plan_pack_vs_reference_planner(dev, oracle, golden_dir, name):
+    from test_oracle_golden import plan_golden_steps, plan_pack_args
+    for g, s, _ in plan_golden_steps(golden_dir, name):
+        got = run_pack(dev, *plan_pack_args(g, s))
+        assert np.array_equal(got['evM_slot'], g[f's{s}_pk_evM_slot']) and np.array_equal(got['evl_src'], g[f's{s}_pk_evl_src']), (name, s)
+        for k in ('S_slot', 'F_slot', 'L_ids', 'A_ids', 'W_slot', 'EVL_ids', 'tops'):
+            assert np.array_equal(got[k], g[f's{s}_pk_cpu_{k}']), (name, s, k)            # the reference's own host lists
+
+
+@pytest.mark.parametrize('nev,K,nF,nS', [(40_000, 3, 3000, 2000), (1, 1, 0, 0), (0, 3, 10, 7), (5000, 5, 0, 1)])
+def test_plan_pack_vs_oracle_large(dev, oracle, nev, K, nF, nS):
+    rng = np.random.default_rng(nev + K + nF)
+    R = 2_000_000
+    loc = rng.integers(-1, 1 << 20, size=R + 1).astype(np.int32)
+    ev_slot = rng.permutation(1 << 20)[:nev].astype(np.int64)
+    rep = rng.random(nev) < 0.4
+    evf_slots = rng.integers(0, 1 << 22, size=nev).astype(np.int64)
+    evl_ids = np.where(rng.random((nev, K)) < 0.5, rng.integers(0, 1 << 24, size=(nev, K)), -1).astype(np.int64)
+    ev_dyn = rng.permutation(1 << 18)[:nev].astype(np.int64) if nev <= (1 << 18) else rng.integers(0, 1 << 18, size=nev).astype(np.int64)
+    F_row = rng.choice(R, size=nF, replace=False).astype(np.int64); S_row = rng.choice(R, size=nS, replace=False).astype(np.int64)
+    nFa = nF // 3
+    c_slots = rng.integers(0, 1 << 22, size=777 if nev else 0).astype(np.int64)
+    L_ids = rng.integers(-1, 1 << 24, size=(1234 if nev else 2, K)).astype(np.int32)
+    a_ids = rng.integers(0, 1 << 24, size=4321 if nev else 0).astype(np.int64)
+    a = (ev_slot, rep, evf_slots, evl_ids, ev_dyn, K, loc, F_row, S_row, nFa, c_slots, L_ids, a_ids, np.array([11, 22, 33]))
+    want = oracle.plan_pack(*a)
+    got = run_pack(dev, *a)
+    for k in want:
+        assert np.array_equal(got[k], want[k]), k

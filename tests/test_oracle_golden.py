@@ -203,3 +203,22 @@ def test_plan_evict_candidates_oracle_vs_reference_planner(oracle, golden_dir, n
         assert np.array_equal(r['keep_dyn'], g[f's{s}_dyn_slots_after'][:len(r['keep_dyn'])]), (name, s)
         n_ev += r['n_exp']
     assert n_ev > 50
+
+
+def plan_pack_args(g, s):
+    return (g[f's{s}_ev_slot'], g[f's{s}_pk_rep'], g[f's{s}_pk_evf_slots'], g[f's{s}_pk_evl_ids'], g[f's{s}_pk_ev_dyn'], int(g['K']), g[f's{s}_pk_loc'],
+            g[f's{s}_pk_F_row'], g[f's{s}_pk_S_row'], int(g[f's{s}_pk_nFa']), g[f's{s}_pk_c_slots'], g[f's{s}_pk_L_ids'], g[f's{s}_pk_a_ids'],
+            g[f's{s}_pk_tops'])
+
+
+@pytest.mark.parametrize('name', ['plan_ttl_T', 'plan_carry_S'])
+def test_plan_pack_oracle_vs_reference_planner(oracle, golden_dir, name):
+    """Packed eviction outputs and host work lists exactly as the reference planner returned them."""
+    n = 0
+    for g, s, _ in plan_golden_steps(golden_dir, name):
+        r = oracle.plan_pack(*plan_pack_args(g, s))
+        assert np.array_equal(r['evM_slot'], g[f's{s}_pk_evM_slot']) and np.array_equal(r['evl_src'], g[f's{s}_pk_evl_src']), (name, s)
+        for k in ('S_slot', 'F_slot', 'L_ids', 'A_ids', 'W_slot', 'EVL_ids', 'tops'):
+            assert np.array_equal(r[k], g[f's{s}_pk_cpu_{k}']), (name, s, k)
+        n += len(r['W_slot'])
+    assert n > 100
