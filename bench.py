@@ -470,7 +470,36 @@ def kernel_figures(dev, peak):
         'us': timed(fusede), 'library_op_chain_us': timed(evict_chain),
         'equal_to_op_chain': bool(int(re_.n_exp.item()) == int(ce[0].item()) and torch.equal(re_.parted, ce[1])),
         'note': 'protected slots, expired dynamic slots and their stable split (srm2/elara.py:220-228, 245-246)'}
-    del code_t, slot_t, seen_t, slot_row_t, pinned_t
+    # packing of a plan's eviction outputs and host work lists: 33,446 evictions with K = 3 history entries each
+    from elara_b200.planner import pack
+    nev = 33_446
+    ev_slot = torch.randperm(Cp, device=dev)[:nev]
+    rep_t = torch.rand(nev, device=dev) < 0.4
+    evf = torch.randint(0, 1 << 22, (nev,), device=dev)
+    evl = torch.where(torch.rand(nev, Kp, device=dev) < 0.5, torch.randint(0, 1 << 24, (nev, Kp), device=dev), torch.full((nev, Kp), -1, device=dev))
+    ev_dyn = torch.randperm(nd, device=dev)[:nev]
+    loc_t = torch.randint(-1, 1 << 22, (Rp + 1,), dtype=torch.int32, device=dev)
+    F_row, S_row = up[1][:3000].contiguous(), up[2][:2000].contiguous()
+    c_sl = torch.randint(0, 1 << 22, (20_000,), device=dev); a_id = torch.randint(0, 1 << 24, (45_000,), device=dev)
+    L_id = torch.randint(-1, 1 << 24, (30_000, Kp), dtype=torch.int32, device=dev)
+    tops = [torch.tensor([v], dtype=torch.int64, device=dev) for v in (11, 22, 33)]
+    kk = torch.arange(Kp, device=dev)
+
+    def pack_chain():
+        om = torch.argsort(rep_t.to(torch.int8), stable=True)
+        evM = ev_slot[om]; evf2 = evf[om]
+        ol = torch.argsort((evl < 0).reshape(-1).to(torch.int8), stable=True)
+        src = (ev_dyn[:, None] * Kp + kk[None, :]).reshape(-1)[ol]
+        F_slot = loc_t[F_row].long(); S_slot = loc_t[S_row].long()
+        W = torch.cat([c_sl, F_slot[1000:], evf2])
+        return evM, src, torch.cat([S_slot, F_slot, L_id.reshape(-1).long(), a_id, W, evl.reshape(-1)[ol], torch.cat(tops + [rep_t.sum().reshape(1)])])
+    fusedk = lambda: pack(ev_slot, rep_t, evf, evl, ev_dyn, Kp, loc_t, F_row, S_row, 1000, c_sl, L_id, a_id, *tops)
+    rk, ck = fusedk(), pack_chain()
+    out['plan_pack_%d_evictions' % nev] = {
+        'us': timed(fusedk), 'library_op_chain_us': timed(pack_chain),
+        'equal_to_op_chain': bool(torch.equal(rk.evM_slot, ck[0]) and torch.equal(rk.evl_src, ck[1]) and torch.equal(rk.flat, ck[2])),
+        'note': 'two stable partitions, gathers and the flat work-list buffer of the plan (srm2/elara.py:389-407)'}
+    del code_t, slot_t, seen_t, slot_row_t, pinned_t, loc_t
     # dedup of one batch
     sizes, offs = synth.table_sizes(33_800_000, N_TABLES, seed=SEED)
     ids = torch.from_numpy(synth.zipf_lookups(sizes, offs, 8192, ALPHA, SEED, 1)).to(dev)
