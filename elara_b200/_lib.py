@@ -19,6 +19,7 @@ SIGNATURES = {
     'srm2_last_cuda_error': (C.c_char_p, []),
     'srm2_launch_count': (C.c_int64, []),
     'srm2_stage_events': (C.c_int, [_vp, _vp]),
+    'srm2_verify_exact': (C.c_int, [_i32, C.c_uint64, C.c_uint64, _i32, _i32, _vp, _vp]),
     'srm2_adam_scalars': (C.c_int, [_f64, _f64, _f64, _f64, _i64, _f8]),
     'srm2_adam_rows_f32': (C.c_int, [_vp, _vp, _i32, _vp, _i64, _i64, _f8, _vp]),
     'srm2_init_rows_f32': (C.c_int, [_vp, _vp, _i64, _i64, _u32, _f32, _vp]),

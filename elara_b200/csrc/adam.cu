@@ -8,6 +8,7 @@
 // traffic per row plus the slot index, no reuse, so it is bound by HBM bandwidth; each thread keeps
 // U*4 independent 16-byte loads in flight.
 #include "common.cuh"
+#include "exact.cuh"
 
 namespace srm2 {
 
@@ -36,10 +37,11 @@ srm2_adam_rows_kernel(float* __restrict__ pool, const SlotT* __restrict__ slots,
       v[u] = *reinterpret_cast<const float4*>(b + 2 * D);
     }
   }
+  const AdamFast fa = adam_fast_prepare(sc);
 #pragma unroll
   for (int u = 0; u < U; ++u) {
     if (base[u] != nullptr) {
-      adam_vec4(w[u], m[u], v[u], g[u], sc);
+      adam_vec4_fast(w[u], m[u], v[u], g[u], fa);
       *reinterpret_cast<float4*>(base[u]) = w[u];
       *reinterpret_cast<float4*>(base[u] + D) = m[u];
       *reinterpret_cast<float4*>(base[u] + 2 * D) = v[u];

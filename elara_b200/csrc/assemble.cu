@@ -9,6 +9,7 @@
 // the five sources are consecutive ranges of the item space, so a warp rarely spans two of them.  Arithmetic of the
 // init and replay rows is the same code as the standalone kernels (common.cuh), hence the same bits.
 #include "common.cuh"
+#include "exact.cuh"
 
 namespace srm2 {
 
@@ -75,7 +76,7 @@ srm2_assemble_kernel(AssembleArgs a) {
     w.z = init_elem(base, 2, rowkey, a.seed, a.bound); w.w = init_elem(base, 3, rowkey, a.seed, a.bound);
 #pragma unroll
     for (int k = 0; k < KMAX; ++k)
-      if (k < c) adam_vec4(w, m, v, g[k], assemble_sc(a.table, a.table_rows, st[k]));
+      if (k < c) { const AdamSc sc = assemble_sc(a.table, a.table_rows, st[k]); adam_vec4_fast(w, m, v, g[k], adam_fast_prepare(sc)); }
     float* b = a.fullL + i * 3 * D + j4 * 4;
     st_stream4(b, w); st_stream4(b + D, m); st_stream4(b + 2 * D, v);
     put(a.L_pos[i], j4, w);

@@ -22,6 +22,7 @@
 //      per long row) and added in order; the only serial part is the fp32 add chain itself.
 // Gradient rows are read exactly once (D*4 bytes per lookup); everything else is small integer traffic.
 #include "common.cuh"
+#include "exact.cuh"
 #include "scan.cuh"
 #include "sort.cuh"
 
@@ -72,7 +73,7 @@ __device__ __forceinline__ void finish_row(const ReduceArgs& a, uint32_t j, int 
     float* b = a.pool + a.slots[j] * (3 * (int64_t)a.D) + j4 * 4;
     float4 w = *reinterpret_cast<const float4*>(b), m = *reinterpret_cast<const float4*>(b + a.D),
            v = *reinterpret_cast<const float4*>(b + 2 * a.D);
-    adam_vec4(w, m, v, g, a.sc);
+    { const AdamSc sc = a.sc; adam_vec4_fast(w, m, v, g, adam_fast_prepare(sc)); }
     *reinterpret_cast<float4*>(b) = w; *reinterpret_cast<float4*>(b + a.D) = m; *reinterpret_cast<float4*>(b + 2 * a.D) = v;
   } else {
     *reinterpret_cast<float4*>(a.out + (int64_t)j * a.D + j4 * 4) = g;
@@ -193,7 +194,7 @@ srm2_segment_descr_kernel(const uint32_t* __restrict__ skey, const uint32_t* __r
 template <bool FUSED>
 __device__ __forceinline__ void finish_loaded(const ReduceArgs& a, float* b, float4 w, float4 m, float4 v, const float4& g) {
   if (FUSED) {
-    adam_vec4(w, m, v, g, a.sc);
+    { const AdamSc sc = a.sc; adam_vec4_fast(w, m, v, g, adam_fast_prepare(sc)); }
     *reinterpret_cast<float4*>(b) = w; *reinterpret_cast<float4*>(b + a.D) = m; *reinterpret_cast<float4*>(b + 2 * a.D) = v;
   } else {
     *reinterpret_cast<float4*>(b) = g;
@@ -291,6 +292,8 @@ srm2_segment_runsum_kernel(ReduceArgs a) {
   if (threadIdx.x == 0) s_nlong = 0;
   __syncthreads();
   float4* mine = stage + threadIdx.x;
+  const AdamSc sc = a.sc;
+  const AdamFast fa = adam_fast_prepare(sc);
   const int64_t items = (int64_t)a.counters->n_runs * a.lpr;
   const int lane = threadIdx.x & 31;
   const unsigned gmask = a.lpr >= 32 ? 0xffffffffu : (((1u << a.lpr) - 1u) << (lane & ~(a.lpr - 1)));
@@ -338,7 +341,7 @@ srm2_segment_runsum_kernel(ReduceArgs a) {
       const float4 g = add4(make_float4(0.f, 0.f, 0.f, 0.f), acc);
       if (FUSED) {
         float4 w = mine[kRun * kRunThreads], m = mine[(kRun + 1) * kRunThreads], v = mine[(kRun + 2) * kRunThreads];
-        adam_vec4(w, m, v, g, a.sc);
+        adam_vec4_fast(w, m, v, g, fa);
         *reinterpret_cast<float4*>(b) = w; *reinterpret_cast<float4*>(b + a.D) = m; *reinterpret_cast<float4*>(b + 2 * a.D) = v;
       } else {
         *reinterpret_cast<float4*>(b) = g;
@@ -400,6 +403,8 @@ srm2_segment_runsum_wide_kernel(ReduceArgs a) {
   if (threadIdx.x == 0) s_nlong = 0;
   __syncthreads();
   float4* mine = stage + threadIdx.x;
+  const AdamSc sc = a.sc;
+  const AdamFast fa = adam_fast_prepare(sc);
   const int64_t items = (int64_t)a.counters->n_runs * a.lpr;
   const int lane = threadIdx.x & 31;
   const unsigned gmask = a.lpr >= 32 ? 0xffffffffu : (((1u << a.lpr) - 1u) << (lane & ~(a.lpr - 1)));
@@ -441,7 +446,7 @@ srm2_segment_runsum_wide_kernel(ReduceArgs a) {
         float* b = e == 0 ? b0 : (e == 1 ? b1 : b2);
         const float4 g = add4(zero, add4(zero, mine[(4 * e) * kRunThreads]));     // the run sum from +0, then the row sum from +0
         float4 w = mine[(4 * e + 1) * kRunThreads], m = mine[(4 * e + 2) * kRunThreads], v = mine[(4 * e + 3) * kRunThreads];
-        adam_vec4(w, m, v, g, a.sc);
+        adam_vec4_fast(w, m, v, g, fa);
         *reinterpret_cast<float4*>(b) = w; *reinterpret_cast<float4*>(b + a.D) = m; *reinterpret_cast<float4*>(b + 2 * a.D) = v;
       }
       if (t < end) p0 = load_pos(d0, run_of(t));
@@ -483,7 +488,7 @@ srm2_segment_runsum_wide_kernel(ReduceArgs a) {
       const float4 g = add4(make_float4(0.f, 0.f, 0.f, 0.f), acc);
       if (FUSED) {
         float4 w = mine[kRun * kRunThreads], m = mine[(kRun + 1) * kRunThreads], v = mine[(kRun + 2) * kRunThreads];
-        adam_vec4(w, m, v, g, a.sc);
+        adam_vec4_fast(w, m, v, g, fa);
         *reinterpret_cast<float4*>(b) = w; *reinterpret_cast<float4*>(b + a.D) = m; *reinterpret_cast<float4*>(b + 2 * a.D) = v;
       } else {
         *reinterpret_cast<float4*>(b) = g;

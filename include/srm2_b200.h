@@ -44,6 +44,27 @@ int64_t srm2_launch_count(void);
  * to clear.  No counterpart in the reference. */
 int srm2_stage_events(void* begin /* cudaEvent_t */, void* end /* cudaEvent_t */);
 
+/* Self-check of the library's short correctly-rounded fp32 division / square-root sequences (the arithmetic inside the
+ * Adam, replay and fused reduce kernels) against the compiler's IEEE operations, run on the current GPU.  No
+ * counterpart in the reference (its kernels use the compiler's operations directly); used by the tests.
+ *   what     SRM2_VERIFY_SQRT: every float bit pattern in [lo, hi) inside the guarded range;
+ *            SRM2_VERIFY_DIV_HARD: divisor significands 2^23 + [lo, hi), every dividend whose quotient lies within `param`
+ *            odd steps of a rounding midpoint (divisors with more than 8 trailing zero bits are left to DIV_ALL);
+ *            SRM2_VERIFY_DIV_ALL: all 2^23 dividend significands against divisors 2^23 + (i << param), i in [lo, hi);
+ *            SRM2_VERIFY_DIV_RANDOM: hi - lo pseudo-random pairs of seed lo over the guarded exponent range;
+ *            SRM2_VERIFY_ADAM: hi - lo pseudo-random whole Adam steps on four elements (seed lo), the packed step against the
+ *            plain IEEE step; param 0 = operands as in training, 1 = arbitrary bit patterns (NaN, infinities, subnormals)
+ *   variant  which sequence (square root: 1..3; division: number of residual corrections, 1 or 2); the kernels use
+ *            variant 1 of each (ignored by SRM2_VERIFY_ADAM)
+ *   out5     device uint64[5], ACCUMULATED into (zero it first): cases tested, mismatches, bits of the first mismatching
+ *            dividend and divisor, divisors whose refined reciprocal is off by more than 2^-22 (DIV_HARD) */
+#define SRM2_VERIFY_SQRT 0
+#define SRM2_VERIFY_DIV_HARD 1
+#define SRM2_VERIFY_DIV_ALL 2
+#define SRM2_VERIFY_DIV_RANDOM 3
+#define SRM2_VERIFY_ADAM 4
+int srm2_verify_exact(int what, uint64_t lo, uint64_t hi, int variant, int param, uint64_t* out5, srm2_stream_t stream);
+
 /* ---------------------------------------------------------------------------------------------------------
  * Adam scalars.  Replaces `adam_scalars` of the reference's host extension
  * (srm2/csrc/srm2_cpu.cpp:13-20 make_scalars, :255-257 export; called at srm2/ops.py:64 and srm2/gpu_ops.py:87).
