@@ -6,6 +6,10 @@ the image), loadable with importlib on any machine that has the same image:
 
   oracle/_ref/srm2_cpu_ext_<level>.so   <- srm2/csrc/srm2_cpu.cpp   (cpu_adam, adam_scalars, ...)
   oracle/_ref/srm2_elara_dir.so         <- srm2/csrc/elara_dir.cpp  (elara_dir_a, elara_dir_b)
+  oracle/_ref/srm2/*.py                 <- srm2/*.py, staged unchanged so that the reference's own planner, executor and
+                                           Triton kernels can be run on the GPU box beside this library (the tests that
+                                           need them skip when the folder is absent).  oracle/_ref/ is never tracked and
+                                           nothing under elara_b200/ imports it.
 
 The reference builds srm2_cpu.cpp with `-O3 -ffp-contract=off -march=native -fno-fast-math`
 (srm2/ops.py:23-25).  `-march=native` cannot travel between machines, so two fixed ISA levels are
@@ -13,7 +17,7 @@ built instead (x86-64-v3 = AVX2, x86-64-v4 = AVX-512) and the loader picks the h
 CPU supports; contraction stays off, so the results are the same bits at either level.
 elara_dir.cpp uses the reference's `-O2` (srm2/ops.py:37).
 
-Usage: python oracle/build_ref.py [--ref /path/to/reference]
+Usage: python oracle/build_ref.py --ref /path/to/reference      (or SRM2_REFERENCE=/path/to/reference)
 """
 import argparse
 import os
@@ -39,13 +43,28 @@ def _flags():
     return common, link
 
 
-def build(ref='/root/reference', force=False):
+def stage_python(ref):
+    """Copies the reference's Python package into the (untracked) oracle/_ref/srm2 for the tests that run it."""
+    import shutil
+    src = Path(ref) / 'srm2'
+    dst = OUT / 'srm2'
+    dst.mkdir(parents=True, exist_ok=True)
+    for f in sorted(src.glob('*.py')):
+        shutil.copyfile(f, dst / f.name)
+    return dst
+
+
+def build(ref=None, force=False):
+    ref = ref or os.environ.get('SRM2_REFERENCE')
+    if not ref:
+        return False
     ref = Path(ref)
     src_cpu = ref / 'srm2/csrc/srm2_cpu.cpp'
     src_dir = ref / 'srm2/csrc/elara_dir.cpp'
     if not src_cpu.exists():
         return False
     OUT.mkdir(exist_ok=True)
+    stage_python(ref)
     common, link = _flags()
     jobs = []
     for level in ('x86-64-v3', 'x86-64-v4'):
@@ -69,7 +88,7 @@ def build(ref='/root/reference', force=False):
 
 if __name__ == '__main__':
     ap = argparse.ArgumentParser()
-    ap.add_argument('--ref', default=os.environ.get('SRM2_REFERENCE', '/root/reference'))
+    ap.add_argument('--ref', default=os.environ.get('SRM2_REFERENCE'), help='the reference checkout (or set SRM2_REFERENCE)')
     ap.add_argument('--force', action='store_true')
     a = ap.parse_args()
     sys.exit(0 if build(a.ref, a.force) else 1)

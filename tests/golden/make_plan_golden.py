@@ -88,7 +88,7 @@ def gen_plan(elara, out, name, dyn, st_mode, kthr, steps=20, seed=5):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument('--ref', default=os.environ.get('SRM2_REFERENCE', '/root/reference'))
+    ap.add_argument('--ref', default=os.environ.get('SRM2_REFERENCE'), required=not os.environ.get('SRM2_REFERENCE'), help='the reference checkout (or set SRM2_REFERENCE)')
     a = ap.parse_args()
     sys.path.insert(0, a.ref)
     from oracle import oracle as O
