@@ -10,6 +10,10 @@ N > 1: the row-sharded variant (launched under torchrun, one rank per GPU): 25 M
 
 Prints ONE JSON line on rank 0.  `value` = unique rows updated per second over all GPUs with the inputs already in
 HBM; `e2e` = the same through host buffers (H2D of ids and gradients, D2H of the step's row count, every step).
+The timed region of --steps K steps is repeated (--windows, default 7) and the median window is reported, with the
+spread beside it.  Before anything is timed, a fresh engine runs three steps of the same batch shape through the same
+exchange and pipeline and every row it touched is compared bit for bit with the CPU oracle on the global batch
+(`parity`; a mismatch ends the run with a non-zero exit code).
 `--impl reference` times the reference's CPU path (torch.unique + aten.embedding_dense_backward on CPU tensors + its
 C++ cpu_adam with all host threads) on the same inputs, on a table compacted to the rows a step touches.
 """
@@ -126,13 +130,20 @@ def run_reference(a, world, rank):
     ids = [step_ids(sizes, offs, a.batch, world, 0, s + 1) for s in range(a.warmup + a.steps)]
     for s in range(a.warmup):
         fn(ids[s], grads[s % 2], state, s + 1)
-    rows = 0
-    t0 = time.perf_counter()
-    for s in range(a.warmup, a.warmup + a.steps):
-        rows += fn(ids[s], grads[s % 2], state, s + 1)
-    dt = time.perf_counter() - t0
+    # windows of --steps steps until at least five seconds have been timed: a single short window moves by tens of percent
+    # with whatever else the host is doing; the median window is reported
+    win = []
+    t_all = time.perf_counter()
+    while len(win) < 3 or (time.perf_counter() - t_all < 5.0 and len(win) < 200):
+        rows = 0
+        t0 = time.perf_counter()
+        for s in range(a.warmup, a.warmup + a.steps):
+            rows += fn(ids[s], grads[s % 2], state, s + 1)
+        win.append((time.perf_counter() - t0, rows))
+    win.sort()
+    dt, rows = win[len(win) // 2]
     val = rows / dt
-    sample = (f'{a.steps} steps of one GPU\'s share of the batch ({a.batch}x{N_TABLES} lookups, d={D}) on a table compacted to the '
+    sample = (f'median of {len(win)} windows of {a.steps} steps of one GPU\'s share of the batch ({a.batch}x{N_TABLES} lookups, d={D}) on a table compacted to the '
               f'rows each step touches; torch.unique + aten.embedding_dense_backward (CPU) + ' +
               ('the reference\'s C++ cpu_adam' if kind == 'reference' else 'the C port of cpu_adam'))
     return {'metric': 'sparse_adam_updated_rows_per_s', 'value': val, 'unit': 'rows/s', 'n_gpus': world, 'steps': a.steps,
@@ -140,7 +151,8 @@ def run_reference(a, world, rank):
             'dtype': 'f32', 'data': 'synthetic', 'impl': 'reference',
             'config': config_dict(a, world, total_rows),
             'cpu_baseline': {'value': val, 'unit': 'rows/s', 'cores': cores, 'kind': kind, 'sample': sample},
-            'e2e': {'value': val, 'unit': 'rows/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0}, 'gpu_launches': 0}
+            'e2e': {'value': val, 'unit': 'rows/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0}, 'gpu_launches': 0,
+            'windows': {'count': len(win), 'ms_per_step': [win[0][0] / a.steps * 1e3, dt / a.steps * 1e3, win[-1][0] / a.steps * 1e3]}}
 
 
 def config_dict(a, world, total_rows):
@@ -154,6 +166,81 @@ def config_dict(a, world, total_rows):
             'l2_policy': 'inputs larger than L2: table of tens of GB gathered at random rows; gradient buffers rotate over 4 x 109 MB'}
 
 
+# ------------------------------------------------------------------------------------------------ parity block
+def parity_grad(pos, step, xp):
+    """Per-lookup gradients of the parity block as a pure function of the GLOBAL lookup position (so every rank and the
+    oracle produce the same bits): a 29-bit integer product rounded to float32 (one rounding, the same in NumPy and
+    torch) times 2^-40 — magnitudes up to ~1e-3 with full significands, so the order of summation shows in the result."""
+    if xp is np:
+        j = np.arange(D, dtype=np.int64)[None, :]
+        h = pos.astype(np.int64)[:, None] * 2654435761 + j * 40503 + int(step) * 97
+        prod = (h % 32749 - 16374) * ((h // 32749) % 32719 + 1)
+        return prod.astype(np.float32) * np.float32(2.0 ** -40)
+    import torch
+    j = torch.arange(D, dtype=torch.int64, device=pos.device)[None, :]
+    h = pos.to(torch.int64)[:, None] * 2654435761 + j * 40503 + int(step) * 97
+    prod = (h % 32749 - 16374) * (torch.div(h, 32749, rounding_mode='floor') % 32719 + 1)
+    return prod.to(torch.float32) * (2.0 ** -40)
+
+
+def parity_block(a, world, rank, dev):
+    """Three steps of a fresh engine (2 M rows per GPU, the benchmark's lookups per GPU, its exchange and its pipelined
+    run_steps) against the single-process oracle on the global batch.  -> dict for the JSON line (rank 0) / None."""
+    import torch
+    import torch.distributed as dist
+    from elara_b200 import synth
+    from elara_b200.sharded import ShardedSparseAdam
+    from oracle import oracle as O                     # the checker; nothing of the timed path touches it
+    steps, rows_per_gpu = 3, 2_000_000
+    R, n = rows_per_gpu * world, a.batch * N_TABLES
+    sizes, offs = synth.table_sizes(R, N_TABLES, seed=SEED + 1)
+    bound = float(np.sqrt(1.0 / sizes.max()))
+    eng = ShardedSparseAdam(R, D, world, rank, dev, seed=SEED, bound=bound, hyper=HYP, max_lookups_per_rank=n,
+                            group=dist.group.WORLD if world > 1 else None)
+    p2p = eng.enable_p2p(n, pull=(a.exchange == 'pull'), grad_slots=a.grad_slots) if world > 1 and a.exchange != 'nccl' else False
+    pull = bool(p2p) and a.exchange == 'pull'
+    ids_all = [[synth.zipf_lookups(sizes, offs, a.batch, ALPHA, SEED + 1, s + 1, first_sample=r * a.batch) for r in range(world)]
+               for s in range(steps)]
+    batches = []
+    for s in range(steps):
+        g = parity_grad(torch.arange(rank * n, (rank + 1) * n, device=dev), s + 1, torch)
+        if pull:
+            slot = eng.grad_slot(s)[:n]
+            slot.copy_(g)
+            g = slot
+        batches.append((torch.from_numpy(ids_all[s][rank]).to(dev), g))
+    counts = eng.run_steps(batches, 1)
+    torch.cuda.synchronize(dev)
+    own = []
+    for s in range(steps):
+        gids = np.concatenate(ids_all[s])                # ranks hold consecutive slices of the global batch
+        pos = np.nonzero(gids % world == rank)[0]
+        own.append((pos, gids[pos] // world))
+    touched = np.unique(np.concatenate([l for _, l in own]))
+    state = O.init_rows(touched * world + rank, D, SEED, bound)
+    ok = True
+    for s, (pos, lids) in enumerate(own):
+        u, inv = O.unique_inverse(lids)
+        gW = O.segment_reduce(parity_grad(pos, s + 1, np), inv, len(u), chunk=10)      # the whole batch is far above the small-input rule
+        O.adam_rows(state, np.searchsorted(touched, u), gW, *HYP, s + 1, nthreads=min(8, os.cpu_count() or 1))
+        ok = ok and int(counts[s][0]) == len(u)
+    got = eng.pool[torch.from_numpy(touched).to(dev)].cpu().numpy()
+    ok = ok and np.array_equal(got.view(np.uint32), state.view(np.uint32))
+    stat = torch.tensor([1.0 if ok else 0.0, float(len(touched))], dtype=torch.float64, device=dev)
+    if world > 1:
+        mn = stat.clone(); dist.all_reduce(mn, op=dist.ReduceOp.MIN)
+        sm = stat.clone(); dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        ok_all, rows = bool(mn[0] > 0.5), int(sm[1])
+    else:
+        ok_all, rows = ok, len(touched)
+    del eng, batches
+    torch.cuda.empty_cache()
+    return {'steps': steps, 'rows_checked': rows, 'rows_per_gpu': rows_per_gpu, 'lookups_per_gpu_per_step': n,
+            'exchange': ('pull' if pull else 'push' if p2p else 'nccl') if world > 1 else 'none', 'path': 'run_steps (pipelined)',
+            'against': 'CPU oracle on the global batch (unique, runs-of-10 segment sums, Adam) restricted to each rank\'s rows',
+            'bitwise_equal': ok_all, 'this_rank_equal': bool(ok)}
+
+
 # ------------------------------------------------------------------------------------------------ our arm
 def run_ours(a, world, rank, local_rank):
     import torch
@@ -165,6 +252,13 @@ def run_ours(a, world, rank, local_rank):
     dev = torch.device('cuda', local_rank)
     torch.cuda.set_device(dev)
     L = _lib.lib()
+    parity = None if a.no_parity else parity_block(a, world, rank, dev)
+    if parity is not None and not parity['bitwise_equal']:
+        if rank == 0:
+            print(json.dumps({'parity': parity, 'error': 'the engine\'s rows differ from the oracle\'s'}), flush=True)
+        if world > 1:
+            dist.barrier()
+        sys.exit(3)
     total_rows, sizes, offs = workload(world, a.rows, a.batch)
     n = a.batch * N_TABLES
     bound = float(np.sqrt(1.0 / sizes.max()))
@@ -172,8 +266,9 @@ def run_ours(a, world, rank, local_rank):
                             max_lookups_per_rank=n, group=dist.group.WORLD if world > 1 else None)
     p2p = eng.enable_p2p(n, pull=(a.exchange == 'pull'), grad_slots=a.grad_slots) if world > 1 and a.exchange != 'nccl' else False
     pull = bool(p2p) and a.exchange == 'pull'
-    nsteps = a.warmup + a.steps
-    ids_np = [step_ids(sizes, offs, a.batch, world, rank, s + 1) for s in range(nsteps)]
+    K, W = a.steps, max(1, a.windows)
+    n_ids = min(a.warmup + K * W, max(64, a.warmup + K))         # distinct batches; longer runs cycle through them
+    ids_np = [step_ids(sizes, offs, a.batch, world, rank, s + 1) for s in range(n_ids)]
     ids_dev = [torch.from_numpy(x).to(dev) for x in ids_np]
     gen = torch.Generator(device=dev).manual_seed(SEED + rank)
     NBUF = a.grad_slots if world > 1 else 4
@@ -189,92 +284,147 @@ def run_ours(a, world, rank, local_rank):
             dist.barrier()
         torch.cuda.synchronize(dev)
 
-    # ---- device-resident timing (value) ----
-    if world == 1 and a.no_pipeline:
-        for s in range(a.warmup):
-            eng.step(ids_dev[s], grads_dev[s % NBUF], s + 1)
+    def batches(first, count):       # step index -> (ids, gradient buffer); buffer k mod NBUF is slot k mod NBUF in pull mode
+        return [(ids_dev[(first + k) % n_ids], grads_dev[k % NBUF]) for k in range(count)]
+
+    # ---- device-resident timing (value): W windows of exactly K steps each ----
+    pipelined = not (world == 1 and a.no_pipeline)
+    step_no = 1
+    if pipelined:
+        eng.run_steps(batches(0, a.warmup), step_no)
     else:
-        eng.run_steps([(ids_dev[s], grads_dev[k % NBUF]) for k, s in enumerate(range(a.warmup))], 1)
-    ev_pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(a.steps)]
+        for k, (i_, g_) in enumerate(batches(0, a.warmup)):
+            eng.step(i_, g_, step_no + k)
+    step_no += a.warmup
+    ev_pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
     for e0, e1 in ev_pairs:
         e0.record(); e1.record()              # materialise the handles
+    use_stage_events = world == 1 or pull
     barrier()
-    launches0 = L.srm2_launch_count()
     sampler = ClockSampler(local_rank) if rank == 0 else None
-    t_begin = torch.cuda.Event(enable_timing=True); t_end = torch.cuda.Event(enable_timing=True)
-    counts = []
-    t_host0 = time.perf_counter()
-    t_begin.record()
-    if world == 1 and a.no_pipeline:
-        for k, s in enumerate(range(a.warmup, nsteps)):
-            L.srm2_stage_events(ev_pairs[k][0].cuda_event, ev_pairs[k][1].cuda_event)
-            counts.append(eng.step(ids_dev[s], grads_dev[s % NBUF], s + 1))
-        L.srm2_stage_events(None, None)
-    else:
-        # the lookup ids are known ahead (as in a training loop that prefetches its batches): everything that depends on
-        # the ids only — routing and the exchange of names (N > 1), dedup, sort and run descriptors — runs one step ahead on
-        # side streams while the kernels that stream the gradient rows update the table on the main stream
-        counts = eng.run_steps([(ids_dev[s], grads_dev[k % NBUF]) for k, s in enumerate(range(a.warmup, nsteps))], a.warmup + 1,
-                               stage_events=ev_pairs if (world == 1 or pull) else None)
-    t_end.record()
-    host_enqueue_us = (time.perf_counter() - t_host0) * 1e6 / a.steps
-    barrier()
-    ms = t_begin.elapsed_time(t_end)
-    launches = L.srm2_launch_count() - launches0
+    win = []                                  # (ms, rows, launches, mean stage ms, host enqueue us per step)
+    for w in range(W):
+        bt = batches(a.warmup + w * K, K)
+        barrier()
+        launches0 = L.srm2_launch_count()
+        t_begin = torch.cuda.Event(enable_timing=True); t_end = torch.cuda.Event(enable_timing=True)
+        t_host0 = time.perf_counter()
+        t_begin.record()
+        if pipelined:
+            # the lookup ids are known ahead (as in a training loop that prefetches its batches): everything that depends on
+            # the ids only — routing and the exchange of names (N > 1), dedup, sort and run descriptors — runs ahead on side
+            # streams while the kernels that stream the gradient rows update the table on the main stream
+            counts = eng.run_steps(bt, step_no, stage_events=ev_pairs if use_stage_events else None)
+        else:
+            counts = []
+            for k, (i_, g_) in enumerate(bt):
+                L.srm2_stage_events(ev_pairs[k][0].cuda_event, ev_pairs[k][1].cuda_event)
+                counts.append(eng.step(i_, g_, step_no + k))
+            L.srm2_stage_events(None, None)
+        t_end.record()
+        host_us = (time.perf_counter() - t_host0) * 1e6 / K
+        barrier()
+        step_no += K
+        stage = float(np.mean([e0.elapsed_time(e1) for e0, e1 in ev_pairs])) if use_stage_events else float('nan')
+        win.append((t_begin.elapsed_time(t_end), int(sum(int(c[0]) for c in counts)), L.srm2_launch_count() - launches0, stage, host_us))
     clocks = sampler.stop() if sampler else None
-    rows_local = int(sum(int(c[0]) for c in counts))
-    lookups_local = eng.last_local_lookups_total
+    lookups_stage = eng.last_local_lookups
     if world > 1 and not pull:      # stage timing of the shard update alone, on a few extra steps outside the timed region
-        for k in range(min(a.steps, 5)):
+        m = min(K, 5)
+        for k, (i_, g_) in enumerate(batches(0, m)):
             L.srm2_stage_events(ev_pairs[k][0].cuda_event, ev_pairs[k][1].cuda_event)
-            eng.step(ids_dev[a.warmup + k], grads_dev[k % NBUF], nsteps + 100 + k)
+            eng.step(i_, g_, step_no + k)
         L.srm2_stage_events(None, None)
         barrier()
-        ev_pairs = ev_pairs[:min(a.steps, 5)]
-    stage_ms = [e0.elapsed_time(e1) for e0, e1 in ev_pairs]
+        step_no += m
+        extra_stage = float(np.mean([e0.elapsed_time(e1) for e0, e1 in ev_pairs[:m]]))
+        win = [(x[0], x[1], x[2], extra_stage, x[4]) for x in win]
 
-    # ---- end-to-end timing (host buffers) ----
-    h_ids = [torch.from_numpy(x).pin_memory() for x in ids_np[a.warmup:]]
+    # ---- NVLink read ceiling of the pull path, measured here: every rank streams 256 MiB out of its neighbour's
+    # gradient slots with the same 16-byte asynchronous copies the fused kernel uses, all ranks at once ----
+    peer_read_gbs = None
+    if pull:
+        P = eng._peer
+        nbytes = min(256 << 20, P['slots'] * P['n_max'] * D * 4) // 16 * 16
+        src = int(P['handles'][4].buffer_ptrs[(rank + 1) % world])
+        sink = torch.zeros(1, device=dev)
+        best = 0.0
+        for r in range(5):
+            barrier()
+            e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+            e0.record()
+            _lib.check(L.srm2_read_probe(src, nbytes, sink.data_ptr(), _lib.stream_of(dev)), 'read_probe')
+            e1.record(); torch.cuda.synchronize(dev)
+            if r:
+                best = max(best, nbytes / (e0.elapsed_time(e1) * 1e-3) / 1e9)
+        peer_read_gbs = best
+
+    # ---- end-to-end timing (host buffers): the H2D of step k+1 overlaps step k (two pinned/device buffer pairs, a copy
+    # stream); every step's row count is read on the host, one step late so that the read does not drain the queue ----
+    e2e_steps = max(10, min(K, 30))
+    h_ids = [torch.from_numpy(ids_np[(a.warmup + k) % n_ids]).pin_memory() for k in range(e2e_steps)]
     h_grads = [g.cpu().pin_memory() for g in grads_dev[:2]]
-    d_ids = torch.empty(n, dtype=torch.int64, device=dev); d_grad = torch.empty(n, D, device=dev)
-    h_count = torch.zeros(2, dtype=torch.int64).pin_memory()
-    e2e_steps = min(a.steps, 10)
-    for k in range(2):                         # warm-up of the copy path
-        d_ids.copy_(h_ids[k % len(h_ids)], non_blocking=True); d_grad.copy_(h_grads[k % 2], non_blocking=True)
-        eng.step(d_ids, d_grad, nsteps + 1 + k)
+    d_ids = [torch.empty(n, dtype=torch.int64, device=dev) for _ in range(2)]
+    d_grad = [torch.empty(n, D, device=dev) for _ in range(2)]
+    h_count = [torch.zeros(2, dtype=torch.int64).pin_memory() for _ in range(2)]
+    copy_stream = torch.cuda.Stream(dev)
+    comp = torch.cuda.current_stream(dev)
+    ev_in = [torch.cuda.Event() for _ in range(2)]; ev_used = [torch.cuda.Event() for _ in range(2)]; ev_cnt = [torch.cuda.Event() for _ in range(2)]
+
+    def e2e_run(steps, first_step):
+        rows = 0
+        for k in range(steps + 1):
+            b = k & 1
+            if k < steps:
+                with torch.cuda.stream(copy_stream):
+                    if k >= 2:
+                        copy_stream.wait_event(ev_used[b])         # step k-2 has consumed this buffer pair
+                    d_ids[b].copy_(h_ids[k % len(h_ids)], non_blocking=True)
+                    d_grad[b].copy_(h_grads[k % 2], non_blocking=True)
+                    ev_in[b].record(copy_stream)
+                comp.wait_event(ev_in[b])
+                c = eng.step(d_ids[b], d_grad[b], first_step + k, defer=True)
+                ev_used[b].record(comp)
+                h_count[b].copy_(c, non_blocking=True)
+                ev_cnt[b].record(comp)
+            if k >= 1:                                             # the result of step k-1 is read on the host
+                ev_cnt[(k - 1) & 1].synchronize()
+                rows += int(h_count[(k - 1) & 1][0])
+        return rows
+    e2e_run(2, step_no); step_no += 2                              # warm-up of the copy path
     barrier()
-    e_rows = 0
     t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
     t0.record()
-    for k in range(e2e_steps):
-        d_ids.copy_(h_ids[k], non_blocking=True)
-        d_grad.copy_(h_grads[k % 2], non_blocking=True)
-        c = eng.step(d_ids, d_grad, nsteps + 3 + k, defer=True)
-        h_count.copy_(c, non_blocking=True)
-        torch.cuda.current_stream(dev).synchronize()          # the step's result is read on the host every step
-        e_rows += int(h_count[0])
+    e_rows = e2e_run(e2e_steps, step_no); step_no += e2e_steps
     t1.record()
     barrier()
     e_ms = t0.elapsed_time(t1)
 
-    # ---- gather over ranks: max time, sum rows ----
-    stats = torch.tensor([ms, e_ms, float(rows_local), float(e_rows), float(np.mean(stage_ms)), float(launches)], dtype=torch.float64, device=dev)
+    # ---- over ranks: max time per window, sum of rows ----
+    wt = torch.tensor([[x[0], float(x[1]), float(x[2]), x[3]] for x in win], dtype=torch.float64, device=dev)      # [W, 4]
+    et = torch.tensor([e_ms, float(e_rows), peer_read_gbs or 0.0], dtype=torch.float64, device=dev)
     if world > 1:
-        mx = stats.clone(); dist.all_reduce(mx, op=dist.ReduceOp.MAX)
-        sm = stats.clone(); dist.all_reduce(sm, op=dist.ReduceOp.SUM)
-        ms, e_ms, stage = float(mx[0]), float(mx[1]), float(mx[4])
-        rows, e_rows_all, launches_all = float(sm[2]), float(sm[3]), float(sm[5])
+        wmx = wt.clone(); dist.all_reduce(wmx, op=dist.ReduceOp.MAX)
+        wsm = wt.clone(); dist.all_reduce(wsm, op=dist.ReduceOp.SUM)
+        emx = et.clone(); dist.all_reduce(emx, op=dist.ReduceOp.MAX)
+        esm = et.clone(); dist.all_reduce(esm, op=dist.ReduceOp.SUM)
+        emn = et.clone(); dist.all_reduce(emn, op=dist.ReduceOp.MIN)
+        ms_w, rows_w, launches_w, stage_w = wmx[:, 0].tolist(), wsm[:, 1].tolist(), wsm[:, 2].tolist(), wmx[:, 3].tolist()
+        e_ms, e_rows_all, peer_read_gbs = float(emx[0]), float(esm[1]), (float(emn[2]) if pull else None)
     else:
-        stage = float(stats[4]); rows, e_rows_all, launches_all = float(rows_local), float(e_rows), float(launches)
+        ms_w, rows_w, launches_w, stage_w = wt[:, 0].tolist(), wt[:, 1].tolist(), wt[:, 2].tolist(), wt[:, 3].tolist()
+        e_rows_all = float(e_rows)
     if rank != 0:
         return None
+    order = np.argsort(ms_w)
+    mid = int(order[len(order) // 2])                              # the median window is the one reported
+    ms, rows, launches, stage_ms = ms_w[mid], rows_w[mid], launches_w[mid], stage_w[mid]
     value = rows / (ms * 1e-3)
     peak, peak_kind = peaks()
     # roofline of the dominant stage (run sums + Adam kernels of the fused reduce), per GPU, this rank's launch
-    lookups_stage = eng.last_local_lookups
-    uniq_stage = rows_local / a.steps
+    uniq_stage = win[mid][1] / K
     alg_bytes = lookups_stage * (D * 4 + 8) + uniq_stage * (6 * D * 4 + 8)
-    achieved = alg_bytes / (float(np.mean(stage_ms)) * 1e-3) / 1e9
+    achieved = alg_bytes / (stage_ms * 1e-3) / 1e9
     traffic = None
     tf = ROOT / 'profiles' / 'traffic.json'
     if tf.exists():      # DRAM bytes of one ncu capture of the same kernel on a smaller table, scaled by algorithmic bytes
@@ -283,26 +433,33 @@ def run_ours(a, world, rank, local_rank):
             traffic = t['dram_bytes'] / t['algorithmic_bytes'] * alg_bytes
         except Exception:
             traffic = None
-    out = {'metric': 'sparse_adam_updated_rows_per_s', 'value': value, 'unit': 'rows/s', 'n_gpus': world, 'steps': a.steps, 'warmup': a.warmup,
-           'ms_per_step': ms / a.steps, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+    h2d = int(n * 8 + n * D * 4)
+    out = {'metric': 'sparse_adam_updated_rows_per_s', 'value': value, 'unit': 'rows/s', 'n_gpus': world, 'steps': K, 'warmup': a.warmup,
+           'ms_per_step': ms / K, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
            'config': config_dict(a, world, total_rows),
+           'windows': {'count': W, 'reported': 'median window', 'ms_per_step': [min(ms_w) / K, ms / K, max(ms_w) / K],
+                       'stage_us': [min(stage_w) * 1e3, stage_ms * 1e3, max(stage_w) * 1e3]},
+           'parity': parity,
            'roofline': {'bound': 'hbm', 'achieved': achieved, 'peak': peak, 'unit': 'GB/s', 'frac': achieved / peak, 'traffic': traffic,
                         'kernel': 'srm2_segment_runsum_wide_kernel (fused run sums + Adam; multi-run rows finished in place; N > 1: gradient rows read from their source rank over NVLink)',
                         'peak_source': f'{peak_kind} (MEASURED_PEAKS.json hbm_gbs)' if peak_kind == 'measured' else 'fallback 6650 GB/s',
-                        'stage_us': float(np.mean(stage_ms)) * 1e3, 'algorithmic_bytes_per_launch': alg_bytes},
-           'e2e': {'value': e_rows_all / (e_ms * 1e-3), 'unit': 'rows/s', 'h2d_bytes_per_step': int(n * 8 + n * D * 4) * world,
-                   'd2h_bytes_per_step': 16 * world, 'steps': e2e_steps},
-           'gpu_launches': int(launches_all), 'clocks': clocks,
-           'rows_updated_per_step': rows / a.steps, 'lookups_per_step_per_gpu': n, 'host_enqueue_us_per_step': host_enqueue_us}
-    out['config']['pipeline'] = ('none: one call after another on one stream' if (world == 1 and a.no_pipeline) else
-                                 'ids known one step ahead: dedup, sort and run descriptors of step s+1 run on a side stream while the run-sum + Adam '
+                        'stage_us': stage_ms * 1e3, 'algorithmic_bytes_per_launch': alg_bytes},
+           'e2e': {'value': e_rows_all / (e_ms * 1e-3), 'unit': 'rows/s', 'h2d_bytes_per_step': h2d * world,
+                   'd2h_bytes_per_step': 16 * world, 'steps': e2e_steps, 'pcie_h2d_GBs_per_gpu': h2d * e2e_steps / (e_ms * 1e-3) / 1e9,
+                   'overlap': 'the H2D of step k+1 runs on a copy stream while step k computes; the count of step k is read one step late'},
+           'gpu_launches': int(launches), 'clocks': clocks,
+           'rows_updated_per_step': rows / K, 'lookups_per_step_per_gpu': n, 'host_enqueue_us_per_step': win[mid][4]}
+    out['config']['pipeline'] = ('none: one call after another on one stream' if not pipelined else
+                                 'ids known ahead: dedup, sort and run descriptors of later steps run on side streams while the run-sum + Adam '
                                  'kernel of step s streams the gradient rows')
     if world > 1 and pull:
         # the gradient rows of (world-1)/world of the lookups are read from peer memory by the same kernel
         nv_bytes = lookups_stage * (world - 1) / world * D * 4
-        nv = nv_bytes / (float(np.mean(stage_ms)) * 1e-3) / 1e9
-        out['roofline']['nvlink'] = {'bytes_per_launch': nv_bytes, 'achieved': nv, 'peak': 657.0, 'unit': 'GB/s', 'frac': nv / 657.0,
-                                     'peak_source': 'peer reads with cp.async measured on this pool (own probe, 256 MiB, 2 GPUs)'}
+        nv = nv_bytes / (stage_ms * 1e-3) / 1e9
+        out['roofline']['nvlink'] = {'bytes_per_launch': nv_bytes, 'achieved': nv, 'peak': peer_read_gbs, 'unit': 'GB/s',
+                                     'frac': nv / peer_read_gbs if peer_read_gbs else None,
+                                     'peak_source': 'measured in this run: 256 MiB read from the next rank\'s gradient slots with 16-byte asynchronous '
+                                                    'copies on every SM, all ranks at once, slowest rank (srm2_read_probe)'}
     if world > 1:
         out['config']['exchange'] = ('pull: lookup names by peer stores, gradient rows read from their source rank by the fused reduce+Adam kernel (NVLink)'
                                      if pull else 'fused routing kernel: peer stores over NVLink' if p2p else 'NCCL all-to-all')
@@ -311,6 +468,28 @@ def run_ours(a, world, rank, local_rank):
 
 
 # ------------------------------------------------------------------------------------------------ per-kernel figures
+def reference_gpu_modules():
+    """The reference's own GPU kernels (Triton; srm2/ops.py, srm2/gpu_ops.py, srm2/elara_kernels.py) where its package has
+    been staged beside its compiled extensions in oracle/_ref/ — the comparison point on the same GPU.  None otherwise."""
+    ref_dir = ROOT / 'oracle' / '_ref'
+    if not (ref_dir / 'srm2' / 'ops.py').exists():
+        return None
+    try:
+        from oracle import oracle as O
+        E, Dx = O.ref_cpu(), O.ref_dir()
+        if E is None:
+            return None
+        if str(ref_dir) not in sys.path:
+            sys.path.insert(0, str(ref_dir))
+        import srm2.ops as rops
+        rops._ext, rops._dir = E, Dx            # what ext() / dir_ext() return once loaded: no JIT build here
+        import srm2.gpu_ops as rgpu
+        import srm2.elara_kernels as rk
+        return rops, rgpu, rk
+    except Exception:
+        return None
+
+
 def kernel_figures(dev, peak):
     """Device-resident timings of the other kernels of the path (CUDA events, L2 flushed between repetitions by
     writing a 256 MB buffer): row-sparse Adam at the 1 M x 16 and d = 128 shapes, counter-hash init, replay of 1..3
@@ -320,6 +499,16 @@ def kernel_figures(dev, peak):
     from elara_b200 import synth, ops
     from elara_b200.gpu_ops import init_rows, replay_rows, ScalarTable
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    refm = reference_gpu_modules()
+    same_bits = lambda x, y: bool(torch.equal(x.view(torch.int32), y.view(torch.int32)))
+
+    def beside(entry, fn):          # the reference's Triton kernel on the same inputs, same timing method
+        if refm is not None:
+            try:
+                entry['reference_triton_us'] = timed(fn)
+            except Exception as e:
+                entry['reference_triton_us'] = None
+                entry['reference_triton_note'] = repr(e)[:120]
 
     def timed(fn, reps=10):
         for _ in range(3):
@@ -342,6 +531,7 @@ def kernel_figures(dev, peak):
     rows = torch.from_numpy(synth.zipf_rows_without_replacement(R, n, 1.05, SEED, 1)).to(dev)
     g = torch.randn(n, d, device=dev) * 1e-3
     out['adam_1Mx16_65536rows'] = fig(timed(lambda: ops.gpu_adam(pool, rows, g, *HYP, 3)), n * (7 * d * 4 + 8), n, 'rows')
+    beside(out['adam_1Mx16_65536rows'], lambda: refm[0].gpu_adam(pool, rows, g, *HYP, 3))
     # the same 100 steps (a different row set each) as one CUDA graph: the launch gaps between 5 us kernels go away; the
     # 192 MB table stays partly L2-resident between steps, which is the workload's own behaviour (no flush inside a graph)
     try:
@@ -372,6 +562,7 @@ def kernel_figures(dev, peak):
     rows = torch.randperm(R, device=dev)[:n].sort().values
     g = torch.randn(n, d, device=dev) * 1e-3
     out['adam_8Mx128_262144rows'] = fig(timed(lambda: ops.gpu_adam(pool, rows, g, *HYP, 3)), n * (7 * d * 4 + 8), n, 'rows')
+    beside(out['adam_8Mx128_262144rows'], lambda: refm[0].gpu_adam(pool, rows, g, *HYP, 3))
     del pool, rows, g
     # init + replay, 262,144 rows x 64, histories of 1..3 gradients
     n, d, K = 262_144, 64, 3
@@ -380,10 +571,18 @@ def kernel_figures(dev, peak):
     table = ScalarTable(*HYP, 50, dev)
     o = torch.empty(n, 3, d, device=dev)
     out['init_262144x64'] = fig(timed(lambda: init_rows(t['rows'], d, 1234, 0.01, out=o)), n * (3 * d * 4 + 8), n, 'rows')
+    o2 = torch.empty_like(o)
+    beside(out['init_262144x64'], lambda: refm[1].init_rows(t['rows'], d, 1234, 0.01, out=o2))
+    if refm is not None:
+        out['init_262144x64']['equal_to_reference_triton'] = same_bits(o, o2)
     nbytes = n * (3 * d * 4 + 8 + 8 + 4 + 4 * K) + c['logs'].nbytes
     out['replay_262144x64_k3'] = fig(timed(lambda: replay_rows(t['rows'], t['logs'], t['offs'], t['steps'], t['cnt'], d, K, 1234, 0.01, table, out=o)),
                                      nbytes, n, 'rows')
-    out['replay_262144x64_k3']['note'] = 'bound by fp32 issue (3 IEEE divisions + 1 square root per element and entry), not by HBM'
+    if refm is not None:
+        rtable = refm[1].ScalarTable(*HYP, 50, dev)
+        beside(out['replay_262144x64_k3'], lambda: refm[1].replay_rows(t['rows'], t['logs'], t['offs'], t['steps'], t['cnt'], d, K, 1234, 0.01, rtable, out=o2))
+        out['replay_262144x64_k3']['equal_to_reference_triton'] = same_bits(o, o2)
+    del o2
     # fused assemble of a step's working matrix: 49,152 unique rows x 128 from a 1 M-row pool: 60 % resident, 10 % never touched,
     # 20 % logged (1..3 gradients), 5 % staged full rows, 5 % staged weights; next to the same result from the separate calls
     from elara_b200.gpu_ops import assemble
@@ -574,6 +773,36 @@ def directory_figures(dev, timed):
             out['reference_note'] = 'srm2/csrc/elara_dir.cpp (compiled in oracle/_ref) on CUDA tensors of the same GPU, calls A and B only'
     except Exception as e:                                      # the comparison is optional
         out['reference_note'] = 'reference extension not available: ' + repr(e)[:80]
+    refm = reference_gpu_modules()
+    if refm is not None:
+        # the reference's fused Triton directory (srm2/elara_kernels.py:146-209) on the same step, driven the way the
+        # planner drives it (srm2/elara.py:282-283, 293, 314-319, 376-378): same transitions, its own log-id order
+        import types
+        rk = refm[2]
+
+        class TritonStep:
+            @staticmethod
+            def elara_dir_a(st, pv_, hs_, L_row_, L_cnt_, ev_, s_):
+                pl = types.SimpleNamespace(d=dev, Kmax=K, n0=n0, Cdyn=Cdyn, MAT=MAT, mat_trash=R, evict_logs=True, R=R, log_cap=Lcap,
+                                           code=st[0], loc=st[1], ent=st[2], lstep=st[3], lfree=st[4], n_lfree=st[5], log_top=st[6],
+                                           mat_top=st[7], live=st[8], adm_c0=st[9], rj=st[10], pstep=st[11], kthr=st[12], toff=st[13],
+                                           slot_of=st[14], slot_row=st[15], rok=st[16])
+                TritonStep.pl, TritonStep.dirk = pl, rk.Directory(pl)
+                rk.lsteps(pl, L_row_, L_cnt_); rk.hits(pl, hs_, s_)
+                ev_row = pl.slot_row[ev_]
+                pl.slot_of[ev_row] = -1; pl.slot_row[ev_] = -1
+                thr_ev = pl.kthr[torch.searchsorted(pl.toff, ev_row, right=True) - 1]
+                TritonStep.rel = TritonStep.dirk.evict(ev_, ev_row, thr_ev)[3]
+
+            @staticmethod
+            def elara_dir_b(st, pv_, a_rows_, a_k_, c_rows_, c_cnt_, s_):
+                dk = TritonStep.dirk
+                dk.appends(a_rows_, a_k_, s_); dk.compact(c_rows_, c_cnt_); dk.release([TritonStep.rel, (c_rows_, c_cnt_)])
+        try:
+            out['reference_triton_us'] = timed_fresh(TritonStep, False)
+            out['reference_triton_note'] = 'srm2/elara_kernels.py Directory / lsteps / hits (Triton) on the same step, calls A and B only'
+        except Exception as e:
+            out['reference_triton_note'] = 'Triton directory not run: ' + repr(e)[:120]
     return out
 
 
@@ -610,6 +839,8 @@ def main():
                     help='N > 1: how routed lookups reach their owner (pull = rows read over NVLink by the reduce kernel)')
     ap.add_argument('--grad-slots', type=int, default=8, help='N > 1: peer-visible gradient buffers per rank (pull exchange)')
     ap.add_argument('--no-pipeline', action='store_true', help='N = 1: one step after the other on one stream (no look-ahead on the ids)')
+    ap.add_argument('--windows', type=int, default=7, help='repetitions of the timed region of --steps steps (median reported)')
+    ap.add_argument('--no-parity', action='store_true', help='skip the bit-for-bit check against the oracle before timing')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-kernels', action='store_true', help='skip the per-kernel figures (N = 1 only)')
     a = ap.parse_args()

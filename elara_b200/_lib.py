@@ -45,7 +45,7 @@ SIGNATURES = {
     'srm2_reduce_adam_nd_f32': (C.c_int, [_vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _vp, _i64, _i32, _f8, _vp, _sz, _vp]),
     'srm2_reduce_adam_index': (C.c_int, [_vp, _vp, _vp, _i64, _vp, _i64, _i64, _vp, _i64, _i32, _vp, _sz, _vp]),
     'srm2_reduce_adam_apply_f32': (C.c_int, [_vp, _vp, _vp, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _f8, _vp, _sz, _vp]),
-    'srm2_peer_barrier': (C.c_int, [_vp, _i64, _i64, C.c_uint64, _vp, _i64, _vp]),
+    'srm2_peer_barrier': (C.c_int, [_vp, _i64, _i64, C.c_uint64, _vp, _i64, _vp, _vp]),
     'srm2_assemble_f32': (C.c_int, [_vp, _i64, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, C.c_uint32, C.c_float, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                     _i64, _i64, _vp, _i64, _vp, _vp, _i64, _vp, _vp, _i64, _vp]),
     'srm2_plan_scratch_bytes': (_sz, [_i64]),
@@ -56,6 +56,7 @@ SIGNATURES = {
     'srm2_plan_pack': (C.c_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _i64, _vp, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp,
                                  _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     'srm2_staged_steps': (C.c_int, [_vp]),
+    'srm2_read_probe': (C.c_int, [_vp, _sz, _vp, _vp]),
     'srm2_route_dispatch_ids': (C.c_int, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _vp, C.c_uint64, _i64, _vp, _sz, _vp]),
     'srm2_route_publish_barrier': (C.c_int, [_vp, _vp, _vp, _i64, _i64, C.c_uint64, _vp, _i64, _vp]),
     'srm2_route_plan_publish': (C.c_int, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, C.c_uint64, _vp, _i64, _vp, _sz, _vp]),

@@ -115,6 +115,14 @@ struct PeerPtrs { void* p[kMaxPeers]; };
 
 // Lane r < world of one warp: arrive at rank r, then wait for rank r.  Callers make their earlier stores visible first
 // (__threadfence_system by every writing thread, then a warp or CTA barrier).
+// A rank that leaves a barrier with its error word set (a peer that never arrived, an overflowed receive buffer, now or
+// in an earlier step: the word is sticky) must not feed what it received to the update kernels: with n_recv != nullptr the
+// lane then sets the count of received lookups to zero, so dedup, index and the fused reduce + Adam of that step see an
+// empty batch and leave the shard untouched.
+__device__ __forceinline__ void contain_failure(const uint32_t* err, int64_t* n_recv) {
+  if (n_recv != nullptr && *reinterpret_cast<const volatile uint32_t*>(err) != 0u) *n_recv = 0;
+}
+
 __device__ __forceinline__ void peer_barrier_lane(const PeerPtrs& sig, int rank, int r, unsigned long long ticket, uint32_t* __restrict__ err,
                                                   long long timeout_ns) {
   unsigned long long* dst = static_cast<unsigned long long*>(sig.p[r]) + rank;
@@ -372,7 +380,10 @@ srm2_route_dispatch_ids_kernel(const int64_t* __restrict__ ids, const uint32_t* 
   __syncthreads();
   if (threadIdx.x == 0) s_last = atomicAdd(done, 1u) == gridDim.x - 1;
   __syncthreads();
-  if (s_last && (int)threadIdx.x < world) peer_barrier_lane(sig, rank, (int)threadIdx.x, ticket, err, timeout_ns);
+  if (s_last && (int)threadIdx.x < world) {
+    peer_barrier_lane(sig, rank, (int)threadIdx.x, ticket, err, timeout_ns);
+    contain_failure(err, n_recv);
+  }
 }
 
 // ---- barrier across the ranks' GPUs ------------------------------------------------------------------------------------
@@ -383,8 +394,11 @@ srm2_route_dispatch_ids_kernel(const int64_t* __restrict__ ids, const uint32_t* 
 // (and an iteration limit behind it): when it runs out the kernel sets bit 1 of *err and returns, so a rank that never
 // arrives costs the others the time limit, never the GPU.
 __global__ void srm2_peer_barrier_kernel(PeerPtrs sig, int rank, int world, unsigned long long ticket, uint32_t* __restrict__ err,
-                                         long long timeout_ns) {
-  if ((int)threadIdx.x < world) peer_barrier_lane(sig, rank, (int)threadIdx.x, ticket, err, timeout_ns);
+                                         long long timeout_ns, int64_t* n_recv) {
+  if ((int)threadIdx.x < world) {
+    peer_barrier_lane(sig, rank, (int)threadIdx.x, ticket, err, timeout_ns);
+    contain_failure(err, n_recv);
+  }
 }
 
 // counts + publish + barrier in one one-warp kernel (the tail of the plan): lane d takes owner d's count from the sort
@@ -553,7 +567,7 @@ extern "C" int srm2_route_dispatch_ids(const int64_t* ids, int64_t n, int64_t wo
 }
 
 extern "C" int srm2_peer_barrier(void* const* peer_tickets, int64_t rank, int64_t world, uint64_t ticket, uint32_t* err, int64_t timeout_ns,
-                                 srm2_stream_t stream) {
+                                 int64_t* n_recv, srm2_stream_t stream) {
   using namespace srm2;
   if (peer_tickets == nullptr || err == nullptr || world < 1 || world > kMaxPeers || rank < 0 || rank >= world || timeout_ns <= 0) return SRM2_ERR_ARG;
   PeerPtrs pp{};
@@ -561,7 +575,8 @@ extern "C" int srm2_peer_barrier(void* const* peer_tickets, int64_t rank, int64_
     if (peer_tickets[r] == nullptr || (reinterpret_cast<uintptr_t>(peer_tickets[r]) & 7u) != 0) return SRM2_ERR_ARG;
     pp.p[r] = peer_tickets[r];
   }
-  srm2_peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pp, (int)rank, (int)world, (unsigned long long)ticket, err, (long long)timeout_ns);
+  srm2_peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pp, (int)rank, (int)world, (unsigned long long)ticket, err, (long long)timeout_ns,
+                                                                            n_recv);
   return launch_status(1);
 }
 
@@ -579,4 +594,40 @@ extern "C" int srm2_route_publish_barrier(const int64_t* counts, void* const* pe
   srm2_route_publish_counts_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(counts, pc, ps, (int)rank, (int)world,
                                                                                            (unsigned long long)ticket, err, (long long)timeout_ns);
   return launch_status(1);
+}
+
+// ------------------------------------------------------------------------------------------------ read probe
+// Streams `bytes` from src (local or peer memory) with 16-byte asynchronous copies into per-thread shared-memory slots,
+// the access the fused reduce + Adam kernel uses for gradient rows; the sum of everything read goes to *sink so that
+// nothing is optimised away.  Used by the benchmark to measure the read ceiling it reports fractions of.
+namespace srm2 {
+constexpr int kProbeThreads = 256, kProbeDepth = 8;
+__global__ void __launch_bounds__(kProbeThreads) srm2_read_probe_kernel(const float4* __restrict__ src, size_t n16, float* sink) {
+  __shared__ __align__(16) float4 slot[kProbeDepth][kProbeThreads];
+  const size_t stride = (size_t)gridDim.x * kProbeThreads;
+  float acc = 0.f;
+  for (size_t i = (size_t)blockIdx.x * kProbeThreads + threadIdx.x; i < n16; i += stride * kProbeDepth) {
+#pragma unroll
+    for (int q = 0; q < kProbeDepth; ++q) {
+      const size_t j = i + q * stride;
+      if (j < n16) {
+        const unsigned sa = (unsigned)__cvta_generic_to_shared(&slot[q][threadIdx.x]);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sa), "l"(src + j) : "memory");
+      }
+    }
+    asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
+#pragma unroll
+    for (int q = 0; q < kProbeDepth; ++q)
+      if (i + q * stride < n16) { const float4 v = slot[q][threadIdx.x]; acc += v.x + v.y + v.z + v.w; }
+  }
+  if (acc == 1.2345e-30f) *sink = acc;
+}
+}  // namespace srm2
+
+extern "C" int srm2_read_probe(const void* src, size_t bytes, float* sink, srm2_stream_t stream) {
+  using namespace srm2;
+  if (src == nullptr || sink == nullptr || !aligned16(src)) return SRM2_ERR_ARG;
+  if (bytes < 16) return SRM2_OK;
+  srm2_read_probe_kernel<<<kSMs * 8, kProbeThreads, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const float4*>(src), bytes / 16, sink);
+  return launch_status();
 }

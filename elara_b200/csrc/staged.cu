@@ -29,7 +29,7 @@ struct Staged {
   void cuda(cudaError_t e) { if (rc == SRM2_OK && note_cuda(e)) rc = SRM2_ERR_CUDA; }
   void barrier(cudaStream_t st) {
     *a.ticket += 1;
-    check(srm2_peer_barrier(a.peer_tickets, a.rank, a.world, (uint64_t)*a.ticket, a.err, a.timeout_ns, st));
+    check(srm2_peer_barrier(a.peer_tickets, a.rank, a.world, (uint64_t)*a.ticket, a.err, a.timeout_ns, nullptr, st));
   }
 
   // stage 5 (world > 1): the routing plan of step k — local work, on the descriptor stream, which has room.  Two scratch sets:

@@ -283,12 +283,14 @@ class ShardedSparseAdam:
 
     barrier_timeout_ns = 5_000_000_000     # a rank whose peers do not arrive within this time flags an error and carries on
 
-    def _barrier(self, stream_handle):
-        """Stream-ordered barrier across the ranks (one one-warp kernel with a bounded wait, srm2_peer_barrier)."""
+    def _barrier(self, stream_handle, n_recv_ptr=0):
+        """Stream-ordered barrier across the ranks (one one-warp kernel with a bounded wait, srm2_peer_barrier).
+        n_recv_ptr: the device count of received lookups of the step this barrier closes; it is set to zero when the
+        exchange has failed (now or earlier), so that the step's update kernels leave the shard untouched."""
         P = self._peer
         P['ticket'] += 1
         _lib.check(_lib.lib().srm2_peer_barrier(P['p_sig'], self.rank, self.world, P['ticket'], P['err'].data_ptr(), self.barrier_timeout_ns,
-                                                stream_handle), 'peer_barrier')
+                                                n_recv_ptr, stream_handle), 'peer_barrier')
 
     def _check_exchange(self):
         e = int(self._peer['err'].item())
@@ -341,7 +343,7 @@ class ShardedSparseAdam:
                 _lib.check(L.srm2_route_dispatch(ids.data_ptr(), grads.data_ptr(), n, D, W, self.rank, cmat_ptr[b], P['p_lid'][b],
                                                  P['p_payload'][b], cap, nrecv_ptr[b], err_ptr, int(self.use_tma), scr_ptr, scr_len, cs),
                            'route_dispatch')
-                self._barrier(cs)                                 # every row has arrived
+                self._barrier(cs, nrecv_ptr[b])                   # every row has arrived (or nothing of this step is applied)
                 ev_payload[k].record(comm)
 
         prepare(0)
@@ -396,7 +398,7 @@ class ShardedSparseAdam:
             scr_len = (L.srm2_route_scratch_bytes(n_max, W) + 255) // 256 * 256
             scr = ops._scratch(self.dev, 2 * scr_len, 'route')        # two sets: the plan runs a step ahead of the names
             scr_ptr = scr.data_ptr()
-            if 'n_recv4' not in P:
+            if 'n_recv_ring' not in P:
                 P['n_recv_ring'] = torch.zeros(8, dtype=torch.int64, device=self.dev)
                 P['counts2'] = torch.zeros(2 * W, dtype=torch.int64, device=self.dev)
             counts_ptr, err_ptr = P['counts2'].data_ptr(), P['err'].data_ptr()
@@ -507,7 +509,7 @@ class ShardedSparseAdam:
                     self.grad_slot(k)[:nk].copy_(grads, non_blocking=True)
             _lib.check(L.srm2_route_dispatch_ids(ids.data_ptr(), nk, W, self.rank, cmat_ptr[b], P['p_lid'][b], P['p_payload'][b], cap,
                                                  nrecv_ptr[k & 7], err_ptr, 0, 0, 0, scr_ptr, scr_len, xss), 'route_dispatch_ids')
-            self._barrier(xss)                                    # every name has arrived, every slot is filled
+            self._barrier(xss, nrecv_ptr[k & 7])                  # every name has arrived, every slot is filled (or nothing is applied)
             ev_x[k].record(xs)
 
         def dedup(k):

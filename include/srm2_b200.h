@@ -290,9 +290,17 @@ int srm2_route_dispatch(const int64_t* ids, const float* grad, int64_t n, int64_
  * any collective on the stream serves as well, this one is a single one-warp kernel).  peer_tickets: host array of
  * `world` device pointers, entry r = rank r's array of 16 uint64 in peer-visible memory, zero before the first use.
  * `ticket` must grow by one with every barrier and be the same on every rank.  A rank whose peers do not arrive within
- * timeout_ns sets bit 1 (value 2) of *err and carries on: the wait is bounded, the caller must check *err. */
+ * timeout_ns sets bit 1 (value 2) of *err and carries on: the wait is bounded, the caller must check *err.
+ * Containment: *err is sticky, and a rank that leaves the barrier with *err != 0 writes 0 to *n_recv when n_recv is given
+ * (the barrier behind the names of a step: pass that step's count of received lookups) — the update kernels of the step
+ * then see an empty batch and leave the shard as it was.  The barrier fused into srm2_route_dispatch_ids does the same. */
 int srm2_peer_barrier(void* const* peer_tickets /* host */, int64_t rank, int64_t world, uint64_t ticket, uint32_t* err,
-                      int64_t timeout_ns, srm2_stream_t stream);
+                      int64_t timeout_ns, int64_t* n_recv /* or NULL */, srm2_stream_t stream);
+/* Measurement aid (no counterpart in the reference): streams `bytes` from src — local memory or a peer's — with the
+ * 16-byte asynchronous copies the fused reduce + Adam kernel uses for gradient rows, on every SM, and discards them.
+ * Time it with events to get the read ceiling of that access path on this machine.  src 16-byte aligned; sink: any
+ * device float (written only for one unlikely value of the checksum). */
+int srm2_read_probe(const void* src, size_t bytes, float* sink, srm2_stream_t stream);
 int srm2_route_dispatch_ids(const int64_t* ids, int64_t n, int64_t world, int64_t rank, const int64_t* cmat,
                             void* const* peer_lid /* host */, void* const* peer_src /* host */, int64_t cap, int64_t* n_recv,
                             uint32_t* err, void* const* peer_tickets /* host or NULL */, uint64_t ticket, int64_t timeout_ns,

@@ -146,11 +146,53 @@ def test_peer_barrier_wait_is_bounded():
     err = torch.zeros(1, dtype=torch.int32, device=dev)
     arr = (C.c_void_p * 2)(mine.data_ptr(), other.data_ptr())
     st = torch.cuda.current_stream(dev).cuda_stream
-    _lib.check(L.srm2_peer_barrier(arr, 0, 2, 1, err.data_ptr(), 2_000_000, st), 'barrier')
+    _lib.check(L.srm2_peer_barrier(arr, 0, 2, 1, err.data_ptr(), 2_000_000, 0, st), 'barrier')
     torch.cuda.synchronize()
     assert int(err.item()) == 2
     assert int(other[0]) == 1 and int(mine[0]) == 1            # its own tickets were delivered
     err.zero_(); mine[1] = 2                                    # "rank 1" has arrived at barrier 2
-    _lib.check(L.srm2_peer_barrier(arr, 0, 2, 2, err.data_ptr(), 2_000_000, st), 'barrier')
+    _lib.check(L.srm2_peer_barrier(arr, 0, 2, 2, err.data_ptr(), 2_000_000, 0, st), 'barrier')
     torch.cuda.synchronize()
     assert int(err.item()) == 0
+
+
+def test_failed_exchange_leaves_the_shard_untouched():
+    """Containment: a barrier that runs out (the peer never arrives) zeroes the step's count of received lookups, and the
+    flag is sticky, so the update kernels of that step and of the next one see an empty batch: no row of the shard changes
+    although the receive buffer holds (stale) lookups.  A healthy barrier leaves the count alone and the update runs."""
+    import ctypes as C
+    from elara_b200 import _lib, ops
+    from elara_b200.gpu_ops import init_rows
+    dev = torch.device('cuda:0')
+    L = _lib.lib()
+    R, D, n = 20_000, 64, 5_000
+    pool = init_rows(torch.arange(R, device=dev), D, 3, 0.01)
+    before = pool.clone()
+    ids = torch.randint(0, R, (n,), device=dev)
+    grad = torch.randn(n, D, device=dev) * 1e-3
+    mine = torch.zeros(16, dtype=torch.int64, device=dev)
+    other = torch.zeros(16, dtype=torch.int64, device=dev)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    arr = (C.c_void_p * 2)(mine.data_ptr(), other.data_ptr())
+    st = torch.cuda.current_stream(dev).cuda_stream
+
+    def update(n_recv, step):
+        u, inv, count = ops.unique_inverse(ids, R, sync=False, n_dev=n_recv)
+        ops.reduce_adam(pool, u, grad, inv, *HYP, step, count=count, order=ops.ORDER_RUNS, n_dev=n_recv)
+        return int(count[0])
+    n_recv = torch.full((1,), n, dtype=torch.int64, device=dev)
+    _lib.check(L.srm2_peer_barrier(arr, 0, 2, 1, err.data_ptr(), 2_000_000, n_recv.data_ptr(), st), 'barrier')     # rank 1 never arrives
+    assert update(n_recv, 1) == 0
+    torch.cuda.synchronize()
+    assert int(err.item()) == 2 and int(n_recv.item()) == 0
+    assert torch.equal(pool.view(torch.int32), before.view(torch.int32))
+    n_recv.fill_(n); mine[1] = 2                                 # the peer is there for barrier 2, but the failure is sticky
+    _lib.check(L.srm2_peer_barrier(arr, 0, 2, 2, err.data_ptr(), 2_000_000, n_recv.data_ptr(), st), 'barrier')
+    assert update(n_recv, 1) == 0
+    assert torch.equal(pool.view(torch.int32), before.view(torch.int32))
+    err.zero_(); n_recv.fill_(n); mine[1] = 3                    # cleared by the host: a healthy barrier changes nothing
+    _lib.check(L.srm2_peer_barrier(arr, 0, 2, 3, err.data_ptr(), 2_000_000, n_recv.data_ptr(), st), 'barrier')
+    assert update(n_recv, 1) == len(torch.unique(ids))
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0 and int(n_recv.item()) == n
+    assert not torch.equal(pool.view(torch.int32), before.view(torch.int32))
