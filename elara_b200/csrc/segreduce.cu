@@ -12,16 +12,18 @@
 //   1. stable LSD radix sort of (key = inverse index, value = lookup position); the number of passes follows from the
 //      bound on the number of unique rows (two 9-bit passes for ~200 k lookups).
 //   2. segment boundaries from the sorted keys.
-//   3. plan: per row its number of work items and partial sums, four block-local exclusive scans packed into two words;
-//      the last CTA to finish scans the per-CTA totals.  A global prefix is (CTA prefix + in-CTA offset).
-//   4. descriptors.  The work item is a CHUNK: up to kChunkRuns consecutive runs (60 lookups) of one row.
-//        rows of one chunk      : one item does everything — run sums, their sum, and the row's Adam update (or store);
+//   3. plan.  The work item is a CHUNK: up to kChunkRuns consecutive runs (60 lookups) of one row.
+//        rows of one chunk      : the row is its own item (nothing to prepare: the run-sum kernel reads the row's segment
+//                                 bounds); it does everything — run sums, their sum, the row's Adam update (or store);
 //        longer rows ("long")   : several items.  The first chunk adds its run sums locally and leaves one partial vector
 //                                 (the sum so far); every later chunk leaves one partial vector per run.  A row's partials
 //                                 are contiguous and in order, so the row total is their left-to-right sum from +0 —
-//                                 exactly the order above.
+//                                 exactly the order above.  One thread per row: a long row takes its range of chunk
+//                                 descriptors and of partial slots from two counters (atomics; which range a row gets
+//                                 does not matter, the order inside a row is fixed by the layout) and writes the
+//                                 descriptors.  No scan, no second kernel.
 //      Long rows' chunks come first in item order, so their partials are ready while the bulk is still streaming.
-//   5. run sums: an aligned group of D/4 lanes per item streams the item's gradient rows through per-thread shared
+//   4. run sums: an aligned group of D/4 lanes per item streams the item's gradient rows through per-thread shared
 //      memory slots with cp.async — five rows in flight while the previous five are added — so a 60-lookup item never
 //      waits for more than its first loads.  One release (fence + counter increment) per chunk of a long row; the chunk
 //      that completes a row adds the row's partials (a rolling window of twelve in flight; rows with many partials are
@@ -43,14 +45,14 @@ constexpr int kSmallN = 3072;       // inputs up to this many lookups use the wi
 constexpr int kWindow = 32;
 constexpr int kPlanThreads = 256;
 
-struct SegCounters { uint32_t n_items, n_lchunks, n_lrows, n_parts, done; };
+struct SegCounters { uint32_t n_lchunks, n_lrows, n_parts; };
 constexpr int kMaxGradPeers = 16;
 constexpr int kPeerShift = 24;      // pull mode: a lookup is named by (source rank << 24) | row in that rank's gradient buffer
 
 struct ReduceArgs {
   const float* grad; int D; int lpr; int shift;
   const uint32_t* skey; const uint32_t* spos; const uint32_t* seg_start; const uint32_t* seg_end;
-  const uint4* item_desc; const uint32_t* pos_sorted; uint4* lrow_info; const SegCounters* counters; int inplace;
+  const uint4* chunk_desc; const uint4* row_desc; const uint32_t* pos_sorted; uint4* lrow_info; const SegCounters* counters; int inplace;
   float* partial;
   float* out;                                     // [nu, D] (unfused) or nullptr
   float* pool; const int64_t* slots; AdamSc sc;   // fused Adam: pool [C,3,D], slots[j] = pool row of unique row j
@@ -92,12 +94,15 @@ __device__ __forceinline__ void finish_row(const ReduceArgs& a, uint32_t j, int 
 // ------------------------------------------------------------------------------------------ boundaries
 // seg_start[j] / seg_end[j] = sorted index range of unique row j.  Both arrays are zeroed first, so a row that no
 // lookup names has an empty range.  Lookups with an invalid index carry key == cap and belong to no row.
+// In pull mode the kernel also leaves, at every sorted index, the name of the lookup's gradient row ((rank, row) code).
 __global__ void __launch_bounds__(256)
-srm2_segment_bounds_kernel(const uint32_t* __restrict__ skey, int64_t n_host, const int64_t* __restrict__ n_dev,
-                           uint32_t* __restrict__ seg_start, uint32_t* __restrict__ seg_end, int64_t cap) {
+srm2_segment_bounds_kernel(const uint32_t* __restrict__ skey, const uint32_t* __restrict__ spos, int64_t n_host,
+                           const int64_t* __restrict__ n_dev, uint32_t* __restrict__ seg_start, uint32_t* __restrict__ seg_end,
+                           int64_t cap, const uint32_t* __restrict__ src_code, uint32_t* __restrict__ names) {
   const int64_t n = eff_count(n_host, n_dev);
   const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
   if (i >= n) return;
+  if (src_code) names[i] = src_code[spos[i]];
   const uint32_t k = skey[i];
   if ((int64_t)k >= cap) return;
   if (i == 0 || skey[i - 1] != k) seg_start[k] = (uint32_t)i;
@@ -114,104 +119,40 @@ __device__ __forceinline__ RowShape row_shape(uint32_t len) {
   return r;
 }
 
-struct PlanOut { uint32_t *lchunk_off, *part_off, *lrow_off, *item_off, *bs_lc, *bs_pt, *bs_lr, *bs_it; };
-
-// Per unique row: chunks of long rows, partial vectors, long rows and one-chunk rows before it inside its CTA (exclusive);
-// per CTA the totals; the last CTA to finish turns the totals into exclusive prefixes and writes the grand totals.
-// Rows without lookups are finished here (zero gradient).
+// One thread per unique row.  Rows without lookups are finished here (zero gradient).  A long row takes `chunks`
+// consecutive chunk descriptors, `parts` consecutive partial slots and one entry of lrow_info, and fills them in:
+//   row_desc[j]   = the row's own item (see below)
+//   chunk_desc[c] = {sorted index of the chunk's first lookup, L | kLongBit (| kFirstBit for the row's first chunk),
+//                    first partial slot the chunk writes, index of the row in lrow_info};  L = lookups of the chunk
+//   lrow_info[w]  = {unique row, number of runs, first partial slot, finished-chunk counter = 0}
+constexpr uint32_t kLongBit = 0x80000000u, kFirstBit = 0x40000000u;
 template <bool FUSED>
 __global__ void __launch_bounds__(kPlanThreads)
-srm2_segment_plan_kernel(ReduceArgs a, PlanOut o, SegCounters* __restrict__ counters, int nblocks, int skip_empty) {
-  __shared__ uint64_t ws[33];
-  __shared__ bool last;
+srm2_segment_plan_kernel(ReduceArgs a, uint4* __restrict__ chunk_desc, uint4* __restrict__ row_desc, SegCounters* __restrict__ counters,
+                         int skip_empty) {
   const int64_t nu = load_nu(a.nu_host, a.nu_dev, a.cap);
   const int64_t j = (int64_t)blockIdx.x * kPlanThreads + threadIdx.x;
-  uint64_t lc = 0, pt = 0, lr = 0, it = 0;
-  if (j < nu) {
-    const uint32_t len = a.seg_end[j] - a.seg_start[j];
-    const RowShape r = row_shape(len);
-    if (r.is_long) { lc = r.chunks; pt = r.parts; lr = 1; } else if (len > 0) it = 1;
-    if (len == 0 && !skip_empty)
-      for (int j4 = 0; j4 < a.lpr; ++j4) finish_row<FUSED>(a, (uint32_t)j, j4, make_float4(0.f, 0.f, 0.f, 0.f));
-  }
-  // two packed scans (32 bits per counter: a CTA's totals are bounded by the number of lookups, below 2^31)
-  uint64_t t0, t1;
-  const uint64_t e0 = block_exclusive_scan64<kPlanThreads>((lc << 32) | pt, ws, &t0);
-  const uint64_t e1 = block_exclusive_scan64<kPlanThreads>((lr << 32) | it, ws, &t1);
-  if (j < a.cap) {
-    o.lchunk_off[j] = (uint32_t)(e0 >> 32); o.part_off[j] = (uint32_t)e0; o.lrow_off[j] = (uint32_t)(e1 >> 32); o.item_off[j] = (uint32_t)e1;
-  }
-  if (threadIdx.x == 0) {
-    o.bs_lc[blockIdx.x] = (uint32_t)(t0 >> 32); o.bs_pt[blockIdx.x] = (uint32_t)t0;
-    o.bs_lr[blockIdx.x] = (uint32_t)(t1 >> 32); o.bs_it[blockIdx.x] = (uint32_t)t1;
-    __threadfence();
-    last = atomicAdd(&counters->done, 1u) == (uint32_t)(nblocks - 1);
-  }
-  __syncthreads();
-  if (!last) return;
-  __threadfence();
-  uint64_t c_lc = 0, c_pt = 0, c_lr = 0, c_it = 0;
-  for (int base = 0; base < nblocks; base += kPlanThreads) {
-    const int i = base + threadIdx.x;
-    const uint64_t v_lc = i < nblocks ? reinterpret_cast<volatile uint32_t*>(o.bs_lc)[i] : 0u;
-    const uint64_t v_pt = i < nblocks ? reinterpret_cast<volatile uint32_t*>(o.bs_pt)[i] : 0u;
-    const uint64_t v_lr = i < nblocks ? reinterpret_cast<volatile uint32_t*>(o.bs_lr)[i] : 0u;
-    const uint64_t v_it = i < nblocks ? reinterpret_cast<volatile uint32_t*>(o.bs_it)[i] : 0u;
-    uint64_t s0, s1;
-    const uint64_t x0 = block_exclusive_scan64<kPlanThreads>((v_lc << 32) | v_pt, ws, &s0);
-    const uint64_t x1 = block_exclusive_scan64<kPlanThreads>((v_lr << 32) | v_it, ws, &s1);
-    if (i < nblocks) {
-      o.bs_lc[i] = (uint32_t)(c_lc + (x0 >> 32)); o.bs_pt[i] = (uint32_t)(c_pt + (uint32_t)x0);
-      o.bs_lr[i] = (uint32_t)(c_lr + (x1 >> 32)); o.bs_it[i] = (uint32_t)(c_it + (uint32_t)x1);
-    }
-    c_lc += s0 >> 32; c_pt += (uint32_t)s0; c_lr += s1 >> 32; c_it += (uint32_t)s1;
-  }
-  if (threadIdx.x == 0) {
-    counters->n_lchunks = (uint32_t)c_lc; counters->n_parts = (uint32_t)c_pt; counters->n_lrows = (uint32_t)c_lr;
-    counters->n_items = (uint32_t)(c_lc + c_it); counters->done = 0u;
-  }
-}
-
-// Item descriptors; one thread per sorted lookup, the first lookup of a chunk writes.  Every lookup also leaves the name
-// of its gradient row (its position, or in pull mode its (rank, row) code) at its sorted index.
-//   item_desc[c] = {x, L | flags, z, w};  L = lookups of the chunk; x = sorted index of its first lookup, or, for a row of
-//     a single lookup, that lookup's name itself;
-//     one-chunk row: c = n_lchunks + rank among such rows, (z, w) = 64-bit target: the pool row (fused) or the row index;
-//     chunk q of a long row: c = (long chunks before the row) + q, flags kLongBit (| kFirstBit for q = 0), z = first partial
-//     slot the chunk writes, w = index of the row in lrow_info.
-//   lrow_info[w] = {unique row, number of runs, first partial slot, finished-chunk counter = 0}
-constexpr uint32_t kLongBit = 0x80000000u, kFirstBit = 0x40000000u;
-__global__ void __launch_bounds__(256)
-srm2_segment_descr_kernel(const uint32_t* __restrict__ skey, const uint32_t* __restrict__ spos, int64_t n_host,
-                          const int64_t* __restrict__ n_dev, const uint32_t* __restrict__ seg_start,
-                          const uint32_t* __restrict__ seg_end, PlanOut o, const SegCounters* __restrict__ counters,
-                          const int64_t* __restrict__ slots, const uint32_t* __restrict__ src_code,
-                          uint4* __restrict__ item_desc, uint32_t* __restrict__ pos_sorted, uint4* __restrict__ lrow_info,
-                          int64_t nu_host, const int64_t* __restrict__ nu_dev, int64_t cap) {
-  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
-  if (i >= eff_count(n_host, n_dev)) return;
-  const uint32_t j = skey[i];
-  const uint32_t code = src_code ? src_code[spos[i]] : spos[i];
-  pos_sorted[i] = code;
-  if ((int64_t)j >= load_nu(nu_host, nu_dev, cap)) return;
-  const uint32_t s = seg_start[j], e = seg_end[j];
-  const uint32_t off = (uint32_t)i - s;
-  if (off % (uint32_t)kChunk != 0u) return;
-  const uint32_t q = off / (uint32_t)kChunk, len = e - s;
-  const uint32_t L = min((uint32_t)kChunk, e - (uint32_t)i);
+  if (j >= nu) return;
+  const uint32_t s = a.seg_start[j], len = a.seg_end[j] - s;
   const RowShape r = row_shape(len);
-  const uint32_t blk = j / kPlanThreads;
-  if (r.is_long) {
-    const uint32_t c = o.bs_lc[blk] + o.lchunk_off[j] + q;
-    const uint32_t base = o.bs_pt[blk] + o.part_off[j];
-    const uint32_t mi = o.bs_lr[blk] + o.lrow_off[j];
+  // the row's own item: {sorted index of its first lookup — or, for a single lookup, that lookup's name —, number of
+  // lookups (0: nothing to do under this entry), 64-bit target: the pool row (fused) or the row index}
+  const uint64_t target = FUSED ? (uint64_t)a.slots[j] : (uint64_t)j;
+  row_desc[j] = make_uint4(len == 1 ? a.pos_sorted[s] : s, (len == 0 || r.is_long) ? 0u : len, (uint32_t)target, (uint32_t)(target >> 32));
+  if (len == 0) {
+    if (!skip_empty)
+      for (int j4 = 0; j4 < a.lpr; ++j4) finish_row<FUSED>(a, (uint32_t)j, j4, make_float4(0.f, 0.f, 0.f, 0.f));
+    return;
+  }
+  if (!r.is_long) return;
+  const uint32_t c0 = atomicAdd(&counters->n_lchunks, r.chunks);
+  const uint32_t base = atomicAdd(&counters->n_parts, r.parts);
+  const uint32_t mi = atomicAdd(&counters->n_lrows, 1u);
+  a.lrow_info[mi] = make_uint4((uint32_t)j, r.runs, base, 0u);
+  for (uint32_t q = 0; q < r.chunks; ++q) {
+    const uint32_t first = s + q * (uint32_t)kChunk, L = min((uint32_t)kChunk, len - q * (uint32_t)kChunk);
     const uint32_t slot = q == 0 ? base : base + 1u + (q - 1u) * (uint32_t)kChunkRuns;
-    item_desc[c] = make_uint4((uint32_t)i, L | kLongBit | (q == 0 ? kFirstBit : 0u), slot, mi);
-    if (q == 0) lrow_info[mi] = make_uint4(j, r.runs, base, 0u);
-  } else {
-    const uint32_t c = counters->n_lchunks + o.bs_it[blk] + o.item_off[j];
-    const uint64_t target = slots ? (uint64_t)slots[j] : (uint64_t)j;
-    item_desc[c] = make_uint4(len == 1 ? code : (uint32_t)i, L, (uint32_t)target, (uint32_t)(target >> 32));
+    chunk_desc[c0 + q] = make_uint4(first, L | kLongBit | (q == 0 ? kFirstBit : 0u), slot, mi);
   }
 }
 
@@ -326,7 +267,10 @@ srm2_segment_runsum_wide_kernel(ReduceArgs a) {
   float4* mine = stage + threadIdx.x;
   const AdamSc sc = a.sc;
   const AdamFast fa = adam_fast_prepare(sc);
-  const int64_t items = (int64_t)a.counters->n_items * a.lpr;
+  // items: the long rows' chunks (descriptors), then every unique row (its segment bounds are its descriptor; long rows
+  // and rows without lookups come out as L = 0 and are skipped)
+  const int64_t n_lchunks = a.counters->n_lchunks;
+  const int64_t items = (n_lchunks + load_nu(a.nu_host, a.nu_dev, a.cap)) * a.lpr;
   const int lane = threadIdx.x & 31;
   const unsigned gmask = a.lpr >= 32 ? 0xffffffffu : (((1u << a.lpr) - 1u) << (lane & ~(a.lpr - 1)));
   const int gleader = a.lpr >= 32 ? 0 : (lane & ~(a.lpr - 1));
@@ -336,17 +280,22 @@ srm2_segment_runsum_wide_kernel(ReduceArgs a) {
   const int64_t end = items;
   const int j4 = (int)(t & (a.lpr - 1));
   const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
-  auto item_of = [&](int64_t tt) { return tt >> a.shift; };
-  auto load_desc = [&](int64_t tt) -> uint4 { return tt < end ? __ldg(a.item_desc + item_of(tt)) : make_uint4(0u, 0u, 0u, 0u); };
+  // descriptor of item tt: {x = sorted index of the first lookup, y = L | flags, (z, w) = target row / (slot, long row)}
+  auto load_desc = [&](int64_t tt) -> uint4 {
+    if (tt >= end) return make_uint4(0u, 0u, 0u, 0u);
+    const int64_t c = tt >> a.shift;
+    return c < n_lchunks ? __ldg(a.chunk_desc + c) : __ldg(a.row_desc + (c - n_lchunks));
+  };
   auto lookups = [](const uint4& d) { return (int)(d.y & 0xffu); };
-  auto lone = [](const uint4& d) { return d.y == 1u; };          // a row with a single lookup (x is the row's name)
-  // names of the first run of an item (lane gl holds row gl)
+  auto lone = [](const uint4& d) { return d.y == 1u; };          // a row with a single lookup
+  // names of the first run of an item (lane gl holds row gl); a single lookup carries its name in the descriptor
   auto first_names = [&](const uint4& d) -> uint32_t {
     const int L = lookups(d);
-    return (!lone(d) && gl < min(L, kRun)) ? __ldg(a.pos_sorted + d.x + gl) : 0u;
+    if (lone(d)) return d.x;
+    return gl < min(L, kRun) ? __ldg(a.pos_sorted + d.x + gl) : 0u;
   };
   uint4 d0 = load_desc(t), d1 = load_desc(t + step), d2 = load_desc(t + 2 * step);
-  uint32_t p0 = t < end ? first_names(d0) : 0u;
+  uint32_t p0 = first_names(d0);
   while (t < end) {
     if (FUSED && lone(d0) && lone(d1) && lone(d2)) {
       // ---- three single-lookup rows at once: 3 x (gradient row, w, m, v) = 12 of the 13 slots, 192 bytes in flight ----
@@ -371,7 +320,7 @@ srm2_segment_runsum_wide_kernel(ReduceArgs a) {
         adam_vec4_fast(w, m, v, g, fa);
         *reinterpret_cast<float4*>(b) = w; *reinterpret_cast<float4*>(b + a.D) = m; *reinterpret_cast<float4*>(b + 2 * a.D) = v;
       }
-      if (t < end) p0 = first_names(d0);
+      p0 = first_names(d0);
       continue;
     }
     const uint4 d = d0;
@@ -380,8 +329,9 @@ srm2_segment_runsum_wide_kernel(ReduceArgs a) {
     const uint32_t names0 = p0;
     // descriptors of the next items and the names of the next item's first run, before this item's work
     d0 = d1; d1 = d2; d2 = load_desc(t + 3 * step);
+    p0 = first_names(d0);
     t += step;
-    if (t < end) p0 = first_names(d0);
+    if (L == 0) continue;                              // a long row's own entry (its chunks are items of their own), or no lookups
     float* b = nullptr;
     if (!is_long) {
       const int64_t target = (int64_t)((uint64_t)d.z | ((uint64_t)d.w << 32));
@@ -396,13 +346,9 @@ srm2_segment_runsum_wide_kernel(ReduceArgs a) {
     float4 total = zero;
     if (L <= kRun) {
       // ---- one run: every copy at once ----
-      if (lone(d)) {
-        cp_async16(mine, grad_row<PEER>(a, d.x) + j4 * 4);
-      } else {
-        for (int q = 0; q < L; ++q) {
-          const uint32_t pos = __shfl_sync(gmask, names0, gleader + q);
-          cp_async16(mine + q * kRunThreads, grad_row<PEER>(a, pos) + j4 * 4);
-        }
+      for (int q = 0; q < L; ++q) {
+        const uint32_t pos = __shfl_sync(gmask, names0, gleader + q);
+        cp_async16(mine + q * kRunThreads, grad_row<PEER>(a, pos) + j4 * 4);
       }
       cp_async_commit();
       cp_async_wait<0>();
@@ -487,14 +433,16 @@ srm2_segment_runsum_kernel(ReduceArgs a) {
   float4* mine = stage + threadIdx.x;
   const AdamSc sc = a.sc;
   const AdamFast fa = adam_fast_prepare(sc);
-  const int64_t items = (int64_t)a.counters->n_items * a.lpr;
+  const int64_t n_lchunks = a.counters->n_lchunks;
+  const int64_t items = (n_lchunks + load_nu(a.nu_host, a.nu_dev, a.cap)) * a.lpr;
   const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int64_t t = (int64_t)blockIdx.x * kRunThreads + threadIdx.x; t < items; t += (int64_t)gridDim.x * kRunThreads) {
     int64_t c; int j4;
     if (a.shift >= 0) { c = t >> a.shift; j4 = (int)(t & (a.lpr - 1)); } else { c = t / a.lpr; j4 = (int)(t - c * a.lpr); }
-    const uint4 d = __ldg(a.item_desc + c);
+    const uint4 d = c < n_lchunks ? __ldg(a.chunk_desc + c) : __ldg(a.row_desc + (c - n_lchunks));
     const int L = (int)(d.y & 0xffu);
-    const bool is_long = (d.y & kLongBit) != 0, is_first = (d.y & kFirstBit) != 0, lone = d.y == 1u;
+    if (L == 0) continue;
+    const bool is_long = (d.y & kLongBit) != 0, is_first = (d.y & kFirstBit) != 0;
     float* b = nullptr;
     if (!is_long) {
       const int64_t target = (int64_t)((uint64_t)d.z | ((uint64_t)d.w << 32));
@@ -513,7 +461,7 @@ srm2_segment_runsum_kernel(ReduceArgs a) {
 #pragma unroll
       for (int q = 0; q < kRun; ++q)
         if (q < len_r) {
-          const uint32_t pos = lone ? d.x : __ldg(a.pos_sorted + d.x + r * kRun + q);
+          const uint32_t pos = d.y == 1u ? d.x : __ldg(a.pos_sorted + d.x + r * kRun + q);
           cp_async16(mine + q * kRunThreads, grad_row<PEER>(a, pos) + j4 * 4);
         }
       cp_async_commit();
@@ -655,8 +603,8 @@ srm2_segment_windowed_kernel(ReduceArgs a) {
 // ------------------------------------------------------------------------------------------ host side
 struct SegScratch {
   uint32_t *keyA, *valA, *keyB, *valB, *hist, *dtot, *seg_start, *seg_end;
-  PlanOut plan; uint4* item_desc; uint32_t* pos_sorted; uint4* lrow_info; SegCounters* counters; float* partial;
-  int tiles, bits, passes, nblocks; char* zero; size_t zero_bytes;
+  uint4* chunk_desc; uint4* row_desc; uint32_t* names; uint4* lrow_info; SegCounters* counters; float* partial;
+  int tiles, bits, passes; char* zero; size_t zero_bytes;
 };
 
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -668,31 +616,28 @@ static size_t seg_layout(int64_t n, int64_t cap, int64_t D, char* base, SegScrat
   const int keybits = ceil_log2(cap + 1 < 2 ? 2 : cap + 1);     // keys 0..cap (cap = invalid index)
   const int passes = (keybits + kMaxRadixBits - 1) / kMaxRadixBits;
   const int bits = (keybits + passes - 1) / passes;
-  const int nblocks = (int)((cap + kPlanThreads - 1) / kPlanThreads);
   size_t off = 0;
   auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return o; };
-  const size_t nn = (size_t)(n > 0 ? n : 1), cc = (size_t)(cap + 1), nb = (size_t)(nblocks + 1);
-  const size_t o_ka = take(nn * 4), o_va = take(nn * 4), o_kb = take(nn * 4), o_vb = take(nn * 4);
+  const size_t nn = (size_t)(n > 0 ? n : 1), cc = (size_t)(cap + 1);
+  const size_t o_ka = take(nn * 4), o_va = take((nn + 16) * 4), o_kb = take(nn * 4), o_vb = take((nn + 16) * 4);
   const size_t o_h = take(sort_hist_words(tiles, bits) * 4);
   // one zero-filled region per call: counters | digit totals | seg_start | seg_end
   const size_t zero_bytes = 256 + align_up(sort_dtot_words(tiles, bits, passes) * 4, 256) + cc * 4 * 2;
   const size_t o_z = take(zero_bytes);
   const size_t o_ct = o_z, o_dt = o_z + 256, o_ss = o_dt + align_up(sort_dtot_words(tiles, bits, passes) * 4, 256);
-  const size_t o_r0 = take(cc * 4), o_r1 = take(cc * 4), o_r2 = take(cc * 4), o_r3 = take(cc * 4);
-  const size_t o_b0 = take(nb * 4), o_b1 = take(nb * 4), o_b2 = take(nb * 4), o_b3 = take(nb * 4);
-  // items: at most one per row of at most kChunk lookups plus one per started chunk of the others -> at most n
-  const size_t o_id = take(nn * 16), o_ps = take((nn + 16) * 4), o_li = take((nn / (kChunk + 1) + 2) * 16);
-  const size_t max_partial = (size_t)(n / kRun + n / (kChunk + 1) + 2);     // runs of long rows, and one more per long row
+  // long rows have more than kChunk lookups: at most n / (kChunk + 1) of them, with at most n / kChunk + that many chunks
+  const size_t max_lrows = nn / (kChunk + 1) + 2;
+  const size_t o_cd = take((nn / kChunk + max_lrows) * 16), o_rd = take(cc * 16), o_nm = take((nn + 16) * 4), o_li = take(max_lrows * 16);
+  const size_t max_partial = (size_t)(n / kRun) + max_lrows;     // one per run of a long row at most, and one more per long row
   const size_t o_p = take(max_partial * (size_t)D * 4);
   if (s) {
     auto u = [&](size_t o) { return reinterpret_cast<uint32_t*>(base + o); };
     s->keyA = u(o_ka); s->valA = u(o_va); s->keyB = u(o_kb); s->valB = u(o_vb); s->hist = u(o_h); s->dtot = u(o_dt);
     s->seg_start = u(o_ss); s->seg_end = u(o_ss) + cc;
-    s->plan = PlanOut{u(o_r0), u(o_r1), u(o_r2), u(o_r3), u(o_b0), u(o_b1), u(o_b2), u(o_b3)};
-    s->item_desc = reinterpret_cast<uint4*>(base + o_id); s->pos_sorted = u(o_ps); s->lrow_info = reinterpret_cast<uint4*>(base + o_li);
+    s->chunk_desc = reinterpret_cast<uint4*>(base + o_cd); s->row_desc = reinterpret_cast<uint4*>(base + o_rd); s->names = u(o_nm); s->lrow_info = reinterpret_cast<uint4*>(base + o_li);
     s->counters = reinterpret_cast<SegCounters*>(base + o_ct);
     s->partial = reinterpret_cast<float*>(base + o_p);
-    s->tiles = tiles; s->bits = bits; s->passes = passes; s->nblocks = nblocks; s->zero = base + o_z; s->zero_bytes = zero_bytes;
+    s->tiles = tiles; s->bits = bits; s->passes = passes; s->zero = base + o_z; s->zero_bytes = zero_bytes;
   }
   return off;
 }
@@ -759,12 +704,14 @@ static int segment_pipeline(bool fused, int order, const float* grad, const int6
     if (rc != SRM2_OK) return rc;
   }
   if (n > 0 && descr_phase) {
-    srm2_segment_bounds_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(skey, n, n_dev, s.seg_start, s.seg_end, cap);
+    srm2_segment_bounds_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(skey, spos, n, n_dev, s.seg_start, s.seg_end, cap,
+                                                                           pull ? pull->src_code : nullptr, s.names);
     ++launches;
   }
   ReduceArgs a{};
   a.grad = grad; a.D = (int)D; a.lpr = lpr; a.shift = shift; a.skey = skey; a.spos = spos; a.seg_start = s.seg_start; a.seg_end = s.seg_end;
-  a.item_desc = s.item_desc; a.pos_sorted = s.pos_sorted; a.lrow_info = s.lrow_info; a.counters = s.counters;
+  // what names a lookup's gradient row: its position (the sort's value array), or in pull mode its (rank, row) code
+  a.chunk_desc = s.chunk_desc; a.row_desc = s.row_desc; a.pos_sorted = pull ? s.names : spos; a.lrow_info = s.lrow_info; a.counters = s.counters;
   a.inplace = wide ? 1 : 0; a.partial = s.partial;
   a.out = out; a.pool = pool; a.slots = slots;
   if (fused && sum_phase) a.sc = AdamSc{sc[0], sc[1], sc[2], sc[3], sc[4], sc[5], sc[6], sc[7]};
@@ -779,21 +726,18 @@ static int segment_pipeline(bool fused, int order, const float* grad, const int6
     stage_end(st);
     return launch_status(launches + 1);
   }
-  // 3. plan, 4. descriptors.  A split call leaves rows without lookups alone (its index half must not write rows).
+  // 3. plan.  A split call leaves rows without lookups alone (its index half must not write rows).
   if (sort_phase && !descr_phase && !sum_phase) return launch_status(launches);
   if (descr_phase) {
     const int skip_empty = phase != kAllPhases;
-    if (fused) srm2_segment_plan_kernel<true><<<s.nblocks, kPlanThreads, 0, st>>>(a, s.plan, s.counters, s.nblocks, skip_empty);
-    else srm2_segment_plan_kernel<false><<<s.nblocks, kPlanThreads, 0, st>>>(a, s.plan, s.counters, s.nblocks, skip_empty);
-    if (n > 0)
-      srm2_segment_descr_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(skey, spos, n, n_dev, s.seg_start, s.seg_end, s.plan, s.counters,
-                                                                            fused ? slots : nullptr, pull ? pull->src_code : nullptr, s.item_desc,
-                                                                            s.pos_sorted, s.lrow_info, nu_host, nu_dev, cap);
-    launches += n > 0 ? 2 : 1;
+    const unsigned plan_blocks = (unsigned)((cap + kPlanThreads - 1) / kPlanThreads);
+    if (fused) srm2_segment_plan_kernel<true><<<plan_blocks, kPlanThreads, 0, st>>>(a, s.chunk_desc, s.row_desc, s.counters, skip_empty);
+    else srm2_segment_plan_kernel<false><<<plan_blocks, kPlanThreads, 0, st>>>(a, s.chunk_desc, s.row_desc, s.counters, skip_empty);
+    launches += 1;
     if (!sum_phase) return launch_status(launches);
   }
-  // 5. run sums (and, for widths whose lane groups do not sit inside a warp, a second kernel for the long rows)
-  const int64_t run_items_max = n * lpr;
+  // 4. run sums (and, for widths whose lane groups do not sit inside a warp, a second kernel for the long rows)
+  const int64_t run_items_max = (n / kChunk + n / (kChunk + 1) + 2 + cap) * lpr;      // long chunks + one entry per unique row
   // Many short-lived CTAs: a CTA that has to add up a row of many partial vectors does so after its last item, so the
   // sooner CTAs end the sooner those chains start; in the split form SM room also frees up every few microseconds for the
   // small kernels of the other streams (the next steps' index work).
