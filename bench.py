@@ -471,23 +471,37 @@ def run_ours(a, world, rank, local_rank):
 def reference_gpu_modules():
     """The reference's own GPU kernels (Triton; srm2/ops.py, srm2/gpu_ops.py, srm2/elara_kernels.py) where its package has
     been staged beside its compiled extensions in oracle/_ref/ — the comparison point on the same GPU.  None otherwise."""
-    ref_dir = ROOT / 'oracle' / '_ref'
-    if not (ref_dir / 'srm2' / 'ops.py').exists():
-        return None
     try:
-        from oracle import oracle as O
-        E, Dx = O.ref_cpu(), O.ref_dir()
-        if E is None:
-            return None
-        if str(ref_dir) not in sys.path:
-            sys.path.insert(0, str(ref_dir))
-        import srm2.ops as rops
-        rops._ext, rops._dir = E, Dx            # what ext() / dir_ext() return once loaded: no JIT build here
-        import srm2.gpu_ops as rgpu
-        import srm2.elara_kernels as rk
-        return rops, rgpu, rk
+        from oracle.ref_pipeline import load_reference
+        r = load_reference()
+        return None if r is None else (r['ops'], r['gpu_ops'], r['elara_kernels'])
     except Exception:
         return None
+
+
+def reference_pipeline_figures(dev):
+    """The reference's own planner + executor on this GPU (2 M-row store, 200 k-slot pool, 53,248 lookups per step, 120
+    steps, no dense model): milliseconds per step stock, with the L0 kernels and the directory re-pointed at this library,
+    and with the executor's assemble/update glue replaced by the fused kernels as well."""
+    try:
+        from oracle.ref_pipeline import load_reference, run_elara
+        ref = load_reference()
+        if ref is None:
+            return None
+        args = dict(R=2_000_000, C=200_000, dyn_slots=32_768, D=128, K=3, batch=2048, steps=120)
+        out = {}
+        for key, kw in (('reference_ms_per_step', dict(substituted=False)), ('with_this_library_ms_per_step', dict(substituted=True)),
+                        ('with_fused_executor_glue_ms_per_step', dict(substituted=True, fused_executor=True))):
+            best = None
+            for _ in range(2):                                   # the first run pays the JIT of the reference's Triton kernels
+                _, st = run_elara(ref, dev, kw['substituted'], fused_executor=kw.get('fused_executor', False), **args)
+                best = st['ms_per_step'] if best is None else min(best, st['ms_per_step'])
+            out[key] = best
+        out['note'] = ('ELARAPlanner(dir_impl=cpp) + ELARAExecutor of the reference, single thread, seeded ids and gradients; host-tier work '
+                       '(arena gathers, cpu_adam) is the reference\'s in all three')
+        return out
+    except Exception as e:
+        return {'unavailable': repr(e)[:160]}
 
 
 def kernel_figures(dev, peak):
@@ -705,6 +719,9 @@ def kernel_figures(dev, peak):
     out['dedup_212992_lookups_33.8M_rows'] = {'us': timed(lambda: ops.unique_inverse(ids, 33_800_000, sync=False)),
                                               'torch_unique_us': timed(lambda: torch.unique(ids, return_inverse=True))}
     out['directory_step'] = directory_figures(dev, timed)
+    rp = reference_pipeline_figures(dev)
+    if rp is not None:
+        out['elara_pipeline_2M_rows'] = rp
     return out
 
 

@@ -46,6 +46,7 @@ SIGNATURES = {
     'srm2_reduce_adam_index': (C.c_int, [_vp, _vp, _vp, _i64, _vp, _i64, _i64, _vp, _i64, _i32, _vp, _sz, _vp]),
     'srm2_reduce_adam_apply_f32': (C.c_int, [_vp, _vp, _vp, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _f8, _vp, _sz, _vp]),
     'srm2_peer_barrier': (C.c_int, [_vp, _i64, _i64, C.c_uint64, _vp, _i64, _vp, _vp]),
+    'srm2_executor_update_f32': (C.c_int, [_vp, _vp]),
     'srm2_assemble_f32': (C.c_int, [_vp, _i64, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, C.c_uint32, C.c_float, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                     _i64, _i64, _vp, _i64, _vp, _vp, _i64, _vp, _vp, _i64, _vp]),
     'srm2_plan_scratch_bytes': (_sz, [_i64]),
@@ -77,6 +78,18 @@ class Staged(C.Structure):
                 [('route_scr', C.c_void_p), ('route_scr_bytes', C.c_int64), ('counts', C.c_void_p), ('err', C.c_void_p), ('n_recv', C.c_void_p)] +
                 [(k, C.c_void_p) for k in ('cmat', 'recv_lid', 'recv_src', 'peer_cmat', 'peer_lid', 'peer_src', 'slot', 'peer_slot',
                                            'peer_tickets', 'ticket')])
+
+
+class Update(C.Structure):
+    """srm2_update of include/srm2_b200.h."""
+    _fields_ = ([(k, C.c_int64) for k in ('D', 'K', 'evl')] + [(k, C.c_void_p) for k in ('G', 'pool', 'glog')] + [('sc', C.c_float * 8)] +
+                [(k, C.c_void_p) for k in ('hit_pos', 'hit_slot', 'hrec_dyn', 'hrec_j')] + [('n_hit', C.c_int64)] +
+                [('S_pos', C.c_void_p), ('n_S', C.c_int64)] +
+                [('fullN', C.c_void_p), ('N_pos', C.c_void_p), ('nNa', C.c_int64), ('nNp', C.c_int64), ('nNc', C.c_int64)] +
+                [('fullL', C.c_void_p), ('L_pos', C.c_void_p), ('nLa', C.c_int64), ('nLp', C.c_int64), ('nLc', C.c_int64)] +
+                [('ff', C.c_void_p), ('F_pos', C.c_void_p), ('nFa', C.c_int64), ('nFn', C.c_int64)] +
+                [('evM_slot', C.c_void_p), ('n_evM', C.c_int64), ('evl_src', C.c_void_p), ('n_evl', C.c_int64)] +
+                [(k, C.c_void_p) for k in ('N_adm_slot', 'L_adm_slot', 'F_adm_slot', 'adm_rec_dyn', 'og', 'of', 'oe')])
 
 
 _lib = None

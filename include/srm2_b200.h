@@ -362,6 +362,38 @@ int srm2_reduce_adam_apply_f32(float* pool, const int64_t* slots, const float* g
                                size_t scratch_bytes, srm2_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------------
+ * Executor update.  Replaces the GPU half of `ELARAExecutor.update` (srm2/elara.py:497-531: ~25 index_select /
+ * index_put_ / index_copy_ / cat calls and three gpu_adam launches) by three kernels on one stream:
+ *   hits   for every resident row: its gradient G[hit_pos[i]] is recorded as entry hrec_j[i] of history row hrec_dyn[i]
+ *          (when evl != 0; glog is the [Cdyn+1, K, D] history tensor, row Cdyn = trash) and applied to pool[hit_slot[i]];
+ *   pack   og [n_S + nNp + nLp, D]  = G[S_pos], G[N_pos[appended]], G[L_pos[appended]]
+ *          of [nNc + nLc + nFn + n_evM, 3, D] = Adam(fullN[compacted]), Adam(fullL[compacted]), Adam(ff[not admitted]),
+ *                                               pool[evM_slot]   (read after `hits`, before `admit`)
+ *          oe [n_evl, D]            = glog.view(-1, D)[evl_src]
+ *   admit  pool[N_adm_slot] = Adam(fullN[admitted]), pool[L_adm_slot] = Adam(fullL[admitted]), pool[F_adm_slot] =
+ *          Adam(ff[admitted]); the gradients of the admitted N and L rows become entry 0 of history row adm_rec_dyn[k]
+ *          (k counts the N admissions, then the L admissions) when evl != 0.
+ * Rows of fullN / fullL / ff are ordered as the planner emits them: admitted, appended, compacted (N, L) and admitted,
+ * not admitted (F) — the index ranges of `p.ix` in the reference.  fullN, fullL and ff are not modified.  Positions,
+ * slots and history indices are int64.  sc: the eight scalars of srm2_adam_scalars for this step.  D % 4 == 0 and
+ * 16-byte aligned float buffers, SRM2_ERR_UNSUPPORTED otherwise.  Every member is 8 bytes wide except sc. */
+typedef struct srm2_update {
+  int64_t D, K, evl;
+  const float* G; float* pool; float* glog;
+  float sc[8];
+  const int64_t* hit_pos; const int64_t* hit_slot; const int64_t* hrec_dyn; const int64_t* hrec_j; int64_t n_hit;
+  const int64_t* S_pos; int64_t n_S;
+  const float* fullN; const int64_t* N_pos; int64_t nNa, nNp, nNc;
+  const float* fullL; const int64_t* L_pos; int64_t nLa, nLp, nLc;
+  const float* ff; const int64_t* F_pos; int64_t nFa, nFn;
+  const int64_t* evM_slot; int64_t n_evM;
+  const int64_t* evl_src; int64_t n_evl;
+  const int64_t* N_adm_slot; const int64_t* L_adm_slot; const int64_t* F_adm_slot; const int64_t* adm_rec_dyn;
+  float* og; float* of; float* oe;
+} srm2_update;
+int srm2_executor_update_f32(const srm2_update* u /* host */, srm2_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------------
  * Fused assemble.  Replaces the body of `ELARAExecutor.assemble` (srm2/elara.py:479-489: torch.empty, init_rows,
  * replay_rows and ten index_select / index_copy_ calls) by one kernel.  W [n, D] receives one weight row per unique row of
  * the step from five sources, each given as (positions in W, source):

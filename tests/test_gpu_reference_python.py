@@ -14,18 +14,11 @@ the folder is untracked test infrastructure and travels with the working tree). 
     compared bit for bit.  First at a middle size, then at the state-directory configuration's own size (33.8 M-row
     store, 8 M-row pool, K = 3, 212,992 lookups per step, 100 steps).
 """
-import collections
-import sys
-from pathlib import Path
-
-import numpy as np
 import pytest
 import torch
 
 pytestmark = pytest.mark.gpu
 
-ROOT = Path(__file__).resolve().parent.parent
-REF = ROOT / 'oracle' / '_ref'
 HYP = (1e-3, 0.9, 0.999, 1e-8)
 
 
@@ -39,20 +32,11 @@ def dev():
 @pytest.fixture(scope='module')
 def ref(dev):
     """The reference's srm2 package with its two compiled extensions already loaded (no JIT build on the box)."""
-    if not (REF / 'srm2' / 'ops.py').exists():
-        pytest.skip('oracle/_ref/srm2 is not staged (python oracle/build_ref.py --ref <reference checkout>)')
-    from oracle import oracle as O
-    E, Dx = O.ref_cpu(), O.ref_dir()
-    if E is None or Dx is None:
-        pytest.skip('the compiled reference extensions are missing')
-    if str(REF) not in sys.path:
-        sys.path.insert(0, str(REF))
-    import srm2.ops as rops
-    rops._ext, rops._dir = E, Dx               # what ext() / dir_ext() return once loaded (srm2/ops.py:19-39)
-    import srm2.gpu_ops as rgpu
-    import srm2.elara as relara
-    import srm2.executor as rexec
-    return dict(ops=rops, gpu_ops=rgpu, elara=relara, executor=rexec, E=E, Dx=Dx)
+    from oracle.ref_pipeline import load_reference
+    r = load_reference()
+    if r is None:
+        pytest.skip('oracle/_ref is not staged (python oracle/build_ref.py --ref <reference checkout>)')
+    return r
 
 
 def same_bits(a, b):
@@ -133,80 +117,13 @@ def test_replay_262144_rows_by_64(dev, ref):
 
 
 # ------------------------------------------------------------------------------------------------ end to end
-def run_elara(ref, dev, substituted, R, C, dyn_slots, D, K, batch, steps, seed=42, L=8, depth=3):
-    """One training-shaped run of the reference's planner + executor; returns the final state as a dict of tensors."""
-    from elara_b200 import synth
-    relara, rexec, rops = ref['elara'], ref['executor'], ref['ops']
-    stock = dict(e_init=relara.init_rows, e_replay=relara.replay_rows, e_adam=relara.gpu_adam, x_init=rexec.init_rows,
-                 x_replay=rexec.replay_rows, x_adam=rexec.gpu_adam, x_table=rexec.ScalarTable, dir_ext=rops.dir_ext)
-    if substituted:        # the re-pointing a maintainer does (the names the reference's modules resolve at call time)
-        import elara_b200.ops as b_ops
-        import elara_b200.gpu_ops as b_gpu
-        relara.init_rows = rexec.init_rows = b_gpu.init_rows
-        relara.replay_rows = rexec.replay_rows = b_gpu.replay_rows
-        relara.gpu_adam = rexec.gpu_adam = b_ops.gpu_adam
-        rexec.ScalarTable = b_gpu.ScalarTable
-        rops.dir_ext = b_ops.dir_ext
-    try:
-        sizes, offs = synth.table_sizes(R, 26, seed=seed)
-        ids = [torch.from_numpy(synth.zipf_lookups(sizes, offs, batch, 1.1, seed, s + 1)).to(dev) for s in range(steps)]
-        U = [torch.unique(i) for i in ids]
-        # static hot set: the most frequent rows of the first ten batches
-        head = torch.cat(ids[:10])
-        uu, cc = torch.unique(head, return_counts=True)
-        n0 = min(C - dyn_slots, uu.numel())
-        static_rows = uu[torch.argsort(cc, descending=True, stable=True)[:n0]].sort().values
-        bound = float(np.sqrt(1.0 / sizes.max()))
-        cfg = dict(lr=HYP[0], b1=HYP[1], b2=HYP[2], eps=HYP[3], seed=seed, bound=bound, max_step=steps)
-        pl = relara.ELARAPlanner(R, C, K, 'static', 'ttl', 'T', static_rows, L, dev, torch.from_numpy(offs),
-                                 torch.full((26,), K, dtype=torch.int8), evict_logs=1, dir_impl='cpp')
-        ex = relara.ELARAExecutor(R, D, cfg, pl, dev, threads=8, depth=depth)
-        ex.load_static()
-        gen = torch.Generator(device=dev).manual_seed(seed)
-        for j in range(min(steps, L + 1)):
-            pl.observe(j + 1, U[j])
-        nxt = [0]
+from oracle.ref_pipeline import run_elara as _run_elara
 
-        def get_plan():
-            s = nxt[0]
-            nxt[0] += 1
-            if s + L + 1 < steps:
-                pl.observe(s + L + 2, U[s + L + 1])
-            p = pl.plan(s + 1, U[s], [U[s + k] for k in range(1, depth) if s + k < steps])
-            if p.barrier:
-                ex.mark_barrier(p.s)
-            return p
-        ahead = collections.deque()
-        for _ in range(min(steps, depth - 1)):
-            ahead.append(get_plan())
-            ex.enqueue_gather(ahead[-1])
-        for s in range(steps):
-            p = ahead.popleft()
-            if s + depth - 1 < steps:
-                ahead.append(get_plan())
-                ex.enqueue_gather(ahead[-1])
-            W, bufs = ex.assemble(p)
-            gW = torch.randn(p.n, D, device=dev, generator=gen) * 1e-3
-            ex.update(p, gW, bufs)
-        ex.drain()
-        torch.cuda.synchronize(dev)
-        Kk, Lcap, Cdyn = pl.Kmax, pl.log_cap, pl.Cdyn
-        nf = int(pl.n_lfree)
-        ent = pl.ent[:R * Kk]
-        live_ids = ent[ent >= 0].long().cpu()
-        out = dict(code=pl.code, loc=pl.loc[:R], ent=ent, lstep=pl.lstep[:Lcap], lfree=pl.lfree[:nf], n_lfree=pl.n_lfree,
-                   log_top=pl.log_top, mat_top=pl.mat_top, live=pl.live, adm_c0=pl.adm_c0, rj=pl.rj, pstep=pl.pstep[:Cdyn],
-                   kthr=pl.kthr, toff=pl.toff, slot_of=pl.slot_of, slot_row=pl.slot_row, rok=pl.rok,
-                   free=pl.free, dyn_slots=pl.dyn_slots, tcount=pl.tcount, pool=ex.pool, glog=ex.glog[:Cdyn],
-                   mat=ex.store.mat[:int(pl.mat_top)].clone(), live_logs=ex.store.logs[live_ids].clone(),
-                   W_last=W)
-        stats = dict(pl.stats)
-        ex.close()
-        return out, stats
-    finally:
-        relara.init_rows, relara.replay_rows, relara.gpu_adam = stock['e_init'], stock['e_replay'], stock['e_adam']
-        rexec.init_rows, rexec.replay_rows, rexec.gpu_adam = stock['x_init'], stock['x_replay'], stock['x_adam']
-        rexec.ScalarTable, rops.dir_ext = stock['x_table'], stock['dir_ext']
+
+def run_elara(*args, **kw):
+    out, stats = _run_elara(*args, **kw)
+    stats.pop('ms_per_step', None)            # the timing is for the benchmark, not part of the comparison
+    return out, stats
 
 
 def compare_runs(a, b):
@@ -236,3 +153,14 @@ def test_reference_planner_and_executor_with_this_library(dev, ref, case):
         assert st_a[key] > 0, f'{key} never happened in this run'
     assert int(stock['live']) > 0 and int(stock['mat_top']) > 0
     compare_runs(stock, ours)
+
+
+def test_fused_executor_glue_under_the_reference_pipeline(dev, ref):
+    """The executor's GPU glue replaced as well: assemble() through the fused assemble kernel and update() through the three
+    update kernels (srm2/elara.py:479-489, 497-532), everything else the reference's own code.  Same final state, bit for
+    bit, as the stock run — with and without recorded resident histories."""
+    args = dict(R=2_000_000, C=200_000, dyn_slots=32_768, D=128, K=3, batch=2048, steps=120)
+    stock, st_a = run_elara(ref, dev, False, **args)
+    fused, st_b = run_elara(ref, dev, True, fused_executor=True, **args)
+    assert st_a == st_b
+    compare_runs(stock, fused)
