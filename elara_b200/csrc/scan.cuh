@@ -69,9 +69,10 @@ __device__ __forceinline__ uint64_t block_exclusive_scan64(uint64_t v, uint64_t*
 }
 
 // out[i] = sum_{k<i} in[i]  for i < count (count read from *count_dev when count_dev != nullptr, else count_host);
-// count is clamped to count_cap (the allocated length); optionally out[count] = total and *total_out = total.  One CTA of kScanThreads threads; in == out allowed.
+// count is clamped to count_cap (the allocated length); optionally out[count] = total and *total_out = total.  One CTA of kScanThreads threads.
+// in == out is allowed (and used by the sort): the two pointers are therefore not declared __restrict__.
 static __global__ void __launch_bounds__(kScanThreads)
-srm2_scan_exclusive_u32_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out, int64_t count_host,
+srm2_scan_exclusive_u32_kernel(const uint32_t* in, uint32_t* out, int64_t count_host,
                                const int64_t* __restrict__ count_dev, int64_t count_cap, int write_tail,
                                uint32_t* __restrict__ total_out) {
   __shared__ uint32_t ws[33];

@@ -51,8 +51,10 @@ class _DirExt:
         nb = L.srm2_dir_scratch_bytes(int(items))
         buf = self._scr.get(dev)
         if buf is None or buf.numel() < nb:
-            buf = torch.zeros(max(nb, 4096) * 2, dtype=torch.uint8, device=dev)
-            self._scr[dev] = buf
+            new = torch.zeros(max(nb, 4096) * 2, dtype=torch.uint8, device=dev)
+            if buf is not None:      # the head of the buffer holds the sticky status word of the plan step under way
+                new[:4096].copy_(buf[:4096])
+            self._scr[dev] = buf = new
         return buf
 
     def elara_dir_a(self, st, pv, hs, L_row, L_cnt, ev_slot, s):

@@ -73,10 +73,12 @@ def replay_rows(rows, logs, offs, steps, cnt, D, K, seed, bound, table, out=None
 
 
 def assemble(n, D, pool, hit_pos, hit_slot, N_pos, N_row, L_pos, L_row, logs, L_off, L_steps, L_cnt, K, seed, bound, table,
-             ff, F_pos, sw, S_pos):
+             ff, F_pos, sw, S_pos, allow_separate_calls=False):
     """The working matrix of a step in one kernel (reference: the body of ELARAExecutor.assemble, srm2/elara.py:479-489).
     Returns (W [n,D], fullN [n_N,3,D] or None, fullL [n_L,3,D] or None) — the reference returns W, (fullN, fullL, ff).
-    Index tensors are cuda int64; any of the five groups may be empty (pass empty tensors)."""
+    Index tensors are cuda int64; any of the five groups may be empty (pass empty tensors).
+    The fused kernel needs D % 4 == 0, K <= 8 and 16-byte aligned buffers.  Other shapes raise, unless
+    allow_separate_calls=True asks for the same result from init_rows / replay_rows and index copies."""
     dev = pool.device
     if not pool.is_cuda:
         raise RuntimeError('pool must be a CUDA tensor: this library has no CPU path')
@@ -99,7 +101,7 @@ def assemble(n, D, pool, hit_pos, hit_slot, N_pos, N_row, L_pos, L_row, logs, L_
                                           _seed32(seed), float(bound), p(fullL), p(L_pos), p(L_row), p(logs), p(L_off), p(L_steps),
                                           p(L_cnt), nL, K, table.t.data_ptr(), table.t.shape[0], p(ff), p(F_pos), nF, p(sw), p(S_pos), nS,
                                           _lib.stream_of(dev))
-    if st == _lib.SRM2_ERR_UNSUPPORTED:      # odd D / K > 8 / unaligned views: the same result from the separate kernels
+    if st == _lib.SRM2_ERR_UNSUPPORTED and allow_separate_calls:      # odd D / K > 8 / unaligned views: the same result from the separate kernels
         if nh: W.index_copy_(0, hit_pos, pool[:, 0].index_select(0, hit_slot))
         if nN: init_rows(N_row, D, seed, bound, out=fullN); W.index_copy_(0, N_pos, fullN[:, 0])
         if nL: replay_rows(L_row, logs, L_off, L_steps, L_cnt, D, K, seed, bound, table, out=fullL); W.index_copy_(0, L_pos, fullL[:, 0])

@@ -86,8 +86,9 @@ _scratch_cache = {}
 
 
 def _scratch(device, nbytes, tag):
-    """A reusable byte buffer per (device, tag); grown when needed.  The library itself allocates nothing."""
-    key = (device, tag)
+    """A reusable byte buffer per (device, tag, current stream); grown when needed.  The library itself allocates nothing.
+    Calls enqueued on different streams therefore never share scratch memory; calls on one stream are ordered by it."""
+    key = (device, tag, torch.cuda.current_stream(device).cuda_stream)
     buf = _scratch_cache.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)

@@ -46,9 +46,13 @@ def test_assemble_vs_oracle(dev, oracle, n, D, K, frac):
     t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
     L = c['L']
     table = ScalarTable(*HYP, 50, dev)
-    W, fullN, fullL = assemble(n, D, t(c['pool']), t(c['pos'][0]), t(c['hit_slot']), t(c['pos'][1]), t(c['N_row']), t(c['pos'][2]), t(L['rows']),
-                               t(L['logs']), t(L['offs']), t(L['steps']), t(L['cnt']), K, 1234, 0.01, table, t(c['ff']), t(c['pos'][3]),
-                               t(c['sw']), t(c['pos'][4]))
+    args = (n, D, t(c['pool']), t(c['pos'][0]), t(c['hit_slot']), t(c['pos'][1]), t(c['N_row']), t(c['pos'][2]), t(L['rows']),
+            t(L['logs']), t(L['offs']), t(L['steps']), t(L['cnt']), K, 1234, 0.01, table, t(c['ff']), t(c['pos'][3]), t(c['sw']), t(c['pos'][4]))
+    odd = bool(D % 4) or K > 8
+    if odd:            # not a shape of the fused kernel: refused unless the caller asks for the separate calls
+        with pytest.raises(RuntimeError):
+            assemble(*args)
+    W, fullN, fullL = assemble(*args, allow_separate_calls=odd)
     want = np.zeros((n, D), np.float32)
     want[c['pos'][0]] = c['pool'][c['hit_slot'], 0]
     if len(c['N_row']):

@@ -147,3 +147,58 @@ def test_reduce_adam_fused_equals_two_calls_and_oracle(dev, oracle, n, D, R):
     assert torch.equal(pool_a.view(torch.int32), pool_b.view(torch.int32))
     assert torch.equal(pool_a.view(torch.int32), pool_c.view(torch.int32))
     assert np.array_equal(bits(pool_a.cpu().numpy()), bits(st))
+
+
+# ------------------------------------------------------------------------------------------------ large inputs
+def _zipf_inverse(rng, n, nu):
+    """Inverse indices of n lookups over nu rows with a heavy head (every row named at least once)."""
+    inv = np.minimum((rng.pareto(1.05, n) * 40).astype(np.int64), nu - 1)
+    mask = rng.random(n) < 0.5
+    inv[mask] = rng.integers(0, nu, int(mask.sum()))
+    inv[:nu] = rng.permutation(nu)
+    return inv
+
+
+def test_segment_reduce_above_two_million_lookups(dev, oracle):
+    """2^21 lookups used to be a limit of the plan's packed scan; there is none now (lookup positions are 32-bit)."""
+    from elara_b200.ops import segment_reduce, reduce_adam
+    from elara_b200.gpu_ops import init_rows
+    rng = np.random.default_rng(21)
+    n, nu, D = (1 << 21) + 4097, 300_000, 8
+    inv = _zipf_inverse(rng, n, nu)
+    g = order_sensitive(rng, n, D)
+    got = segment_reduce(torch.from_numpy(g).to(dev), torch.from_numpy(inv).to(dev), nu).cpu().numpy()
+    want = oracle.segment_reduce(g, inv, nu)
+    assert np.array_equal(bits(got), bits(want))
+    pool = init_rows(torch.arange(nu, device=dev), D, 3, 0.01)
+    st = oracle.init_rows(np.arange(nu), D, 3, 0.01)
+    reduce_adam(pool, torch.arange(nu, device=dev), torch.from_numpy(g).to(dev), torch.from_numpy(inv).to(dev), *HYP, 2, n_unique=nu)
+    oracle.adam_rows(st, np.arange(nu), want, *HYP, 2)
+    assert np.array_equal(bits(pool.cpu().numpy()), bits(st))
+
+
+def test_segment_reduce_sort_with_separate_scan(dev, oracle):
+    """More than 2^23 (tile, digit) histogram entries: the radix passes scan their histogram with the single-CTA scan kernel
+    (in place) instead of deriving the offsets inside the scatter kernel."""
+    from elara_b200.ops import segment_reduce
+    rng = np.random.default_rng(23)
+    n, nu, D = 4_300_000, 4_000_000, 4
+    inv = rng.integers(0, nu, n)
+    inv[:nu] = rng.permutation(nu)
+    inv[nu:nu + 100_000] = 7                       # one long row as well
+    g = order_sensitive(rng, n, D)
+    got = segment_reduce(torch.from_numpy(g).to(dev), torch.from_numpy(inv).to(dev), nu).cpu().numpy()
+    assert np.array_equal(bits(got), bits(oracle.segment_reduce(g, inv, nu)))
+
+
+def test_segment_reduce_size_limit_is_reported(dev):
+    """Lookup positions are 32-bit: a count of 2^31 or more is refused on the host, before anything is enqueued."""
+    from elara_b200 import _lib
+    L = _lib.lib()
+    t = torch.zeros(64, device=dev)
+    i = torch.zeros(64, dtype=torch.int64, device=dev)
+    scr = torch.zeros(4096, dtype=torch.uint8, device=dev)
+    rc = L.srm2_segment_reduce_f32(t.data_ptr(), i.data_ptr(), 1 << 31, 4, 16, 0, 16, 1, t.data_ptr(), scr.data_ptr(), scr.numel(), 0)
+    assert rc == _lib.SRM2_ERR_UNSUPPORTED
+    with pytest.raises(RuntimeError, match='outside what the kernels are built for|size'):
+        _lib.check(rc, 'segment_reduce')
