@@ -36,11 +36,12 @@ def load_reference():
     return dict(ops=rops, gpu_ops=rgpu, elara=relara, executor=rexec, elara_kernels=rk, E=E, Dx=Dx)
 
 
-def run_elara(ref, dev, substituted, R, C, dyn_slots, D, K, batch, steps, seed=42, L=8, depth=3, fused_executor=False):
+def run_elara(ref, dev, substituted, R, C, dyn_slots, D, K, batch, steps, seed=42, L=8, depth=3, fused_executor=False, fused_plan=False):
     """One training-shaped run of the reference's planner + executor (single thread, default stream, the loop of
     srm2/train.py:409-444 without the dense model: the reduced gradient of a step is a seeded random matrix).
     substituted: gpu_adam / init_rows / replay_rows / ScalarTable / dir_ext re-pointed at this library;
-    fused_executor: assemble() and update() through the fused kernels as well.
+    fused_executor: assemble() and update() through the fused kernels as well;
+    fused_plan: ELARAPlanner.plan replaced by elara_b200.planner.plan (needs substituted=True: it uses this library's directory).
     -> (final state as a dict of tensors, planner statistics + 'ms_per_step' of the step loop)."""
     from elara_b200 import synth
     relara, rexec, rops = ref['elara'], ref['executor'], ref['ops']
@@ -54,7 +55,10 @@ def run_elara(ref, dev, substituted, R, C, dyn_slots, D, K, batch, steps, seed=4
         relara.gpu_adam = rexec.gpu_adam = b_ops.gpu_adam
         rexec.ScalarTable = b_gpu.ScalarTable
         rops.dir_ext = b_ops.dir_ext
-    stock_update, stock_assemble = relara.ELARAExecutor.update, relara.ELARAExecutor.assemble
+    stock_update, stock_assemble, stock_plan = relara.ELARAExecutor.update, relara.ELARAExecutor.assemble, relara.ELARAPlanner.plan
+    if fused_plan:
+        from elara_b200 import planner as b_planner
+        relara.ELARAPlanner.plan = b_planner.plan
     if fused_executor:     # the executor's GPU glue as well: assemble and update through the fused kernels
         from elara_b200 import executor_ops
         import elara_b200.gpu_ops as b_gpu
@@ -104,13 +108,16 @@ def run_elara(ref, dev, substituted, R, C, dyn_slots, D, K, batch, steps, seed=4
         for j in range(min(steps, L + 1)):
             pl.observe(j + 1, U[j])
         nxt = [0]
+        plan_s = [0.0]
 
         def get_plan():
             s = nxt[0]
             nxt[0] += 1
             if s + L + 1 < steps:
                 pl.observe(s + L + 2, U[s + L + 1])
-            p = pl.plan(s + 1, U[s], [U[s + k] for k in range(1, depth) if s + k < steps])
+            t_p = time.perf_counter()
+            p = pl.plan(s + 1, U[s], [U[s + k] for k in range(1, depth) if s + k < steps])      # ends with its device-to-host copy
+            plan_s[0] += time.perf_counter() - t_p
             if p.barrier:
                 ex.mark_barrier(p.s)
             return p
@@ -143,6 +150,7 @@ def run_elara(ref, dev, substituted, R, C, dyn_slots, D, K, batch, steps, seed=4
                    W_last=W)
         stats = dict(pl.stats)
         stats['ms_per_step'] = ms_per_step
+        stats['plan_ms_per_step'] = plan_s[0] * 1e3 / steps
         ex.close()
         return out, stats
     finally:
@@ -150,3 +158,4 @@ def run_elara(ref, dev, substituted, R, C, dyn_slots, D, K, batch, steps, seed=4
         rexec.init_rows, rexec.replay_rows, rexec.gpu_adam = stock['x_init'], stock['x_replay'], stock['x_adam']
         rexec.ScalarTable, rops.dir_ext = stock['x_table'], stock['dir_ext']
         relara.ELARAExecutor.update, relara.ELARAExecutor.assemble = stock_update, stock_assemble
+        relara.ELARAPlanner.plan = stock_plan

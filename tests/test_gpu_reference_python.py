@@ -122,7 +122,8 @@ from oracle.ref_pipeline import run_elara as _run_elara
 
 def run_elara(*args, **kw):
     out, stats = _run_elara(*args, **kw)
-    stats.pop('ms_per_step', None)            # the timing is for the benchmark, not part of the comparison
+    stats.pop('ms_per_step', None); stats.pop('plan_ms_per_step', None)      # the timings are for the benchmark, not part of the comparison
+    stats.pop('syncs', None)                  # the fused plan() reads the host less often
     return out, stats
 
 
@@ -164,3 +165,7 @@ def test_fused_executor_glue_under_the_reference_pipeline(dev, ref):
     fused, st_b = run_elara(ref, dev, True, fused_executor=True, **args)
     assert st_a == st_b
     compare_runs(stock, fused)
+    # ... and with the planner's plan() on the fused kernels too: nothing of the reference's GPU code is left on the step
+    fused2, st_c = run_elara(ref, dev, True, fused_executor=True, fused_plan=True, **args)
+    assert st_a == st_c
+    compare_runs(stock, fused2)
