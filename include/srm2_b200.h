@@ -362,6 +362,18 @@ int srm2_reduce_adam_apply_f32(float* pool, const int64_t* slots, const float* g
                                size_t scratch_bytes, srm2_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------------
+ * Capacity-tier arenas in device memory.  Replace `cpu_gather` / `cpu_scatter` of the reference's host extension
+ * (srm2/csrc/srm2_cpu.cpp:58-81) for arenas that live in HBM instead of host DRAM: the MAT arena [Mcap+1, 3, D] and the log
+ * arena [Lcap+1, 1, D] of `ArenaStore` (srm2/elara.py:40-48), addressed by the physical ids the planner hands out.
+ *   gather   out[i] [ncomp, D] = the first ncomp D-vectors of record ids[i] of arena [n_rec, W, D]
+ *   scatter  the first Wc D-vectors of record ids[i] = src[i] [Wc, D]   (ids distinct, as the reference's are)
+ * ids int64; an id outside [0, n_rec) is skipped and sets bit 0 of *bad (device uint32, may be NULL).  D % 4 == 0. */
+int srm2_arena_gather_f32(float* out, const float* arena, const int64_t* ids, int64_t n, int64_t n_rec, int64_t W, int64_t ncomp,
+                          int64_t D, uint32_t* bad, srm2_stream_t stream);
+int srm2_arena_scatter_f32(float* arena, const float* src, const int64_t* ids, int64_t n, int64_t n_rec, int64_t W, int64_t Wc,
+                           int64_t D, uint32_t* bad, srm2_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------------
  * Executor update.  Replaces the GPU half of `ELARAExecutor.update` (srm2/elara.py:497-531: ~25 index_select /
  * index_put_ / index_copy_ / cat calls and three gpu_adam launches) by three kernels on one stream:
  *   hits   for every resident row: its gradient G[hit_pos[i]] is recorded as entry hrec_j[i] of history row hrec_dyn[i]

@@ -56,9 +56,14 @@ def test_struct_layouts_match_the_header(tmp_path):
     src = tmp_path / 'layout.c'
     src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "srm2_b200.h"\n'
                    'int main(void) { printf("%zu %zu %zu %zu %zu\\n", sizeof(srm2_staged), offsetof(srm2_staged, pool), offsetof(srm2_staged, u),\n'
-                   '                        offsetof(srm2_staged, world), offsetof(srm2_staged, ticket)); return 0; }\n')
+                   '                        offsetof(srm2_staged, world), offsetof(srm2_staged, ticket));\n'
+                   '  printf("%zu %zu %zu %zu %zu %zu\\n", sizeof(srm2_update), offsetof(srm2_update, sc), offsetof(srm2_update, hit_pos),\n'
+                   '         offsetof(srm2_update, nNa), offsetof(srm2_update, evl_src), offsetof(srm2_update, oe)); return 0; }\n')
     exe = tmp_path / 'layout'
     subprocess.check_call(['gcc', '-I', str(ROOT / 'include'), '-o', str(exe), str(src)])
-    size, o_pool, o_u, o_world, o_ticket = map(int, subprocess.check_output([str(exe)]).split())
+    lines = subprocess.check_output([str(exe)]).decode().splitlines()
+    size, o_pool, o_u, o_world, o_ticket = map(int, lines[0].split())
     S = _lib.Staged
     assert (ctypes.sizeof(S), S.pool.offset, S.u.offset, S.world.offset, S.ticket.offset) == (size, o_pool, o_u, o_world, o_ticket)
+    U = _lib.Update
+    assert (ctypes.sizeof(U), U.sc.offset, U.hit_pos.offset, U.nNa.offset, U.evl_src.offset, U.oe.offset) == tuple(map(int, lines[1].split()))
