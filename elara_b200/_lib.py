@@ -48,6 +48,7 @@ SIGNATURES = {
     'srm2_peer_barrier': (C.c_int, [_vp, _i64, _i64, C.c_uint64, _vp, _i64, _vp, _vp]),
     'srm2_arena_gather_f32': (C.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp]),
     'srm2_arena_scatter_f32': (C.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp]),
+    'srm2_gather_rows_f32': (C.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     'srm2_executor_update_f32': (C.c_int, [_vp, _vp]),
     'srm2_assemble_f32': (C.c_int, [_vp, _i64, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, C.c_uint32, C.c_float, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                     _i64, _i64, _vp, _i64, _vp, _vp, _i64, _vp, _vp, _i64, _vp]),

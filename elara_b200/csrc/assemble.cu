@@ -89,7 +89,36 @@ srm2_assemble_kernel(AssembleArgs a) {
   }
 }
 
+// Forward gather of the step: emb[p] = W[inv[p]] (srm2/train.py:427).  W has just been written by the assemble kernel and
+// sits in L2 (n_unique x D x 4 bytes, ~25 MB for a DLRM-shaped step), so the lookups' rows are served from there: the
+// gather writes n*D*4 bytes to HBM and reads almost nothing from it.
+__global__ void __launch_bounds__(256)
+srm2_gather_rows_kernel(float* __restrict__ out, const float* __restrict__ W, const int64_t* __restrict__ inv, int64_t items, int lpr,
+                        int shift, int D, int64_t n_rows) {
+  const int64_t t = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (t >= items) return;
+  int64_t p; int j4;
+  if (shift >= 0) { p = t >> shift; j4 = (int)(t & (lpr - 1)); } else { p = t / lpr; j4 = (int)(t - p * lpr); }
+  const int64_t r = inv[p];
+  const float4 v = (r >= 0 && r < n_rows) ? *reinterpret_cast<const float4*>(W + r * D + j4 * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+  st_stream4(out + p * D + j4 * 4, v);
+}
+
 }  // namespace srm2
+
+extern "C" int srm2_gather_rows_f32(float* out, const float* W, const int64_t* inv, int64_t n, int64_t n_rows, int64_t D, srm2_stream_t stream) {
+  using namespace srm2;
+  if (n < 0 || n_rows < 0 || D <= 0) return SRM2_ERR_ARG;
+  if (n == 0) return SRM2_OK;
+  if (out == nullptr || W == nullptr || inv == nullptr) return SRM2_ERR_ARG;
+  if ((D & 3) != 0 || !aligned16(out) || !aligned16(W)) return SRM2_ERR_UNSUPPORTED;
+  const int lpr = (int)(D / 4);
+  const int shift = (lpr & (lpr - 1)) == 0 ? __builtin_ctz(lpr) : -1;
+  const int64_t items = n * lpr, blocks = (items + 255) / 256;
+  if (blocks > 0x7fffffffLL) return SRM2_ERR_UNSUPPORTED;
+  srm2_gather_rows_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(out, W, inv, items, lpr, shift, (int)D, n_rows);
+  return launch_status();
+}
 
 extern "C" int srm2_assemble_f32(float* W, int64_t n, int64_t D, const float* pool, const int64_t* hit_pos, const int64_t* hit_slot,
                                  int64_t n_hit, float* fullN, const int64_t* N_pos, const int64_t* N_row, int64_t n_N, uint32_t seed,

@@ -73,10 +73,12 @@ def replay_rows(rows, logs, offs, steps, cnt, D, K, seed, bound, table, out=None
 
 
 def assemble(n, D, pool, hit_pos, hit_slot, N_pos, N_row, L_pos, L_row, logs, L_off, L_steps, L_cnt, K, seed, bound, table,
-             ff, F_pos, sw, S_pos, allow_separate_calls=False):
+             ff, F_pos, sw, S_pos, allow_separate_calls=False, inv=None, emb_out=None):
     """The working matrix of a step in one kernel (reference: the body of ELARAExecutor.assemble, srm2/elara.py:479-489).
     Returns (W [n,D], fullN [n_N,3,D] or None, fullL [n_L,3,D] or None) — the reference returns W, (fullN, fullL, ff).
     Index tensors are cuda int64; any of the five groups may be empty (pass empty tensors).
+    inv (cuda int64 [n_lookups]) given: the forward gather of the step, emb[p] = W[inv[p]] (srm2/train.py:427), is enqueued
+    right behind the assemble kernel (into emb_out [n_lookups, D] when given) and (W, fullN, fullL, emb) is returned.
     The fused kernel needs D % 4 == 0, K <= 8 and 16-byte aligned buffers.  Other shapes raise, unless
     allow_separate_calls=True asks for the same result from init_rows / replay_rows and index copies."""
     dev = pool.device
@@ -107,6 +109,23 @@ def assemble(n, D, pool, hit_pos, hit_slot, N_pos, N_row, L_pos, L_row, logs, L_
         if nL: replay_rows(L_row, logs, L_off, L_steps, L_cnt, D, K, seed, bound, table, out=fullL); W.index_copy_(0, L_pos, fullL[:, 0])
         if nF: W.index_copy_(0, F_pos, ff[:, 0])
         if nS: W.index_copy_(0, S_pos, sw)
-        return W, fullN, fullL
+        return (W, fullN, fullL) if inv is None else (W, fullN, fullL, gather_rows(W, inv, out=emb_out))
     _lib.check(st, 'assemble')
-    return W, fullN, fullL
+    if inv is None:
+        return W, fullN, fullL
+    return W, fullN, fullL, gather_rows(W, inv, out=emb_out)
+
+
+def gather_rows(W, inv, out=None):
+    """out[p] = W[inv[p]]: `torch.index_select(W, 0, inv)` of the training step (reference: srm2/train.py:427)."""
+    if not W.is_cuda:
+        raise RuntimeError('W must be a CUDA tensor: this library has no CPU path')
+    n, D = inv.numel(), W.shape[1]
+    if out is None:
+        out = torch.empty(n, D, device=W.device)
+    if inv.dtype != torch.int64 or W.dtype != torch.float32 or not (W.is_contiguous() and inv.is_contiguous() and out.is_contiguous()) or out.numel() != n * D:
+        raise RuntimeError('W float32 [rows, D], inv int64 [n] and out float32 [n, D] must be contiguous')
+    with torch.cuda.device(W.device):
+        st = _lib.lib().srm2_gather_rows_f32(out.data_ptr(), W.data_ptr(), inv.data_ptr(), n, W.shape[0], D, _lib.stream_of(W.device))
+    _lib.check(st, 'gather_rows')
+    return out

@@ -418,6 +418,10 @@ int srm2_executor_update_f32(const srm2_update* u /* host */, srm2_stream_t stre
  * (the update step scatters them into the pool).  A position outside [0, n) is skipped.  D % 4 == 0, K <= 8 and 16-byte
  * aligned float buffers; SRM2_ERR_UNSUPPORTED otherwise (use the separate calls then).
  */
+/* Forward gather of the step, the companion of srm2_assemble_f32 on the same stream: out[p] = W[inv[p]] for the n lookups
+ * (replaces `torch.index_select(W, 0, inv)`, srm2/train.py:427).  W [n_rows, D] as just assembled (L2-resident), inv int64 [n]
+ * (an index outside [0, n_rows) yields a zero row), out [n, D].  D % 4 == 0, 16-byte aligned buffers. */
+int srm2_gather_rows_f32(float* out, const float* W, const int64_t* inv, int64_t n, int64_t n_rows, int64_t D, srm2_stream_t stream);
 int srm2_assemble_f32(float* W, int64_t n, int64_t D, const float* pool, const int64_t* hit_pos, const int64_t* hit_slot,
                       int64_t n_hit, float* fullN, const int64_t* N_pos, const int64_t* N_row, int64_t n_N, uint32_t seed,
                       float bound, float* fullL, const int64_t* L_pos, const int64_t* L_row, const float* logs,

@@ -83,3 +83,20 @@ def test_assemble_skips_bad_positions(dev):
                        torch.tensor([2, -1, n], device=dev))
     torch.cuda.synchronize()
     assert torch.equal(W[2], sw[0])
+
+
+def test_forward_gather_behind_assemble(dev):
+    """emb[p] = W[inv[p]] as the second launch of the assemble call equals torch.index_select (srm2/train.py:427)."""
+    from elara_b200.gpu_ops import assemble, gather_rows, ScalarTable
+    n, D, nl = 5000, 128, 60_000
+    g = torch.Generator(device=dev).manual_seed(3)
+    pool = torch.randn(8000, 3, D, device=dev, generator=g)
+    hit_slot = torch.randperm(8000, device=dev, generator=g)[:n]
+    pos = torch.arange(n, device=dev)
+    inv = torch.randint(0, n, (nl,), device=dev, generator=g)
+    e64 = torch.empty(0, dtype=torch.int64, device=dev); e32 = torch.empty(0, dtype=torch.int32, device=dev); ef = torch.empty(0, device=dev)
+    W, _, _, emb = assemble(n, D, pool, pos, hit_slot, e64, e64, e64, e64, ef, e64, e32, e32, 3, 1, 0.01, ScalarTable(*HYP, 5, dev), ef, e64, ef, e64,
+                            inv=inv)
+    assert torch.equal(W, pool[hit_slot, 0])
+    assert torch.equal(emb, torch.index_select(W, 0, inv))
+    assert torch.equal(gather_rows(W, torch.tensor([0, -1, n, 7], device=dev)), torch.stack([W[0], torch.zeros(D, device=dev), torch.zeros(D, device=dev), W[7]]))
