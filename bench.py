@@ -197,7 +197,7 @@ def parity_block(a, world, rank, dev):
     bound = float(np.sqrt(1.0 / sizes.max()))
     eng = ShardedSparseAdam(R, D, world, rank, dev, seed=SEED, bound=bound, hyper=HYP, max_lookups_per_rank=n,
                             group=dist.group.WORLD if world > 1 else None)
-    p2p = eng.enable_p2p(n, pull=(a.exchange == 'pull'), grad_slots=a.grad_slots) if world > 1 and a.exchange != 'nccl' else False
+    p2p = eng.enable_p2p(n, pull=(a.exchange == 'pull'), grad_slots=a.grad_slots, presum=not a.no_presum) if world > 1 and a.exchange != 'nccl' else False
     pull = bool(p2p) and a.exchange == 'pull'
     ids_all = [[synth.zipf_lookups(sizes, offs, a.batch, ALPHA, SEED + 1, s + 1, first_sample=r * a.batch) for r in range(world)]
                for s in range(steps)]
@@ -264,7 +264,7 @@ def run_ours(a, world, rank, local_rank):
     bound = float(np.sqrt(1.0 / sizes.max()))
     eng = ShardedSparseAdam(total_rows, D, world, rank, dev, seed=SEED, bound=bound, hyper=HYP,
                             max_lookups_per_rank=n, group=dist.group.WORLD if world > 1 else None)
-    p2p = eng.enable_p2p(n, pull=(a.exchange == 'pull'), grad_slots=a.grad_slots) if world > 1 and a.exchange != 'nccl' else False
+    p2p = eng.enable_p2p(n, pull=(a.exchange == 'pull'), grad_slots=a.grad_slots, presum=not a.no_presum) if world > 1 and a.exchange != 'nccl' else False
     pull = bool(p2p) and a.exchange == 'pull'
     K, W = a.steps, max(1, a.windows)
     n_ids = min(a.warmup + K * W, max(64, a.warmup + K))         # distinct batches; longer runs cycle through them
@@ -858,6 +858,7 @@ def main():
     ap.add_argument('--batch', type=int, default=8192, help='samples per GPU per step (x26 lookups)')
     ap.add_argument('--exchange', default='pull', choices=['pull', 'push', 'nccl'],
                     help='N > 1: how routed lookups reach their owner (pull = rows read over NVLink by the reduce kernel)')
+    ap.add_argument('--no-presum', action='store_true', help='N > 1, pull exchange: every lookup\'s gradient row crosses NVLink on its own (no sums prepared at the source)')
     ap.add_argument('--grad-slots', type=int, default=8, help='N > 1: peer-visible gradient buffers per rank (pull exchange)')
     ap.add_argument('--no-pipeline', action='store_true', help='N = 1: one step after the other on one stream (no look-ahead on the ids)')
     ap.add_argument('--windows', type=int, default=7, help='repetitions of the timed region of --steps steps (median reported)')

@@ -45,6 +45,9 @@ SIGNATURES = {
     'srm2_reduce_adam_nd_f32': (C.c_int, [_vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _vp, _i64, _i32, _f8, _vp, _sz, _vp]),
     'srm2_reduce_adam_index': (C.c_int, [_vp, _vp, _vp, _i64, _vp, _i64, _i64, _vp, _i64, _i32, _vp, _sz, _vp]),
     'srm2_reduce_adam_apply_f32': (C.c_int, [_vp, _vp, _vp, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _f8, _vp, _sz, _vp]),
+    'srm2_reduce_adam_apply_pull_f32': (C.c_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _f8, _vp, _sz, _vp]),
+    'srm2_presum_request': (C.c_int, [_i64, _vp, _i64, _i64, _vp, _sz, _vp, _vp]),
+    'srm2_presum_rows_f32': (C.c_int, [_vp, _i64, _i64, _vp, _vp]),
     'srm2_peer_barrier': (C.c_int, [_vp, _i64, _i64, C.c_uint64, _vp, _i64, _vp, _vp]),
     'srm2_arena_gather_f32': (C.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp]),
     'srm2_arena_scatter_f32': (C.c_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp]),
@@ -80,7 +83,17 @@ class Staged(C.Structure):
                 [(k, C.c_int64) for k in ('world', 'rank', 'cap', 'n_recv_bufs', 'n_slots', 'timeout_ns')] +
                 [('route_scr', C.c_void_p), ('route_scr_bytes', C.c_int64), ('counts', C.c_void_p), ('err', C.c_void_p), ('n_recv', C.c_void_p)] +
                 [(k, C.c_void_p) for k in ('cmat', 'recv_lid', 'recv_src', 'peer_cmat', 'peer_lid', 'peer_src', 'slot', 'peer_slot',
-                                           'peer_tickets', 'ticket')])
+                                           'peer_tickets', 'ticket')] +
+                [('presum_cap', C.c_int64)] +
+                [(k, C.c_void_p) for k in ('peer_req', 'peer_req_n', 'req', 'req_n', 'req_count', 'peer_push', 'peer_out', 'peer_tickets_req',
+                                           'peer_tickets_sum', 'presum_done')])
+
+
+class Presum(C.Structure):
+    """srm2_presum of include/srm2_b200.h (every member 8 bytes wide)."""
+    _fields_ = ([(k, C.c_int64) for k in ('world', 'rank', 'cap', 'timeout_ns')] + [('err', C.c_void_p), ('peer_tickets', C.c_void_p)] +
+                [('ticket', C.c_uint64)] +
+                [(k, C.c_void_p) for k in ('peer_req', 'peer_req_n', 'req_count', 'req', 'req_n', 'peer_out', 'done')])
 
 
 class Update(C.Structure):

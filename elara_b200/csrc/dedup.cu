@@ -82,23 +82,26 @@ srm2_unique_mark_kernel(const int64_t* __restrict__ ids, int64_t n_host, const i
     if (tag[i] != 0xffffffffu) atomicOr(bitmap + tag[i], val[i]);
 }
 
-// Per block of 1024 words: number of set bits.  The last block to finish turns bsum into its exclusive scan and
-// writes the total (= number of unique ids).
+// Per block of 1024 words: number of set bits (a CTA takes every gridDim.x-th block).  The last CTA to finish turns bsum
+// into its exclusive scan and writes the total (= number of unique ids).
 __global__ void __launch_bounds__(kDT)
 srm2_unique_count_kernel(const uint32_t* __restrict__ bitmap, uint32_t* __restrict__ bsum, uint32_t* __restrict__ counter,
                          const uint32_t* __restrict__ flag, int64_t nblocks, int64_t* __restrict__ out_count) {
   __shared__ uint32_t ws[33];
   __shared__ bool last;
-  const uint4* src = reinterpret_cast<const uint4*>(bitmap + (int64_t)blockIdx.x * kWordsPerBlock) + threadIdx.x * (kWordsPerThread / 4);
-  uint32_t c = 0;
+  for (int64_t blk = blockIdx.x; blk < nblocks; blk += gridDim.x) {
+    const uint4* src = reinterpret_cast<const uint4*>(bitmap + blk * kWordsPerBlock) + threadIdx.x * (kWordsPerThread / 4);
+    uint32_t c = 0;
 #pragma unroll
-  for (int k = 0; k < kWordsPerThread / 4; ++k) { const uint4 v = src[k]; c += __popc(v.x) + __popc(v.y) + __popc(v.z) + __popc(v.w); }
-  uint32_t total;
-  block_exclusive_scan<kDT>(c, ws, &total);
+    for (int k = 0; k < kWordsPerThread / 4; ++k) { const uint4 v = src[k]; c += __popc(v.x) + __popc(v.y) + __popc(v.z) + __popc(v.w); }
+    uint32_t total;
+    block_exclusive_scan<kDT>(c, ws, &total);
+    if (threadIdx.x == 0) bsum[blk] = total;
+    __syncthreads();                                   // ws is reused by the next block of words
+  }
   if (threadIdx.x == 0) {
-    bsum[blockIdx.x] = total;
     __threadfence();
-    last = atomicAdd(counter, 1u) == (uint32_t)(nblocks - 1);
+    last = atomicAdd(counter, 1u) == gridDim.x - 1u;
   }
   __syncthreads();
   if (!last) return;
@@ -123,41 +126,45 @@ srm2_unique_count_kernel(const uint32_t* __restrict__ bitmap, uint32_t* __restri
 // The prefixes are computed with each thread owning 4 consecutive words (one 16-byte load).
 __global__ void __launch_bounds__(kDT)
 srm2_unique_emit_kernel(const uint32_t* __restrict__ bitmap, const uint32_t* __restrict__ bsum, uint32_t* __restrict__ wprefix,
-                        int64_t* __restrict__ uniq, int64_t uniq_cap) {
+                        int64_t* __restrict__ uniq, int64_t uniq_cap, int64_t nblocks) {
   __shared__ uint32_t ws[33];
   __shared__ uint32_t s_w[kWordsPerBlock];
   __shared__ uint32_t s_p[kWordsPerBlock];
-  const int64_t wb = (int64_t)blockIdx.x * kWordsPerBlock;
-  const int t0 = threadIdx.x * kWordsPerThread;
-  uint32_t wv[kWordsPerThread];
-  const uint4* src = reinterpret_cast<const uint4*>(bitmap + wb + t0);
-  const uint32_t bbase = bsum[blockIdx.x];
-  uint32_t c = 0;
+  for (int64_t blk = blockIdx.x; blk < nblocks; blk += gridDim.x) {
+    const int64_t wb = blk * kWordsPerBlock;
+    const int t0 = threadIdx.x * kWordsPerThread;
+    uint32_t wv[kWordsPerThread];
+    const uint4* src = reinterpret_cast<const uint4*>(bitmap + wb + t0);
+    const uint32_t bbase = bsum[blk];
+    uint32_t c = 0;
 #pragma unroll
-  for (int k = 0; k < kWordsPerThread / 4; ++k) {
-    const uint4 v = src[k];
-    wv[4 * k] = v.x; wv[4 * k + 1] = v.y; wv[4 * k + 2] = v.z; wv[4 * k + 3] = v.w;
-    c += __popc(v.x) + __popc(v.y) + __popc(v.z) + __popc(v.w);
-  }
-  uint32_t total;
-  uint32_t run = bbase + block_exclusive_scan<kDT>(c, ws, &total);
-  uint32_t pf[kWordsPerThread];
-#pragma unroll
-  for (int k = 0; k < kWordsPerThread; ++k) { pf[k] = run; run += __popc(wv[k]); s_w[t0 + k] = wv[k]; s_p[t0 + k] = pf[k]; }
-  uint4* dst = reinterpret_cast<uint4*>(wprefix + wb + t0);
-#pragma unroll
-  for (int k = 0; k < kWordsPerThread / 4; ++k) dst[k] = make_uint4(pf[4 * k], pf[4 * k + 1], pf[4 * k + 2], pf[4 * k + 3]);
-  if (total == 0) return;                            // uniform: nothing to emit in this block of words
-  __syncthreads();
-  // ids: the words are dealt round-robin to the threads (word i -> thread i mod 256), so a run of dense words (the
-  // frequent ids of a table are its smallest) is spread over many threads instead of piling up in one
-  for (int i = threadIdx.x; i < kWordsPerBlock; i += kDT) {
-    uint32_t bits = s_w[i]; uint32_t r = s_p[i];
-    while (bits) {
-      const int b = __ffs(bits) - 1; bits &= bits - 1;
-      if ((int64_t)r < uniq_cap) uniq[r] = ((wb + i) << 5) + b;
-      ++r;
+    for (int k = 0; k < kWordsPerThread / 4; ++k) {
+      const uint4 v = src[k];
+      wv[4 * k] = v.x; wv[4 * k + 1] = v.y; wv[4 * k + 2] = v.z; wv[4 * k + 3] = v.w;
+      c += __popc(v.x) + __popc(v.y) + __popc(v.z) + __popc(v.w);
     }
+    uint32_t total;
+    uint32_t run = bbase + block_exclusive_scan<kDT>(c, ws, &total);
+    uint32_t pf[kWordsPerThread];
+#pragma unroll
+    for (int k = 0; k < kWordsPerThread; ++k) { pf[k] = run; run += __popc(wv[k]); s_w[t0 + k] = wv[k]; s_p[t0 + k] = pf[k]; }
+    uint4* dst = reinterpret_cast<uint4*>(wprefix + wb + t0);
+#pragma unroll
+    for (int k = 0; k < kWordsPerThread / 4; ++k) dst[k] = make_uint4(pf[4 * k], pf[4 * k + 1], pf[4 * k + 2], pf[4 * k + 3]);
+    __syncthreads();
+    // ids: the words are dealt round-robin to the threads (word i -> thread i mod 256), so a run of dense words (the
+    // frequent ids of a table are its smallest) is spread over many threads instead of piling up in one
+    if (total != 0) {                                  // uniform: anything to emit in this block of words?
+      for (int i = threadIdx.x; i < kWordsPerBlock; i += kDT) {
+        uint32_t bits = s_w[i]; uint32_t r = s_p[i];
+        while (bits) {
+          const int b = __ffs(bits) - 1; bits &= bits - 1;
+          if ((int64_t)r < uniq_cap) uniq[r] = ((wb + i) << 5) + b;
+          ++r;
+        }
+      }
+    }
+    __syncthreads();                                   // s_w, s_p and ws are reused by the next block of words
   }
 }
 
@@ -200,11 +207,11 @@ extern "C" int srm2_unique_inverse_nd_i64(const int64_t* ids, int64_t n, const i
   dedup_layout(n_rows, static_cast<char*>(scratch), &s);
   // bitmap (padded to whole blocks), block sums and the finished-blocks counter start at zero
   if (note_cuda(cudaMemsetAsync(s.bitmap, 0, (size_t)(s.nblocks * kWordsPerBlock) * 4 + 8, st))) return SRM2_ERR_CUDA;   // + counter, flag
-  const int grid_n = (int)((n + kDT - 1) / kDT < kSMs * 8 ? (n + kDT - 1) / kDT : kSMs * 8);
+  const unsigned grid_n = index_grid((n + kDT - 1) / kDT);
   const int64_t mark_blocks = (n + kDT * kMarkPerThread - 1) / (kDT * kMarkPerThread);
   if (n > 0) srm2_unique_mark_kernel<<<(unsigned)mark_blocks, kDT, 0, st>>>(ids, n, n_dev, n_rows, s.bitmap, s.flag);
-  srm2_unique_count_kernel<<<(unsigned)s.nblocks, kDT, 0, st>>>(s.bitmap, s.bsum, s.counter, s.flag, s.nblocks, out_count);
-  srm2_unique_emit_kernel<<<(unsigned)s.nblocks, kDT, 0, st>>>(s.bitmap, s.bsum, s.wprefix, uniq, uniq_cap);
+  srm2_unique_count_kernel<<<index_grid(s.nblocks), kDT, 0, st>>>(s.bitmap, s.bsum, s.counter, s.flag, s.nblocks, out_count);
+  srm2_unique_emit_kernel<<<index_grid(s.nblocks), kDT, 0, st>>>(s.bitmap, s.bsum, s.wprefix, uniq, uniq_cap, s.nblocks);
   if (n > 0) srm2_unique_inverse_kernel<<<grid_n, kDT, 0, st>>>(ids, n, n_dev, n_rows, s.bitmap, s.wprefix, inv);
   return launch_status(n > 0 ? 4 : 2);
 }

@@ -29,10 +29,9 @@
 //      that completes a row adds the row's partials (a rolling window of twelve in flight; rows with many partials are
 //      left to the whole CTA, which copies ~50 of them at a time into shared memory, double-buffered) and finishes it.
 // Gradient rows are read exactly once (D*4 bytes per lookup); everything else is small integer traffic.
-#include <cstdlib>
-
 #include "common.cuh"
 #include "exact.cuh"
+#include "peer.cuh"
 #include "scan.cuh"
 #include "sort.cuh"
 
@@ -48,6 +47,10 @@ constexpr int kPlanThreads = 256;
 struct SegCounters { uint32_t n_lchunks, n_lrows, n_parts; };
 constexpr int kMaxGradPeers = 16;
 constexpr int kPeerShift = 24;      // pull mode: a lookup is named by (source rank << 24) | row in that rank's gradient buffer
+// Pull mode with sums prepared at the source (srm2_presum_request): a name with kOutBit set is a row of the source rank's
+// buffer of prepared sums instead of its gradient buffer; kSkipName marks a lookup whose gradient is part of such a sum.
+constexpr uint32_t kOutBit = 0x800000u, kSkipName = 0xffffffffu;
+constexpr int kReqWords = 12;       // a request: {number of rows m, their positions [10], unused}
 
 struct ReduceArgs {
   const float* grad; int D; int lpr; int shift;
@@ -58,6 +61,8 @@ struct ReduceArgs {
   float* pool; const int64_t* slots; AdamSc sc;   // fused Adam: pool [C,3,D], slots[j] = pool row of unique row j
   int64_t nu_host; const int64_t* nu_dev; int64_t cap; int64_t n;
   const float* peer[kMaxGradPeers];               // pull mode: gradient buffers of all ranks (peer pointers), see grad_row
+  const float* peer_out[kMaxGradPeers];           // ... and their buffers of prepared sums (this rank's region), or unused
+  const uint32_t* err;                            // pull mode: status word of the exchange, or nullptr; non-zero: touch nothing
 };
 
 __device__ __forceinline__ int64_t load_nu(int64_t nu_host, const int64_t* nu_dev, int64_t cap) {
@@ -73,7 +78,11 @@ __device__ __forceinline__ float4 add4(const float4& a, const float4& b) {
 // of the rank that produced it and is read from there (peer memory over NVLink, plain 16-byte asynchronous copies).
 template <bool PEER>
 __device__ __forceinline__ const float* grad_row(const ReduceArgs& a, uint32_t code) {
-  if (PEER) return a.peer[code >> kPeerShift] + (int64_t)(code & ((1u << kPeerShift) - 1u)) * a.D;
+  if (PEER) {
+    const uint32_t r = code >> kPeerShift;
+    if (code & kOutBit) return a.peer_out[r] + (int64_t)(code & (kOutBit - 1u)) * a.D;
+    return a.peer[r] + (int64_t)(code & (kOutBit - 1u)) * a.D;
+  }
   return a.grad + (int64_t)code * a.D;
 }
 
@@ -100,13 +109,13 @@ srm2_segment_bounds_kernel(const uint32_t* __restrict__ skey, const uint32_t* __
                            const int64_t* __restrict__ n_dev, uint32_t* __restrict__ seg_start, uint32_t* __restrict__ seg_end,
                            int64_t cap, const uint32_t* __restrict__ src_code, uint32_t* __restrict__ names) {
   const int64_t n = eff_count(n_host, n_dev);
-  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
-  if (i >= n) return;
-  if (src_code) names[i] = src_code[spos[i]];
-  const uint32_t k = skey[i];
-  if ((int64_t)k >= cap) return;
-  if (i == 0 || skey[i - 1] != k) seg_start[k] = (uint32_t)i;
-  if (i == n - 1 || skey[i + 1] != k) seg_end[k] = (uint32_t)(i + 1);
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (int64_t)gridDim.x * 256) {
+    if (src_code) names[i] = src_code[spos[i]];
+    const uint32_t k = skey[i];
+    if ((int64_t)k >= cap) continue;
+    if (i == 0 || skey[i - 1] != k) seg_start[k] = (uint32_t)i;
+    if (i == n - 1 || skey[i + 1] != k) seg_end[k] = (uint32_t)(i + 1);
+  }
 }
 
 // ------------------------------------------------------------------------------------------ plan
@@ -131,28 +140,28 @@ __global__ void __launch_bounds__(kPlanThreads)
 srm2_segment_plan_kernel(ReduceArgs a, uint4* __restrict__ chunk_desc, uint4* __restrict__ row_desc, SegCounters* __restrict__ counters,
                          int skip_empty) {
   const int64_t nu = load_nu(a.nu_host, a.nu_dev, a.cap);
-  const int64_t j = (int64_t)blockIdx.x * kPlanThreads + threadIdx.x;
-  if (j >= nu) return;
-  const uint32_t s = a.seg_start[j], len = a.seg_end[j] - s;
-  const RowShape r = row_shape(len);
-  // the row's own item: {sorted index of its first lookup — or, for a single lookup, that lookup's name —, number of
-  // lookups (0: nothing to do under this entry), 64-bit target: the pool row (fused) or the row index}
-  const uint64_t target = FUSED ? (uint64_t)a.slots[j] : (uint64_t)j;
-  row_desc[j] = make_uint4(len == 1 ? a.pos_sorted[s] : s, (len == 0 || r.is_long) ? 0u : len, (uint32_t)target, (uint32_t)(target >> 32));
-  if (len == 0) {
-    if (!skip_empty)
-      for (int j4 = 0; j4 < a.lpr; ++j4) finish_row<FUSED>(a, (uint32_t)j, j4, make_float4(0.f, 0.f, 0.f, 0.f));
-    return;
-  }
-  if (!r.is_long) return;
-  const uint32_t c0 = atomicAdd(&counters->n_lchunks, r.chunks);
-  const uint32_t base = atomicAdd(&counters->n_parts, r.parts);
-  const uint32_t mi = atomicAdd(&counters->n_lrows, 1u);
-  a.lrow_info[mi] = make_uint4((uint32_t)j, r.runs, base, 0u);
-  for (uint32_t q = 0; q < r.chunks; ++q) {
-    const uint32_t first = s + q * (uint32_t)kChunk, L = min((uint32_t)kChunk, len - q * (uint32_t)kChunk);
-    const uint32_t slot = q == 0 ? base : base + 1u + (q - 1u) * (uint32_t)kChunkRuns;
-    chunk_desc[c0 + q] = make_uint4(first, L | kLongBit | (q == 0 ? kFirstBit : 0u), slot, mi);
+  for (int64_t j = (int64_t)blockIdx.x * kPlanThreads + threadIdx.x; j < nu; j += (int64_t)gridDim.x * kPlanThreads) {
+    const uint32_t s = a.seg_start[j], len = a.seg_end[j] - s;
+    const RowShape r = row_shape(len);
+    // the row's own item: {sorted index of its first lookup — or, for a single lookup, that lookup's name —, number of
+    // lookups (0: nothing to do under this entry), 64-bit target: the pool row (fused) or the row index}
+    const uint64_t target = FUSED ? (uint64_t)a.slots[j] : (uint64_t)j;
+    row_desc[j] = make_uint4(len == 1 ? a.pos_sorted[s] : s, (len == 0 || r.is_long) ? 0u : len, (uint32_t)target, (uint32_t)(target >> 32));
+    if (len == 0) {
+      if (!skip_empty)
+        for (int j4 = 0; j4 < a.lpr; ++j4) finish_row<FUSED>(a, (uint32_t)j, j4, make_float4(0.f, 0.f, 0.f, 0.f));
+      continue;
+    }
+    if (!r.is_long) continue;
+    const uint32_t c0 = atomicAdd(&counters->n_lchunks, r.chunks);
+    const uint32_t base = atomicAdd(&counters->n_parts, r.parts);
+    const uint32_t mi = atomicAdd(&counters->n_lrows, 1u);
+    a.lrow_info[mi] = make_uint4((uint32_t)j, r.runs, base, 0u);
+    for (uint32_t q = 0; q < r.chunks; ++q) {
+      const uint32_t first = s + q * (uint32_t)kChunk, L = min((uint32_t)kChunk, len - q * (uint32_t)kChunk);
+      const uint32_t slot = q == 0 ? base : base + 1u + (q - 1u) * (uint32_t)kChunkRuns;
+      chunk_desc[c0 + q] = make_uint4(first, L | kLongBit | (q == 0 ? kFirstBit : 0u), slot, mi);
+    }
   }
 }
 
@@ -163,6 +172,14 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+// Stages this lane's 16 bytes of a lookup's gradient row.  A lookup whose gradient went into a sum prepared at its source
+// contributes +0 instead (the running sum of a run starts at +0 and is therefore never -0, so adding +0 leaves it as it is).
+template <bool PEER>
+__device__ __forceinline__ void stage_lookup(const ReduceArgs& a, float4* slot, uint32_t name, int j4) {
+  if (PEER && name == kSkipName) *slot = make_float4(0.f, 0.f, 0.f, 0.f);
+  else cp_async16(slot, grad_row<PEER>(a, name) + j4 * 4);
+}
 
 constexpr int kRunThreads = 256;
 constexpr int kRunStageVecs = kRun + 3;                                  // gradient rows + w, m, v
@@ -262,8 +279,13 @@ srm2_segment_runsum_wide_kernel(ReduceArgs a) {
   extern __shared__ __align__(128) float4 stage[];                 // [kRunStageVecs][kRunThreads]
   uint32_t* s_long = reinterpret_cast<uint32_t*>(stage + kRunStageVecs * kRunThreads);   // behind the staging slots, so
   uint32_t& s_nlong = s_long[kLongCap];                                                  // that those stay 128-byte aligned
-  if (threadIdx.x == 0) s_nlong = 0;
+  uint32_t& s_stop = s_long[kLongCap + 1];
+  if (threadIdx.x == 0) {
+    s_nlong = 0;
+    if (PEER) s_stop = a.err != nullptr ? *reinterpret_cast<const volatile uint32_t*>(a.err) : 0u;
+  }
   __syncthreads();
+  if (PEER && s_stop != 0u) return;                  // the exchange of this (or an earlier) step failed: the shard stays as it is
   float4* mine = stage + threadIdx.x;
   const AdamSc sc = a.sc;
   const AdamFast fa = adam_fast_prepare(sc);
@@ -348,7 +370,7 @@ srm2_segment_runsum_wide_kernel(ReduceArgs a) {
       // ---- one run: every copy at once ----
       for (int q = 0; q < L; ++q) {
         const uint32_t pos = __shfl_sync(gmask, names0, gleader + q);
-        cp_async16(mine + q * kRunThreads, grad_row<PEER>(a, pos) + j4 * 4);
+        stage_lookup<PEER>(a, mine + q * kRunThreads, pos, j4);
       }
       cp_async_commit();
       cp_async_wait<0>();
@@ -364,7 +386,7 @@ srm2_segment_runsum_wide_kernel(ReduceArgs a) {
 #pragma unroll
         for (int q = 0; q < kRun / 2; ++q) {
           const uint32_t pos = __shfl_sync(gmask, nm, gleader + h * (kRun / 2) + q);
-          if (h * (kRun / 2) + q < len_r) cp_async16(mine + (h * (kRun / 2) + q) * kRunThreads, grad_row<PEER>(a, pos) + j4 * 4);
+          if (h * (kRun / 2) + q < len_r) stage_lookup<PEER>(a, mine + (h * (kRun / 2) + q) * kRunThreads, pos, j4);
         }
         cp_async_commit();
       };
@@ -431,6 +453,7 @@ __global__ void __launch_bounds__(kRunThreads)
 srm2_segment_runsum_kernel(ReduceArgs a) {
   extern __shared__ __align__(128) float4 stage[];                 // [kRunStageVecs][kRunThreads]
   float4* mine = stage + threadIdx.x;
+  if (PEER && a.err != nullptr && *reinterpret_cast<const volatile uint32_t*>(a.err) != 0u) return;
   const AdamSc sc = a.sc;
   const AdamFast fa = adam_fast_prepare(sc);
   const int64_t n_lchunks = a.counters->n_lchunks;
@@ -462,7 +485,7 @@ srm2_segment_runsum_kernel(ReduceArgs a) {
       for (int q = 0; q < kRun; ++q)
         if (q < len_r) {
           const uint32_t pos = d.y == 1u ? d.x : __ldg(a.pos_sorted + d.x + r * kRun + q);
-          cp_async16(mine + q * kRunThreads, grad_row<PEER>(a, pos) + j4 * 4);
+          stage_lookup<PEER>(a, mine + q * kRunThreads, pos, j4);
         }
       cp_async_commit();
       cp_async_wait<0>();
@@ -527,7 +550,8 @@ srm2_segment_final_kernel(ReduceArgs a, int short_rows, int chunk_rows) {
   __shared__ uint32_t s_j[kFinalWarps], s_nr[kFinalWarps], s_pb[kFinalWarps];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float4* mine = smf + (size_t)warp * short_rows * a.lpr;
-  const uint32_t n_lrows = a.counters->n_lrows;
+  if (a.err != nullptr && *reinterpret_cast<const volatile uint32_t*>(a.err) != 0u) return;   // read once per thread, before any barrier:
+  const uint32_t n_lrows = a.counters->n_lrows;                                                // the run-sum kernel has ended by now
   for (uint32_t g = blockIdx.x; g * kFinalWarps < n_lrows; g += gridDim.x) {
     const uint32_t mi = g * kFinalWarps + warp;
     uint32_t j = 0, nr = 0, pb = 0;
@@ -655,7 +679,8 @@ static int launch_runsum(const ReduceArgs& a, bool wide, int grid, cudaStream_t 
   return SRM2_OK;
 }
 
-struct PullSource { const float* const* peer_grad; int world; const uint32_t* src_code; };   // pull mode (fused, runs order only)
+// pull mode (fused, runs order only); peer_out / err: optional (sums prepared at the source, status word of the exchange)
+struct PullSource { const float* const* peer_grad; int world; const uint32_t* src_code; const float* const* peer_out; const uint32_t* err; };
 
 // phase bits: kSortPhase (radix passes) and kDescrPhase (boundaries, plan, item descriptors) together are the index half —
 // everything that depends on the lookups' row indices only; kSumPhase = the kernels that read gradients and write rows.
@@ -704,7 +729,7 @@ static int segment_pipeline(bool fused, int order, const float* grad, const int6
     if (rc != SRM2_OK) return rc;
   }
   if (n > 0 && descr_phase) {
-    srm2_segment_bounds_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(skey, spos, n, n_dev, s.seg_start, s.seg_end, cap,
+    srm2_segment_bounds_kernel<<<index_grid((n + 255) / 256), 256, 0, st>>>(skey, spos, n, n_dev, s.seg_start, s.seg_end, cap,
                                                                            pull ? pull->src_code : nullptr, s.names);
     ++launches;
   }
@@ -716,7 +741,13 @@ static int segment_pipeline(bool fused, int order, const float* grad, const int6
   a.out = out; a.pool = pool; a.slots = slots;
   if (fused && sum_phase) a.sc = AdamSc{sc[0], sc[1], sc[2], sc[3], sc[4], sc[5], sc[6], sc[7]};
   a.nu_host = nu_host; a.nu_dev = nu_dev; a.cap = cap; a.n = n;
-  if (pull && sum_phase) for (int r = 0; r < pull->world; ++r) a.peer[r] = pull->peer_grad[r];
+  if (pull && sum_phase) {
+    for (int r = 0; r < pull->world; ++r) {
+      a.peer[r] = pull->peer_grad[r];
+      a.peer_out[r] = pull->peer_out ? pull->peer_out[r] : nullptr;
+    }
+    a.err = pull->err;
+  }
   if (small) {
     const int64_t row_items = cap * lpr;
     const int grid_rows = (int)((row_items + 255) / 256 < (int64_t)kSMs * 16 ? (row_items + 255) / 256 : (int64_t)kSMs * 16);
@@ -730,7 +761,7 @@ static int segment_pipeline(bool fused, int order, const float* grad, const int6
   if (sort_phase && !descr_phase && !sum_phase) return launch_status(launches);
   if (descr_phase) {
     const int skip_empty = phase != kAllPhases;
-    const unsigned plan_blocks = (unsigned)((cap + kPlanThreads - 1) / kPlanThreads);
+    const unsigned plan_blocks = index_grid((cap + kPlanThreads - 1) / kPlanThreads);
     if (fused) srm2_segment_plan_kernel<true><<<plan_blocks, kPlanThreads, 0, st>>>(a, s.chunk_desc, s.row_desc, s.counters, skip_empty);
     else srm2_segment_plan_kernel<false><<<plan_blocks, kPlanThreads, 0, st>>>(a, s.chunk_desc, s.row_desc, s.counters, skip_empty);
     launches += 1;
@@ -741,8 +772,7 @@ static int segment_pipeline(bool fused, int order, const float* grad, const int6
   // Many short-lived CTAs: a CTA that has to add up a row of many partial vectors does so after its last item, so the
   // sooner CTAs end the sooner those chains start; in the split form SM room also frees up every few microseconds for the
   // small kernels of the other streams (the next steps' index work).
-  static const int ctas_per_sm = getenv("SRM2_RUNSUM_CTAS") ? atoi(getenv("SRM2_RUNSUM_CTAS")) : 32;
-  const int64_t cta_cap = (int64_t)kSMs * ctas_per_sm;
+  const int64_t cta_cap = (int64_t)kSMs * 32;
   const int grid_runs = (int)((run_items_max + 255) / 256 < cta_cap ? (run_items_max + 255) / 256 : cta_cap);
   const int rows_fit = (int)(kFinalSmemBytes / (D * 4));                 // partial vectors that fit the CTA's staging buffer
   const int short_rows = rows_fit / kFinalWarps, chunk_rows = rows_fit;
@@ -795,7 +825,7 @@ extern "C" int srm2_reduce_adam_pull_f32(float* pool, const int64_t* slots, cons
                                          int64_t n_unique, const int64_t* n_unique_dev, int64_t max_unique, const float sc[8],
                                          void* scratch, size_t scratch_bytes, srm2_stream_t stream) {
   if (peer_grad == nullptr || world < 1 || world > srm2::kMaxGradPeers) return SRM2_ERR_ARG;
-  const srm2::PullSource pull{peer_grad, (int)world, src_code};
+  const srm2::PullSource pull{peer_grad, (int)world, src_code, nullptr, nullptr};
   return srm2::segment_pipeline(true, SRM2_ORDER_RUNS, nullptr, inv, n, n_dev, D, n_unique, n_unique_dev, max_unique, nullptr, pool, slots, sc,
                                 scratch, scratch_bytes, static_cast<cudaStream_t>(stream), &pull);
 }
@@ -804,7 +834,7 @@ extern "C" int srm2_reduce_adam_index(const int64_t* slots, const uint32_t* src_
                                       int64_t D, int64_t n_unique, const int64_t* n_unique_dev, int64_t max_unique, int part, void* scratch,
                                       size_t scratch_bytes, srm2_stream_t stream) {
   if (part < 0 || part > 2) return SRM2_ERR_ARG;
-  const srm2::PullSource pull{nullptr, 1, src_code};
+  const srm2::PullSource pull{nullptr, 1, src_code, nullptr, nullptr};
   const int phase = part == SRM2_INDEX_SORT ? srm2::kSortPhase : (part == SRM2_INDEX_DESCRIPTORS ? srm2::kDescrPhase : srm2::kIndexPhase);
   return srm2::segment_pipeline(true, SRM2_ORDER_RUNS, nullptr, inv, n, n_dev, D, n_unique, n_unique_dev, max_unique, nullptr, nullptr, slots, nullptr,
                                 scratch, scratch_bytes, static_cast<cudaStream_t>(stream), src_code ? &pull : nullptr, phase);
@@ -815,9 +845,151 @@ extern "C" int srm2_reduce_adam_apply_f32(float* pool, const int64_t* slots, con
                                           int64_t max_unique, const float sc[8], void* scratch, size_t scratch_bytes, srm2_stream_t stream) {
   if ((grad == nullptr) == (peer_grad == nullptr) && n > 0) return SRM2_ERR_ARG;       // exactly one gradient source
   if (peer_grad != nullptr && (world < 1 || world > srm2::kMaxGradPeers)) return SRM2_ERR_ARG;
-  const srm2::PullSource pull{peer_grad, (int)world, nullptr};
+  const srm2::PullSource pull{peer_grad, (int)world, nullptr, nullptr, nullptr};
   return srm2::segment_pipeline(true, SRM2_ORDER_RUNS, grad, nullptr, n, n_dev, D, n_unique, n_unique_dev, max_unique, nullptr, pool, slots, sc,
                                 scratch, scratch_bytes, static_cast<cudaStream_t>(stream), peer_grad ? &pull : nullptr, srm2::kSumPhase);
+}
+
+extern "C" int srm2_reduce_adam_apply_pull_f32(float* pool, const int64_t* slots, const float* const* peer_grad, const float* const* peer_out,
+                                               const uint32_t* err, int64_t world, int64_t n, const int64_t* n_dev, int64_t D, int64_t n_unique,
+                                               const int64_t* n_unique_dev, int64_t max_unique, const float sc[8], void* scratch,
+                                               size_t scratch_bytes, srm2_stream_t stream) {
+  if (peer_grad == nullptr || world < 1 || world > srm2::kMaxGradPeers) return SRM2_ERR_ARG;
+  for (int r = 0; peer_out != nullptr && r < world; ++r)
+    if (peer_out[r] == nullptr || !srm2::aligned16(peer_out[r])) return SRM2_ERR_ARG;
+  const srm2::PullSource pull{peer_grad, (int)world, nullptr, peer_out, err};
+  return srm2::segment_pipeline(true, SRM2_ORDER_RUNS, nullptr, nullptr, n, n_dev, D, n_unique, n_unique_dev, max_unique, nullptr, pool, slots, sc,
+                                scratch, scratch_bytes, static_cast<cudaStream_t>(stream), &pull, srm2::kSumPhase);
+}
+
+// ------------------------------------------------------------------------------------------ sums prepared at the source
+// Owner side.  After the descriptors of a step: one thread per run of every row looks at the run's leading lookups that
+// come from one other rank; two or more of them are replaced by a single row that the source rank will have summed (in
+// the same order, from +0) and stored into this rank's buffer of sums by the time the run-sum kernel reads it.  The thread
+// takes the next free request entry for that source (atomic counters; which entry a run gets does not matter), stores
+// the request into the source's request buffer over NVLink, and renames the run's lookups: the first one to the entry in
+// this rank's buffer of sums (region of that source), the others to kSkipName.  A run that finds the request buffer full
+// stays as it is: its rows are then read from the source one by one, as without any of this.  Every other lookup of
+// another rank — further back in a run, or alone at its head — becomes a request for a single row, so that it, too,
+// arrives in this rank's memory instead of being read over NVLink by the run-sum kernel.
+namespace srm2 {
+
+__global__ void __launch_bounds__(256)
+srm2_presum_request_kernel(const uint32_t* __restrict__ skey, const uint32_t* __restrict__ seg_start, const uint32_t* __restrict__ seg_end,
+                           uint32_t* __restrict__ names, uint4* __restrict__ row_desc, int64_t n_host, const int64_t* __restrict__ n_dev,
+                           int64_t cap_rows, int rank, int world, uint32_t cap_req, PeerPtrs req, uint32_t* __restrict__ req_count, PeerPtrs req_n,
+                           PeerPtrs sig, unsigned long long ticket, uint32_t* __restrict__ err, long long timeout_ns) {
+  __shared__ uint32_t s_cnt[kMaxPeers], s_base[kMaxPeers];
+  __shared__ bool s_last;
+  const int64_t n = eff_count(n_host, n_dev);
+  const int64_t n_round = (n + 255) / 256 * 256;
+  const uint32_t pm = kOutBit - 1u;
+  bool wrote = false;
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n_round; i += (int64_t)gridDim.x * 256) {
+    if (threadIdx.x < kMaxPeers) s_cnt[threadIdx.x] = 0;
+    __syncthreads();
+    // the thread at the head of a run looks after the whole run
+    uint32_t nm[kRun], k = 0;
+    int m_max = 0, m = 0;
+    bool lone = false;
+    if (i < n) {
+      k = skey[i];
+      if ((int64_t)k < cap_rows) {
+        const uint32_t s = seg_start[k], e = seg_end[k];
+        if (((uint32_t)i - s) % (uint32_t)kRun == 0u) { m_max = (int)min((uint32_t)kRun, e - (uint32_t)i); lone = e - s == 1u; }
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < kRun; ++q) nm[q] = q < m_max ? names[i + q] : kSkipName;
+    auto from_peer = [&](uint32_t code) { const uint32_t r = code >> kPeerShift; return r != (uint32_t)rank && r < (uint32_t)world; };
+    if (m_max > 0 && from_peer(nm[0])) {               // the leading lookups that come from the rank of the first one
+      m = 1;
+      bool same = true;
+#pragma unroll
+      for (int q = 1; q < kRun; ++q) { same = same && (nm[q] >> kPeerShift) == (nm[0] >> kPeerShift); m += same ? 1 : 0; }
+    }
+    // one request for the leading group (m rows), one for every later lookup of another rank; first a place among the CTA's
+    // requests for the same source, then one range per source and CTA, taken from the source's counter
+    uint32_t loc[kRun];
+    uint32_t asks = 0;
+#pragma unroll
+    for (int q = 0; q < kRun; ++q) {
+      const bool a = q < m_max && (q == 0 ? m >= 1 : (q >= m && from_peer(nm[q])));
+      if (a) { asks |= 1u << q; loc[q] = atomicAdd(s_cnt + (nm[q] >> kPeerShift), 1u); }
+    }
+    __syncthreads();
+    if ((int)threadIdx.x < world && s_cnt[threadIdx.x] != 0u) s_base[threadIdx.x] = atomicAdd(req_count + threadIdx.x, s_cnt[threadIdx.x]);
+    __syncthreads();
+#pragma unroll
+    for (int q = 0; q < kRun; ++q) {
+      if (!(asks >> q & 1u)) continue;
+      const uint32_t src = nm[q] >> kPeerShift, idx = s_base[src] + loc[q];
+      if (idx >= cap_req) continue;                    // no room in the source's buffer: these lookups stay as they are
+      uint4* r = static_cast<uint4*>(req.p[src]) + ((size_t)rank * cap_req + idx) * (kReqWords / 4);
+      if (q == 0 && m >= 2) {
+        r[0] = make_uint4((uint32_t)m, nm[0] & pm, nm[1] & pm, m > 2 ? nm[2] & pm : 0u);
+        r[1] = make_uint4(m > 3 ? nm[3] & pm : 0u, m > 4 ? nm[4] & pm : 0u, m > 5 ? nm[5] & pm : 0u, m > 6 ? nm[6] & pm : 0u);
+        r[2] = make_uint4(m > 7 ? nm[7] & pm : 0u, m > 8 ? nm[8] & pm : 0u, m > 9 ? nm[9] & pm : 0u, 0u);
+#pragma unroll
+        for (int e = 1; e < kRun; ++e)
+          if (e < m) names[i + e] = kSkipName;
+      } else {
+        r[0] = make_uint4(1u, nm[q] & pm, 0u, 0u); r[1] = make_uint4(0u, 0u, 0u, 0u); r[2] = make_uint4(0u, 0u, 0u, 0u);
+      }
+      const uint32_t renamed = (src << kPeerShift) | kOutBit | idx;
+      names[i + q] = renamed;
+      if (lone) row_desc[k].x = renamed;               // a row of one lookup carries the name in its descriptor
+      wrote = true;
+    }
+    __syncthreads();                                   // s_cnt and s_base are reused by the next round
+  }
+  // the last CTA to finish tells every source how many requests this rank has left in its buffer, leaves the counters
+  // zero for the next call, and goes through the barrier: all ranks have left their requests everywhere
+  if (wrote) __threadfence_system();
+  __syncthreads();
+  uint32_t* done = req_count + kMaxPeers;
+  if (threadIdx.x == 0) { __threadfence(); s_last = atomicAdd(done, 1u) == gridDim.x - 1u; }
+  __syncthreads();
+  if (!s_last) return;
+  const int sidx = threadIdx.x;
+  if (sidx < world) {
+    const uint32_t c = min(*reinterpret_cast<volatile uint32_t*>(req_count + sidx), cap_req);
+    static_cast<uint32_t*>(req_n.p[sidx])[rank] = c;
+    req_count[sidx] = 0u;
+    __threadfence_system();
+  }
+  if (sidx == 0) *done = 0u;
+  if (sidx < 32) __syncwarp();
+  if (sidx < world && ticket != 0) peer_barrier_lane(sig, rank, sidx, ticket, err, timeout_ns);
+}
+
+}  // namespace srm2
+
+extern "C" int srm2_presum_request(int64_t n, const int64_t* n_dev, int64_t D, int64_t max_unique, void* scratch, size_t scratch_bytes,
+                                   const srm2_presum* ps, srm2_stream_t stream) {
+  using namespace srm2;
+  if (ps == nullptr || n < 0 || D <= 0 || max_unique < 0) return SRM2_ERR_ARG;
+  const int64_t W = ps->world;
+  if (W < 1 || W > kMaxPeers || ps->rank < 0 || ps->rank >= W || ps->cap < 1 || ps->cap >= (int64_t)kOutBit || ps->peer_req == nullptr ||
+      ps->peer_req_n == nullptr || ps->req_count == nullptr || ps->err == nullptr)
+    return SRM2_ERR_ARG;
+  if (ps->ticket != 0 && (ps->peer_tickets == nullptr || ps->timeout_ns <= 0)) return SRM2_ERR_ARG;
+  if ((D & 3) != 0 || n >= (int64_t)kOutBit || max_unique >= ((int64_t)1 << 31)) return SRM2_ERR_UNSUPPORTED;   // positions must leave kOutBit free
+  if (scratch == nullptr || !aligned16(scratch) || scratch_bytes < seg_layout(n, max_unique, D, nullptr, nullptr)) return SRM2_ERR_SCRATCH;
+  PeerPtrs pr{}, pn{}, pt{};
+  for (int r = 0; r < W; ++r) {
+    if (ps->peer_req[r] == nullptr || !aligned16(ps->peer_req[r]) || ps->peer_req_n[r] == nullptr) return SRM2_ERR_ARG;
+    if (ps->ticket != 0 && ps->peer_tickets[r] == nullptr) return SRM2_ERR_ARG;
+    pr.p[r] = ps->peer_req[r]; pn.p[r] = ps->peer_req_n[r]; pt.p[r] = ps->ticket != 0 ? ps->peer_tickets[r] : nullptr;
+  }
+  SegScratch s;
+  seg_layout(n, max_unique, D, static_cast<char*>(scratch), &s);
+  const uint32_t* skey = (s.passes & 1) ? s.keyA : s.keyB;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  srm2_presum_request_kernel<<<index_grid((n + 255) / 256), 256, 0, st>>>(skey, s.seg_start, s.seg_end, s.names, s.row_desc, n, n_dev, max_unique,
+                                                                        (int)ps->rank, (int)W, (uint32_t)ps->cap, pr, ps->req_count, pn, pt,
+                                                                        (unsigned long long)ps->ticket, ps->err, (long long)ps->timeout_ns);
+  return launch_status(1);
 }
 
 extern "C" int srm2_reduce_adam_nd_f32(float* pool, const int64_t* slots, const float* grad, const int64_t* inv, int64_t n,

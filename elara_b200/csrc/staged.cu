@@ -3,7 +3,7 @@
 // about twenty launches and an interpreted host loop needs longer to issue them than the GPU needs to run them.
 #include "common.cuh"
 
-static_assert(sizeof(srm2_staged) == 55 * 8, "srm2_staged: every member is 8 bytes wide");
+static_assert(sizeof(srm2_staged) == 66 * 8, "srm2_staged: every member is 8 bytes wide");
 
 namespace srm2 {
 namespace {
@@ -13,12 +13,13 @@ constexpr int kSets = 4;           // buffer sets: dedup, sort, descriptors and 
 
 struct Staged {
   const srm2_staged& a;
-  cudaStream_t xs, ds, so, ix, ms;
-  bool pull;
+  cudaStream_t xs, ds, so, ix, ms, pr = nullptr, pl = nullptr;
+  bool pull, presum;
   int rc = SRM2_OK;
-  explicit Staged(const srm2_staged& s) : a(s), pull(s.world > 1) {
+  explicit Staged(const srm2_staged& s) : a(s), pull(s.world > 1), presum(s.world > 1 && s.presum_cap > 0) {
     xs = static_cast<cudaStream_t>(a.streams[0]); ds = static_cast<cudaStream_t>(a.streams[1]);
     so = static_cast<cudaStream_t>(a.streams[2]); ix = static_cast<cudaStream_t>(a.streams[3]); ms = static_cast<cudaStream_t>(a.streams[4]);
+    if (pull) { pr = static_cast<cudaStream_t>(a.streams[5]); pl = static_cast<cudaStream_t>(a.streams[6]); }
   }
   cudaEvent_t ev(int stage, int64_t k) const { return static_cast<cudaEvent_t>(a.events[stage * kRing + (int)(k % kRing)]); }
   bool ok() const { return rc == SRM2_OK; }
@@ -32,13 +33,19 @@ struct Staged {
     check(srm2_peer_barrier(a.peer_tickets, a.rank, a.world, (uint64_t)*a.ticket, a.err, a.timeout_ns, nullptr, st));
   }
 
-  // stage 5 (world > 1): the routing plan of step k — local work, on the descriptor stream, which has room.  Two scratch sets:
+  srm2_presum presum_base() const {
+    srm2_presum ps{};
+    ps.world = a.world; ps.rank = a.rank; ps.cap = a.presum_cap; ps.timeout_ns = a.timeout_ns; ps.err = a.err;
+    return ps;
+  }
+
+  // stage 5 (world > 1): the routing plan of step k — local work, on a stream of its own.  Two scratch sets:
   // the names stage of step k-2 was the last reader of this one.
   char* route_set(int64_t k) const { return static_cast<char*>(a.route_scr) + (k & 1) * a.route_scr_bytes; }
   void plan(int64_t k) {
-    if (k >= 2) cuda(cudaStreamWaitEvent(ix, ev(0, k - 2), 0));
-    check(srm2_route_plan(static_cast<const int64_t*>(a.ids[k]), a.n_k[k], a.world, a.counts + (k & 1) * a.world, route_set(k), (size_t)a.route_scr_bytes, ix));
-    cuda(cudaEventRecord(ev(5, k), ix));
+    if (k >= 2) cuda(cudaStreamWaitEvent(pl, ev(0, k - 2), 0));
+    check(srm2_route_plan(static_cast<const int64_t*>(a.ids[k]), a.n_k[k], a.world, a.counts + (k & 1) * a.world, route_set(k), (size_t)a.route_scr_bytes, pl));
+    cuda(cudaEventRecord(ev(5, k), pl));
   }
   // stage 0: names of step k to their owners
   void exchange(int64_t k) {
@@ -80,21 +87,51 @@ struct Staged {
     trace(k, part == SRM2_INDEX_SORT ? 2 : 3, 0, st);
     const uint32_t* src = pull ? a.recv_src[k % a.n_recv_bufs] : nullptr;
     const int64_t* n_dev = pull ? a.n_recv + (k & 7) : nullptr;
-    check(srm2_reduce_adam_index(a.u[q], src, a.inv[q], a.n, n_dev, a.D, -1, a.counts_out + 2 * k, a.cap_u < a.n ? a.cap_u : a.n, part, a.scr_s[q],
-                                 (size_t)a.scr_s_bytes, st));
+    const int64_t cap_u = a.cap_u < a.n ? a.cap_u : a.n;
+    check(srm2_reduce_adam_index(a.u[q], src, a.inv[q], a.n, n_dev, a.D, -1, a.counts_out + 2 * k, cap_u, part, a.scr_s[q], (size_t)a.scr_s_bytes, st));
+    if (presum && part == SRM2_INDEX_DESCRIPTORS) {
+      // requests for sums prepared at the source: set k mod n_slots of every rank's request buffers (the sums of step
+      // k - n_slots, their last reader, ended on every rank before anybody left the first barrier of this step's exchange)
+      const int64_t set = k % a.n_slots;
+      srm2_presum ps = presum_base();
+      ps.peer_req = a.peer_req + set * a.world; ps.peer_req_n = a.peer_req_n + set * a.world; ps.req_count = a.req_count + set * 32;
+      ps.peer_tickets = a.peer_tickets_req; *a.ticket += 1; ps.ticket = (uint64_t)*a.ticket;
+      check(srm2_presum_request(a.n, n_dev, a.D, cap_u, a.scr_s[q], (size_t)a.scr_s_bytes, &ps, st));
+    }
     trace(k, part == SRM2_INDEX_SORT ? 2 : 3, 1, st);
     cuda(cudaEventRecord(ev(part == SRM2_INDEX_SORT ? 2 : 3, k), st));
+  }
+  // stage 6 (sums prepared at the source), between descriptors and sums on a stream of its own: this rank adds up what its
+  // peers asked for out of the step's gradient slot and stores the sums into the peers' buffers; the kernel ends with a
+  // barrier, so every rank's sums have arrived when the stage is complete.  It depends on gradients, but not on the table:
+  // with the next step's gradients in place it runs while the run-sum kernel of the step before is still at work.
+  // Three buffers of sums per rank: the stage of step k waits for this rank's sums stage of step k - 2, so it runs at most
+  // two steps ahead, and its kernel starts behind the barrier of step k - 1 (same stream), which no rank entered before its
+  // own sums stage of step k - 3 — the last reader of the buffer that is written now — had ended.
+  void prepare_sums(int64_t k) {
+    const int64_t set = k % a.n_slots;
+    cuda(cudaStreamWaitEvent(pr, ev(3, k), 0));                            // the requests are complete (barrier of the descriptors stage)
+    if (k >= 2) cuda(cudaStreamWaitEvent(pr, ev(4, k - 2), 0));
+    srm2_presum ps = presum_base();
+    ps.req = a.req[set]; ps.req_n = a.req_n[set]; ps.peer_out = a.peer_push + (k % 3) * a.world; ps.done = a.presum_done;
+    ps.peer_tickets = a.peer_tickets_sum; *a.ticket += 1; ps.ticket = (uint64_t)*a.ticket;
+    check(srm2_presum_rows_f32(a.slot[set], a.n_k[k], a.D, &ps, pr));
+    cuda(cudaEventRecord(ev(6, k), pr));
   }
   // stage 4
   void sums(int64_t k) {
     const int64_t q = k % kSets;
     cuda(cudaStreamWaitEvent(ms, ev(3, k), 0));
+    if (presum) cuda(cudaStreamWaitEvent(ms, ev(6, k), 0));                // every rank's prepared sums of this step have arrived
     trace(k, 4, 0, ms);
     float sc[8];
     check(srm2_adam_scalars(a.lr, a.b1, a.b2, a.eps, a.first_step + k, sc));
     if (a.stage_events) srm2_stage_events(a.stage_events[2 * k], a.stage_events[2 * k + 1]);
     const int64_t cap_u = a.cap_u < a.n ? a.cap_u : a.n;
-    if (pull)
+    if (presum) {
+      check(srm2_reduce_adam_apply_pull_f32(a.pool, a.u[q], a.peer_slot + (k % a.n_slots) * a.world, a.peer_out + (k % 3) * a.world, a.err, a.world, a.n,
+                                            a.n_recv + (k & 7), a.D, -1, a.counts_out + 2 * k, cap_u, sc, a.scr_s[q], (size_t)a.scr_s_bytes, ms));
+    } else if (pull)
       check(srm2_reduce_adam_apply_f32(a.pool, a.u[q], nullptr, a.peer_slot + (k % a.n_slots) * a.world, a.world, a.n, a.n_recv + (k & 7), a.D, -1,
                                        a.counts_out + 2 * k, cap_u, sc, a.scr_s[q], (size_t)a.scr_s_bytes, ms));
     else
@@ -110,6 +147,7 @@ struct Staged {
     cudaEvent_t start = ev(4, kRing - 1);
     cuda(cudaEventRecord(start, ms));
     for (cudaStream_t st : {xs, ds, so, ix}) cuda(cudaStreamWaitEvent(st, start, 0));
+    if (pull) { cuda(cudaStreamWaitEvent(pr, start, 0)); cuda(cudaStreamWaitEvent(pl, start, 0)); }
     // prologue; then every iteration enqueues one step of every stage, the oldest first, so that a stage only ever waits
     // for events that have been recorded by then
     for (int64_t k = 0; k < 5 && k < K && pull && ok(); ++k) {           // plan(k) overwrites what exchange(k-2) read
@@ -120,9 +158,11 @@ struct Staged {
     for (int64_t k = 0; k < 3 && k < K && ok(); ++k) dedup(k);
     for (int64_t k = 0; k < 2 && k < K && ok(); ++k) index(k, SRM2_INDEX_SORT);
     if (K > 0 && ok()) index(0, SRM2_INDEX_DESCRIPTORS);
+    if (presum && K > 0 && ok()) prepare_sums(0);
     for (int64_t k = 0; k < K && ok(); ++k) {
       sums(k);
       if (k + 1 < K && ok()) index(k + 1, SRM2_INDEX_DESCRIPTORS);
+      if (presum && k + 1 < K && ok()) prepare_sums(k + 1);
       if (k + 2 < K && ok()) index(k + 2, SRM2_INDEX_SORT);
       if (k + 3 < K && ok()) dedup(k + 3);
       if (pull && k + 4 < K && ok()) exchange(k + 4);
@@ -135,6 +175,10 @@ struct Staged {
       for (cudaStream_t st : {xs, ds, so, ix}) {
         cudaEvent_t j = ev(stage++, K);                                   // a ring entry nobody waits on any more
         cudaEventRecord(j, st); cudaStreamWaitEvent(ms, j, 0);
+      }
+      if (pull) {
+        cudaEvent_t j = ev(6, K); cudaEventRecord(j, pr); cudaStreamWaitEvent(ms, j, 0);
+        j = ev(5, K); cudaEventRecord(j, pl); cudaStreamWaitEvent(ms, j, 0);
       }
     }
     if (pull && ok()) barrier(ms);                                        // no rank returns while a peer may still read its slots
@@ -157,6 +201,10 @@ extern "C" int srm2_staged_steps(const srm2_staged* a) {
         a->timeout_ns <= 0 || a->route_scr == nullptr || a->counts == nullptr || a->err == nullptr || a->n_recv == nullptr || a->cmat == nullptr ||
         a->recv_lid == nullptr || a->recv_src == nullptr || a->peer_cmat == nullptr || a->peer_lid == nullptr || a->peer_src == nullptr ||
         a->slot == nullptr || a->peer_slot == nullptr || a->peer_tickets == nullptr || a->ticket == nullptr)
+      return SRM2_ERR_ARG;
+    if (a->presum_cap > 0 && (a->peer_req == nullptr || a->peer_req_n == nullptr || a->req == nullptr || a->req_n == nullptr || a->req_count == nullptr ||
+                              a->peer_push == nullptr || a->peer_out == nullptr || a->peer_tickets_req == nullptr || a->peer_tickets_sum == nullptr ||
+                              a->presum_done == nullptr))
       return SRM2_ERR_ARG;
   } else {
     for (int64_t k = 0; k < a->K; ++k)

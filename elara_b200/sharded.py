@@ -229,11 +229,13 @@ class ShardedSparseAdam:
     # Exchange fused into the routing kernel: routed lookups are stored straight into the owners' receive buffers through
     # peer pointers (NVLink), see srm2_route_plan / publish / dispatch.  Nothing is read on the host: the receive buffers
     # have a fixed capacity, unused rows carry id -1 and are ignored by the shard update.
-    def enable_p2p(self, max_lookups_per_rank, slack=1.5, pull=True, grad_slots=4):
+    def enable_p2p(self, max_lookups_per_rank, slack=1.5, pull=True, grad_slots=4, presum=True):
         """Allocates the symmetric buffers and exchanges their addresses.  Collective over the group.
         pull=True: only lookup names are exchanged and the owners read the gradient rows from `grad_slots` peer-visible
         gradient buffers of [max_lookups_per_rank, D] (grad_slot(k) is the one step k uses: write the gradients there to
         avoid a copy).  pull=False: the rows are stored into the owners' receive buffers.
+        presum (pull only): the leading lookups of a run that come from one rank are added up by that rank and cross
+        NVLink as one row (srm2_presum_*; same bits, fewer bytes); needs fewer than 2^23 lookups per rank.
         Returns True when peer access is available; otherwise the NCCL all-to-all path stays in use."""
         import ctypes as C
         import torch.distributed as dist
@@ -255,8 +257,17 @@ class ShardedSparseAdam:
             else:
                 payload = symm.empty(2 * cap * D, dtype=torch.float32, device=self.dev)        # gradient rows
                 gbuf = None
-            sig = symm.empty(16, dtype=torch.int64, device=self.dev)                               # barrier tickets
+            sig = symm.empty(48, dtype=torch.int64, device=self.dev)       # barrier tickets: exchange | requests | prepared sums
             ts = [rlid, payload, cmat, sig] + ([gbuf] if pull else [])
+            presum = bool(presum and pull and n_max < (1 << 23))
+            if presum:
+                # per (source, owner) pair: a source's n_max lookups make at most n_max / 2 requests in all; the owners share
+                # them evenly on average (row id mod W), twice that is kept per owner; a full region costs bytes, not bits
+                pcap = min(n_max // 2 + 1, max(1024, 2 * n_max // W))
+                req = symm.empty(grad_slots * W * pcap * 12, dtype=torch.int32, device=self.dev)
+                req_n = symm.empty(grad_slots * 16, dtype=torch.int32, device=self.dev)
+                outbox = symm.empty(3 * W * pcap * D, dtype=torch.float32, device=self.dev)     # three buffers of sums (step mod 3)
+                ts += [req, req_n, outbox]
             h = [symm.rendezvous(t, self.group) for t in ts]
             arr = lambda ptrs: (C.c_void_p * W)(*[int(x) for x in ptrs])
             pbytes = 4 if pull else D * 4
@@ -271,6 +282,20 @@ class ShardedSparseAdam:
             if pull:
                 peer['slots'] = grad_slots
                 peer['p_gbuf'] = [arr([h[4].buffer_ptrs[r] + s * n_max * D * 4 for r in range(W)]) for s in range(grad_slots)]
+            peer['presum'] = presum
+            if presum:
+                hr, hn, ho = h[5], h[6], h[7]
+                req_n.zero_()
+                peer.update(pcap=pcap, req=req, req_n=req_n, outbox=outbox,
+                            req_count=torch.zeros(grad_slots * 32, dtype=torch.int32, device=self.dev),
+                            presum_done=torch.zeros(1, dtype=torch.int32, device=self.dev),
+                            p_sig_req=arr([h[3].buffer_ptrs[r] + 128 for r in range(W)]), p_sig_sum=arr([h[3].buffer_ptrs[r] + 256 for r in range(W)]),
+                            p_req=[arr([hr.buffer_ptrs[r] + s * W * pcap * 48 for r in range(W)]) for s in range(grad_slots)],
+                            p_req_n=[arr([hn.buffer_ptrs[r] + s * 64 for r in range(W)]) for s in range(grad_slots)],
+                            # by step mod 3: where this rank stores what rank r asked for (its region of r's buffer of sums),
+                            # and where it finds what rank r prepared for it (region r of its own buffer)
+                            p_push=[arr([ho.buffer_ptrs[r] + ((b * W + self.rank) * pcap) * D * 4 for r in range(W)]) for b in range(3)],
+                            p_out=[arr([outbox.data_ptr() + ((b * W + r) * pcap) * D * 4 for r in range(W)]) for b in range(3)])
             rlid.fill_(-1); cmat.zero_(); sig.zero_()
             torch.cuda.synchronize(self.dev)
             dist.barrier(group=self.group)
@@ -292,12 +317,27 @@ class ShardedSparseAdam:
         _lib.check(_lib.lib().srm2_peer_barrier(P['p_sig'], self.rank, self.world, P['ticket'], P['err'].data_ptr(), self.barrier_timeout_ns,
                                                 n_recv_ptr, stream_handle), 'peer_barrier')
 
+    def _presum_struct(self, set_, parity, tickets):
+        """srm2_presum for request set `set_` (step mod grad_slots) and buffer of sums `parity` (step mod 3), with the next ticket."""
+        import ctypes as C
+        P, W, D = self._peer, self.world, self.D
+        pc = P['pcap']
+        P['ticket'] += 1
+        ps = _lib.Presum()
+        ps.world, ps.rank, ps.cap, ps.timeout_ns, ps.err = W, self.rank, pc, self.barrier_timeout_ns, P['err'].data_ptr()
+        ps.peer_tickets, ps.ticket = C.cast(tickets, C.c_void_p), P['ticket']
+        ps.peer_req, ps.peer_req_n = C.cast(P['p_req'][set_], C.c_void_p), C.cast(P['p_req_n'][set_], C.c_void_p)
+        ps.req_count = P['req_count'][set_ * 32:].data_ptr()
+        ps.req, ps.req_n = P['req'][set_ * W * pc * 12:].data_ptr(), P['req_n'][set_ * 16:].data_ptr()
+        ps.peer_out, ps.done = C.cast(P['p_push'][parity], C.c_void_p), P['presum_done'].data_ptr()
+        return ps
+
     def _check_exchange(self):
         e = int(self._peer['err'].item())
         if e != 0:
             self._peer['err'].zero_()
             raise RuntimeError('exchange failed (status %d: 1 = a receive buffer overflowed, 2 = a rank did not reach a barrier in time, '
-                               '4 = a copy did not complete)' % e)
+                               '4 = a copy did not complete, 8 = a request for a prepared sum named a row outside the gradient buffer)' % e)
 
     def grad_slot(self, k):
         """Pull mode: the peer-visible gradient buffer [max_lookups_per_rank, D] that step k reads (k mod grad_slots)."""
@@ -388,8 +428,11 @@ class ShardedSparseAdam:
         comp = torch.cuda.current_stream(self.dev)
         st = getattr(self, '_stage_streams', None)
         if st is None:
-            st = self._stage_streams = [torch.cuda.Stream(self.dev, priority=-1) for _ in range(4)]
-        xs, ds, so, ix = st
+            # the index stages above everything (small kernels in chains: what they need is to start at once), the sums
+            # prepared at the source in between (a bandwidth-bound kernel that would otherwise hold the SMs against them),
+            # the caller's stream with the run-sum kernel below (values outside the device's range are clamped)
+            st = self._stage_streams = [torch.cuda.Stream(self.dev, priority=-1 if q == 4 else -3) for q in range(6)]
+        xs, ds, so, ix, pr, pl = st
         xss, dss, sos, ixs, ms = xs.cuda_stream, ds.cuda_stream, so.cuda_stream, ix.cuda_stream, comp.cuda_stream
         if pull:
             if n_max > P['n_max']:
@@ -425,6 +468,8 @@ class ShardedSparseAdam:
         su_ptr, su_len = f['scr_u'].data_ptr(), f['scr_u'].numel()
         pool_ptr = self.pool.data_ptr()
 
+        import ctypes as C
+        presum = bool(pull and P['presum'] and getattr(self, 'presum', True))
         trace = bool(getattr(self, 'trace', False))               # timing events at the stage boundaries (diagnostics)
         if not getattr(self, 'host_loop', False):
             # the same loop inside the library (srm2_staged_steps): a step is ~20 launches, and issuing them from Python takes
@@ -433,7 +478,7 @@ class ShardedSparseAdam:
             vp = lambda xs: (C.c_void_p * len(xs))(*[int(x) for x in xs])
             ring = getattr(self, '_event_ring', None)
             if ring is None:
-                ring = self._event_ring = [torch.cuda.Event() for _ in range(96)]
+                ring = self._event_ring = [torch.cuda.Event() for _ in range(112)]
                 for e in ring:
                     e.record(comp)                                # materialise the handles
             A = _lib.Staged()
@@ -441,7 +486,7 @@ class ShardedSparseAdam:
             A.lr, A.b1, A.b2, A.eps = self.hyper
             A.pool, A.counts_out = pool_ptr, counts_out.data_ptr()
             keep = [vp([i.data_ptr() for i, _ in batches]), vp([g.data_ptr() for _, g in batches]),
-                    (C.c_int64 * K)(*[i.numel() for i, _ in batches]), vp([xss, dss, sos, ixs, ms]), vp([e.cuda_event for e in ring])]
+                    (C.c_int64 * K)(*[i.numel() for i, _ in batches]), vp([xss, dss, sos, ixs, ms, pr.cuda_stream, pl.cuda_stream]), vp([e.cuda_event for e in ring])]
             A.ids, A.grads, A.n_k, A.streams, A.events = (C.cast(x, C.c_void_p) for x in keep)
             for q in range(4):
                 A.u[q], A.inv[q], A.scr_s[q] = u_ptr[q], inv_ptr[q], ss_ptr[q]
@@ -455,6 +500,7 @@ class ShardedSparseAdam:
                 for e in tev:
                     e.record(comp)
                 t0ev.record(comp)
+                self.trace_origin = t0ev                          # the event the trace's microseconds count from
                 keep.append(vp([e.cuda_event for e in tev]))
                 A.trace_events = C.cast(keep[-1], C.c_void_p)
             A.world, A.rank = W, self.rank
@@ -468,6 +514,14 @@ class ShardedSparseAdam:
                 (A.cmat, A.recv_lid, A.recv_src, A.peer_cmat, A.peer_lid, A.peer_src, A.slot, A.peer_slot) = (C.cast(x, C.c_void_p) for x in keep[-9:-1])
                 A.peer_tickets = C.cast(P['p_sig'], C.c_void_p)
                 A.ticket = C.cast(C.pointer(tk), C.c_void_p)
+                if presum:
+                    pc = P['pcap']
+                    keep += [flat(P['p_req']), flat(P['p_req_n']), vp([P['req'][q * W * pc * 12:].data_ptr() for q in range(S)]),
+                             vp([P['req_n'][q * 16:].data_ptr() for q in range(S)]), flat(P['p_push']), flat(P['p_out'])]
+                    A.presum_cap = pc
+                    (A.peer_req, A.peer_req_n, A.req, A.req_n, A.peer_push, A.peer_out) = (C.cast(x, C.c_void_p) for x in keep[-6:])
+                    A.req_count, A.presum_done = P['req_count'].data_ptr(), P['presum_done'].data_ptr()
+                    A.peer_tickets_req, A.peer_tickets_sum = C.cast(P['p_sig_req'], C.c_void_p), C.cast(P['p_sig_sum'], C.c_void_p)
             rc = L.srm2_staged_steps(C.byref(A))
             if pull:
                 P['ticket'] = tk.value
@@ -486,7 +540,7 @@ class ShardedSparseAdam:
             self.last_local_lookups_total += nr * K
             return [counts_out[k] for k in range(K)]
         mkev = lambda: torch.cuda.Event(enable_timing=trace)
-        ev_x, ev_d, ev_i, ev_done = ([mkev() for _ in range(K)] for _ in range(4))
+        ev_x, ev_d, ev_i, ev_done, ev_p = ([mkev() for _ in range(K)] for _ in range(5))
         ev_begin = {q: [mkev() for _ in range(K)] for q in 'xdis'} if trace else None
         ev_start = mkev(); ev_start.record(comp)
         for q in st:
@@ -533,17 +587,33 @@ class ShardedSparseAdam:
             src, n_dev = (rs_ptr[b], nrecv_ptr[k & 7]) if pull else (0, 0)
             _lib.check(L.srm2_reduce_adam_index(u_ptr[q], src, inv_ptr[q], n, n_dev, D, -1, cnt_ptr[k], cap_u, 0, ss_ptr[q], ss_len, ixs),
                        'reduce_adam_index')
+            if presum:                                            # requests for sums prepared at the source (set k mod S)
+                ps = self._presum_struct(k % S, k % 3, P['p_sig_req'])
+                _lib.check(L.srm2_presum_request(n, n_dev, D, cap_u, ss_ptr[q], ss_len, C.byref(ps), ixs), 'presum_request')
             ev_i[k].record(ix)
+
+        def prepare_sums(k):        # sums prepared at the source: gradients of step k, no table; at most two steps ahead of the sums
+            pr.wait_event(ev_i[k])
+            if k >= 2:
+                pr.wait_event(ev_done[k - 2])
+            ps = self._presum_struct(k % S, k % 3, P['p_sig_sum'])
+            _lib.check(L.srm2_presum_rows_f32(slot_ptr[k % S], batches[k][0].numel(), D, C.byref(ps), pr.cuda_stream), 'presum_rows')
+            ev_p[k].record(pr)
 
         def sums(k):
             q = k % NB
             comp.wait_event(ev_i[k])
+            if presum:
+                comp.wait_event(ev_p[k])
             if trace:
                 ev_begin['s'][k].record(comp)
             sc = ops._scalars(*self.hyper, first_step + k)
             if self._stage_events:
                 L.srm2_stage_events(self._stage_events[k][0].cuda_event, self._stage_events[k][1].cuda_event)
-            if pull:
+            if presum:
+                rc = L.srm2_reduce_adam_apply_pull_f32(pool_ptr, u_ptr[q], P['p_gbuf'][k % S], P['p_out'][k % 3], err_ptr, W, n, nrecv_ptr[k & 7], D,
+                                                       -1, cnt_ptr[k], cap_u, sc, ss_ptr[q], ss_len, ms)
+            elif pull:
                 rc = L.srm2_reduce_adam_apply_f32(pool_ptr, u_ptr[q], 0, P['p_gbuf'][k % S], W, n, nrecv_ptr[k & 7], D, -1, cnt_ptr[k], cap_u, sc,
                                                   ss_ptr[q], ss_len, ms)
             else:
@@ -560,6 +630,8 @@ class ShardedSparseAdam:
         for k in range(min(2, K)):
             dedup(k)
         index(0)
+        if presum:
+            prepare_sums(0)
         if pull and K > 2:
             exchange(2)
         out = []
@@ -568,6 +640,8 @@ class ShardedSparseAdam:
             out.append(counts_out[k])
             if k + 1 < K:
                 index(k + 1)
+                if presum:
+                    prepare_sums(k + 1)
             if k + 2 < K:
                 dedup(k + 2)
             if pull and k + 3 < K:

@@ -476,16 +476,75 @@ int srm2_plan_pack(const int64_t* ev_slot, const uint8_t* rep, const int64_t* ev
                    int64_t* evM_slot, int64_t* evl_src, int64_t* flat, void* scratch, size_t scratch_bytes, srm2_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------------
+ * Pull exchange with sums prepared at the source (no counterpart in the reference).  In the pull form every lookup's
+ * gradient row crosses NVLink on its own, although most lookups belong to rows that many lookups of the same rank name,
+ * and the owner's run-sum kernel waits an NVLink round trip for each.  The order of summation (runs of ten consecutive
+ * lookups of a row, each summed from +0) allows this much: the LEADING lookups of a run that come from one rank can be
+ * added up by that rank — same values, same order, same start, hence the same bits — and travel as one row.  (Lookups
+ * further back in a run continue a sum that other ranks' rows opened and must be added one by one by the owner.)  With
+ * Zipf(1.1) lookups this more than halves the rows that cross.  The source stores what it prepared — sums and the
+ * remaining single rows alike — into the owner's memory, so the owner's run-sum kernel reads local memory only.
+ *   owner, after srm2_reduce_adam_index(..., SRM2_INDEX_DESCRIPTORS) of a step, same n / D / max_unique / scratch:
+ *     srm2_presum_request   per run: two or more leading lookups from one other rank s -> a request {m, positions[10]} in
+ *                           region `rank` of rank s's request buffer (peer store), the run's first lookup renamed to the
+ *                           entry of region s of this rank's buffer of sums, the others marked as taken; then every
+ *                           lookup of another rank that is left -> a request for that one row, renamed the same way.
+ *                           A lookup that finds its region full (cap entries per owner and source) stays as it is and is
+ *                           read from its source by the run-sum kernel.  The counts go to every source's count array,
+ *                           then the barrier (ticket != 0).  n < 2^23.
+ *   source, when the step's gradients are in place:
+ *     srm2_presum_rows_f32  sums every requested group from `grad` (this rank's [n, D] gradient rows) and stores it into
+ *                           entry idx of peer_out[o] = region `rank` of owner o's buffer of sums [cap][D] (peer store);
+ *                           its last CTA goes through the barrier (ticket != 0).  A position >= n sets bit 3 (value 8)
+ *                           of *err.
+ *   owner: srm2_reduce_adam_apply_pull_f32 = srm2_reduce_adam_apply_f32 in pull form with
+ *                           peer_out[s] = region s of this rank's buffer of sums (host array of device pointers; NULL:
+ *                           no prepared sums in this step) and err = the status word of the exchange (or NULL): when it
+ *                           is non-zero at the start of the kernel the step is not applied (a rank that missed a barrier
+ *                           must not consume half-written sums; the word is sticky).
+ * Both barriers are srm2_peer_barrier's (bounded wait, bit 1 of *err); they need ticket arrays of their own — two further
+ * sets of 16 uint64 per rank — because they run on other streams than the exchange's barriers.  All members are 8 bytes wide.
+ */
+typedef struct srm2_presum {
+  int64_t world, rank;
+  int64_t cap;                 /* request entries per (source, owner) pair and step, < 2^23 */
+  int64_t timeout_ns;
+  uint32_t* err;
+  void* const* peer_tickets;   /* (host) [world] or NULL */
+  uint64_t ticket;             /* 0: no barrier (all ranks' buffers on one device and the calls made in order) */
+  /* srm2_presum_request */
+  void* const* peer_req;       /* (host) [world]: rank s's request buffer of this step, uint32 [world][cap][12] */
+  void* const* peer_req_n;     /* (host) [world]: rank s's request counts of this step, uint32 [world] */
+  uint32_t* req_count;         /* [32] counters of this rank for this step, zero before the first call (left zero) */
+  /* srm2_presum_rows_f32 */
+  const void* req;             /* this rank's request buffer of this step */
+  const uint32_t* req_n;       /* this rank's request counts of this step */
+  void* const* peer_out;       /* (host) [world]: region `rank` of rank o's buffer of sums of this step, float [cap][D] */
+  uint32_t* done;              /* one uint32, zero before the first call (left zero) */
+} srm2_presum;
+int srm2_presum_request(int64_t n, const int64_t* n_dev, int64_t D, int64_t max_unique, void* scratch, size_t scratch_bytes,
+                        const srm2_presum* ps /* host */, srm2_stream_t stream);
+int srm2_presum_rows_f32(const float* grad, int64_t n, int64_t D, const srm2_presum* ps /* host */, srm2_stream_t stream);
+int srm2_reduce_adam_apply_pull_f32(float* pool, const int64_t* slots, const float* const* peer_grad /* host */,
+                                    const float* const* peer_out /* host or NULL */, const uint32_t* err /* or NULL */, int64_t world,
+                                    int64_t n, const int64_t* n_dev, int64_t D, int64_t n_unique, const int64_t* n_unique_dev,
+                                    int64_t max_unique, const float sc[8] /* host */, void* scratch, size_t scratch_bytes,
+                                    srm2_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------------
  * A window of K steps as a pipeline of stages on five streams, enqueued by one call (no counterpart in the reference;
  * the reference's driver is a Python loop).  It issues exactly the calls documented above, in this order per
  * iteration k — sums(k), descriptors(k+1), sort(k+2), dedup(k+3), exchange(k+4), plan(k+5) — with CUDA events between:
- *   plan (world > 1)      srm2_route_plan                                                  on streams[3] (it has room there)
+ *   plan (world > 1)      srm2_route_plan                                                  on streams[6]
  *   exchange (world > 1)  srm2_route_publish_barrier, [copy of the step's gradients into its slot],
  *                         srm2_route_dispatch_ids with the barrier in its last CTA         on streams[0]
  *   dedup                 srm2_unique_inverse_nd_i64                                       on streams[1]
  *   sort                  srm2_reduce_adam_index(SRM2_INDEX_SORT)                          on streams[2]
  *   descriptors           srm2_reduce_adam_index(SRM2_INDEX_DESCRIPTORS)                   on streams[3]
  *   sums                  srm2_reduce_adam_apply_f32 (local rows, or peer_grad at world>1) on streams[4], the caller's
+ * With presum_cap > 0 the descriptors stage ends with srm2_presum_request, a further stage on streams[5] —
+ * srm2_presum_rows_f32(k + 1), which needs that step's gradients but not the table — runs beside sums(k), and the sums
+ * stage is srm2_reduce_adam_apply_pull_f32.
  * A host loop that makes these calls itself gives the same result; this entry point exists because at ~20 launches per
  * step the host, not the GPU, bounds such a loop.  All members are 8 bytes wide.  Pointers marked (host) are host
  * arrays; everything else is device memory.  Nothing is allocated or synchronised; the call returns when the window is
@@ -501,8 +560,8 @@ typedef struct srm2_staged {
   const int64_t* n_k;                            /* (host) [K] lookups of each step; world 1: all equal n */
   int64_t* u[4]; int64_t* inv[4]; void* scr_s[4];/* four buffer sets: unique rows [cap_u], inverse [n], reduce scratch */
   int64_t scr_s_bytes; void* scr_u; int64_t scr_u_bytes;
-  void* const* streams;                          /* (host) [5] cudaStream_t */
-  void* const* events;                           /* (host) [96] cudaEvent_t without timing: 16 per stage */
+  void* const* streams;                          /* (host) [5] cudaStream_t; [7] at world > 1 */
+  void* const* events;                           /* (host) [112] cudaEvent_t without timing: 16 per stage */
   void* const* stage_events;                     /* (host) [2K] or NULL: recorded around the sums of each step */
   void* const* trace_events;                     /* (host) [K * 10] or NULL: cudaEvent_t with timing, (begin, end) of the five
                                                     stages of every step, step-major (diagnostics) */
@@ -518,6 +577,16 @@ typedef struct srm2_staged {
   const float* const* peer_slot;                 /* (host) [n_slots * world] */
   void* const* peer_tickets;                     /* (host) [world] */
   int64_t* ticket;                               /* (host) in/out: last ticket used */
+  /* world > 1, optional: sums prepared at the source (srm2_presum_*); presum_cap == 0 leaves them out */
+  int64_t presum_cap;                            /* request entries per (source, owner) pair */
+  void* const* peer_req; void* const* peer_req_n;/* (host) [n_slots * world] every rank's request buffers / count arrays */
+  const void* const* req;                        /* (host) [n_slots] this rank's request buffers */
+  const uint32_t* const* req_n;                  /* (host) [n_slots] this rank's count arrays */
+  uint32_t* req_count;                           /* [n_slots][32] counters, zero before the first call */
+  void* const* peer_push;                        /* (host) [3 * world] region `rank` of every rank's buffers of sums, by step mod 3 */
+  const float* const* peer_out;                  /* (host) [3 * world] the regions of this rank's own buffers of sums */
+  void* const* peer_tickets_req; void* const* peer_tickets_sum;   /* (host) [world] each: ticket arrays of the two barriers */
+  uint32_t* presum_done;                         /* one zero uint32 */
 } srm2_staged;
 int srm2_staged_steps(const srm2_staged* a /* host */);
 

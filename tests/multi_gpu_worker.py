@@ -62,13 +62,31 @@ def main():
     eng5.enable_p2p(batch * 26, pull=True, grad_slots=5)
     eng5.host_loop = True                                # the same stages issued from Python instead of srm2_staged_steps
     counts5 = eng5.run_steps(batches[:2], 1) + eng5.run_steps(batches[2:], 3)
+    # the pull form without sums prepared at the source (every lookup's row crosses on its own)
+    eng6 = ShardedSparseAdam(total_rows, D, world, rank, dev, seed=42, bound=0.01, hyper=HYP, max_lookups_per_rank=batch * 26,
+                             group=dist.group.WORLD)
+    eng6.enable_p2p(batch * 26, pull=True, grad_slots=4, presum=False)
+    counts6 = eng6.run_steps(batches, 1)
     torch.cuda.synchronize(dev)
+    ok6 = torch.equal(eng.pool.view(torch.int32), eng6.pool.view(torch.int32)) and sum(int(c[0]) for c in counts6) == rows_updated
     shard = eng.pool.cpu().numpy()
     ok = np.array_equal(shard.view(np.uint32), st[rank::world].view(np.uint32))
     ok = ok and torch.equal(eng.pool.view(torch.int32), eng2.pool.view(torch.int32)) and sum(int(c[0]) for c in counts) == rows_updated
     ok = ok and torch.equal(eng.pool.view(torch.int32), eng3.pool.view(torch.int32)) and sum(int(c[0]) for c in counts3) == rows_updated
     ok = ok and torch.equal(eng.pool.view(torch.int32), eng4.pool.view(torch.int32)) and sum(int(c[0]) for c in counts4) == rows_updated
     ok = ok and torch.equal(eng.pool.view(torch.int32), eng5.pool.view(torch.int32)) and sum(int(c[0]) for c in counts5) == rows_updated
+    # a longer window: every buffer set of the pipeline (gradient slots, request sets, both buffers of sums) is used again
+    more = []
+    for step in range(4, 16):
+        ids = synth.zipf_lookups(sizes, offs, batch, 1.1, 7, step, first_sample=rank * batch)
+        grad = synth.normal_f32((len(ids), D), 1e-3, 7, step, stream=10 + rank)
+        more.append((torch.from_numpy(ids).to(dev), torch.from_numpy(grad).to(dev)))
+    eng2.run_steps(more, 4); eng4.run_steps(more, 4); eng6.run_steps(more[:5], 4); eng6.run_steps(more[5:], 9)
+    torch.cuda.synchronize(dev)
+    ok6 = ok6 and torch.equal(eng2.pool.view(torch.int32), eng4.pool.view(torch.int32)) and torch.equal(eng2.pool.view(torch.int32), eng6.pool.view(torch.int32))
+    if not (ok and ok6):
+        print(f'rank {rank}: three-step checks {int(ok)}, prepared sums on/off and the longer window {int(ok6)}', flush=True)
+    ok = ok and ok6
     flag = torch.tensor([int(ok), rows_updated], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:

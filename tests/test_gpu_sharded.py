@@ -103,6 +103,116 @@ def test_pull_exchange_emulated_on_one_gpu(oracle, n, D, W):
         assert np.array_equal(pool.cpu().numpy().view(np.uint32), state[d::W].view(np.uint32)), d
 
 
+@pytest.mark.parametrize('n,D,W,pcap', [(3000, 16, 2, 3001), (40000, 128, 4, 20000), (90000, 64, 3, 40), (212992, 128, 8, 53248),
+                                        (50000, 24, 2, 30001)])
+def test_pull_exchange_with_sums_prepared_at_the_source(oracle, n, D, W, pcap):
+    """The pull exchange in which the leading lookups of a run that come from one rank are added up by that rank and read
+    by the owner as one row (srm2_presum_request / srm2_presum_rows_f32 / srm2_reduce_adam_apply_pull_f32), all W ranks'
+    buffers on one device, no barriers (the calls are made in the order the barriers would enforce).  The shards must
+    equal the single-process oracle bit for bit — also where the request regions are far too small (pcap = 40: most runs
+    stay as they were) — and the requests must cover a good part of the lookups."""
+    import ctypes as C
+    from elara_b200 import _lib, ops
+    from elara_b200.gpu_ops import init_rows
+    from elara_b200.sharded import local_rows
+    dev = torch.device('cuda:0')
+    L = _lib.lib()
+    R = 50_000
+    rng = np.random.default_rng(n + W)
+    p = np.arange(1, R + 1, dtype=np.float64) ** -1.1
+    perm0 = rng.permutation(R)
+    ids = [perm0[rng.choice(R, size=n, p=p / p.sum())].astype(np.int64) for _ in range(W)]
+    grads = [(rng.standard_normal((n, D)) * 10.0 ** rng.integers(-3, 4, size=(n, 1))).astype(np.float32) for _ in range(W)]
+    for g in grads:
+        g[rng.integers(0, n, 50)] = -0.0                         # signed zeros must come out as the one-by-one sum leaves them
+    t_ids = [torch.from_numpy(x).to(dev) for x in ids]
+    t_grads = [torch.from_numpy(x).to(dev) for x in grads]
+    cap = 3 * n + 4096
+    st = torch.cuda.current_stream(dev).cuda_stream
+    arr = lambda ts: (C.c_void_p * W)(*[t.data_ptr() for t in ts])
+    rlid = [torch.full((cap,), -1, dtype=torch.int64, device=dev) for _ in range(W)]
+    rsrc = [torch.zeros(cap, dtype=torch.int32, device=dev) for _ in range(W)]
+    cmat = [torch.zeros(W * W, dtype=torch.int64, device=dev) for _ in range(W)]
+    n_recv = torch.zeros(W, dtype=torch.int64, device=dev)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    nb = L.srm2_route_scratch_bytes(n, W)
+    scr = [torch.empty(nb, dtype=torch.uint8, device=dev) for _ in range(W)]
+    counts = torch.zeros(W, dtype=torch.int64, device=dev)
+    for r in range(W):
+        _lib.check(L.srm2_route_plan(t_ids[r].data_ptr(), n, W, counts.data_ptr(), scr[r].data_ptr(), nb, st), 'plan')
+        _lib.check(L.srm2_route_publish(counts.data_ptr(), arr(cmat), r, W, st), 'publish')
+    for r in range(W):
+        _lib.check(L.srm2_route_dispatch_ids(t_ids[r].data_ptr(), n, W, r, cmat[r].data_ptr(), arr(rlid), arr(rsrc), cap,
+                                             n_recv[r:].data_ptr(), err.data_ptr(), 0, 0, 0, scr[r].data_ptr(), nb, st), 'dispatch_ids')
+    assert int(err.item()) == 0
+    all_ids = np.concatenate(ids); all_grads = np.concatenate(grads)
+    state = oracle.init_rows(np.arange(R), D, 7, 0.01)
+    u, inv = oracle.unique_inverse(all_ids)
+    oracle.adam_rows(state, u, oracle.segment_reduce(all_grads, inv, len(u), chunk=oracle.SEGMENT_CHUNK), *HYP, 3)
+    sc = ops._scalars(*HYP, 3)
+    # per rank: request buffer [W][pcap][12], counts [W], buffer of sums [W][pcap][D]
+    req = [torch.zeros(W * pcap * 12, dtype=torch.int32, device=dev) for _ in range(W)]
+    req_n = [torch.zeros(16, dtype=torch.int32, device=dev) for _ in range(W)]
+    outbox = [torch.full((W * pcap * D,), float('nan'), device=dev) for _ in range(W)]
+    req_count = torch.zeros(32, dtype=torch.int32, device=dev)
+    done = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    keep = []
+
+    def presum(rank):
+        ps = _lib.Presum()
+        ps.world, ps.rank, ps.cap, ps.timeout_ns, ps.err, ps.ticket = W, rank, pcap, 10**9, err.data_ptr(), 0
+        ps.peer_req, ps.peer_req_n = C.cast(arr(req), C.c_void_p), C.cast(arr(req_n), C.c_void_p)
+        ps.req_count, ps.req, ps.req_n = req_count.data_ptr(), req[rank].data_ptr(), req_n[rank].data_ptr()
+        # where rank `rank` stores what owner o asked for: region `rank` of o's buffer of sums
+        keep.append((C.c_void_p * W)(*[outbox[o][rank * pcap * D:].data_ptr() for o in range(W)]))
+        ps.peer_out, ps.done = C.cast(keep[-1], C.c_void_p), done.data_ptr()
+        return ps
+
+    owners = []
+    for d in range(W):                       # every owner: dedup, index half, requests
+        nl = local_rows(R, W, d)
+        pool = init_rows(torch.arange(nl, device=dev) * W + d, D, 7, 0.01)
+        uq = torch.empty(min(cap, nl), dtype=torch.int64, device=dev); iv = torch.empty(cap, dtype=torch.int64, device=dev)
+        cnt = torch.zeros(2, dtype=torch.int64, device=dev)
+        su = torch.empty(L.srm2_unique_scratch_bytes(nl), dtype=torch.uint8, device=dev)
+        ss = torch.empty(L.srm2_segment_scratch_bytes(cap, uq.numel(), D), dtype=torch.uint8, device=dev)
+        _lib.check(L.srm2_unique_inverse_nd_i64(rlid[d].data_ptr(), cap, n_recv[d:].data_ptr(), nl, uq.data_ptr(), uq.numel(), iv.data_ptr(),
+                                                cnt.data_ptr(), su.data_ptr(), su.numel(), st), 'unique')
+        _lib.check(L.srm2_reduce_adam_index(uq.data_ptr(), rsrc[d].data_ptr(), iv.data_ptr(), cap, n_recv[d:].data_ptr(), D, -1, cnt.data_ptr(),
+                                            uq.numel(), 0, ss.data_ptr(), ss.numel(), st), 'index')
+        ps = presum(d)
+        _lib.check(L.srm2_presum_request(cap, n_recv[d:].data_ptr(), D, uq.numel(), ss.data_ptr(), ss.numel(), C.byref(ps), st), 'request')
+        owners.append((pool, uq, cnt, ss))
+    for r in range(W):                       # every source: the sums its peers asked for
+        ps = presum(r)
+        _lib.check(L.srm2_presum_rows_f32(t_grads[r].data_ptr(), n, D, C.byref(ps), st), 'presum_rows')
+    assert int(err.item()) == 0
+    asked = torch.stack(req_n).cpu().numpy()[:, :W]
+    assert asked.max() <= pcap and all(asked[r, r] == 0 for r in range(W))
+    if pcap > 1000:                          # every row that left its rank is part of a request; far fewer requests than rows
+        taken = sum(int(req[r].view(W, pcap, 12)[o, :asked[r, o], 0].sum()) for r in range(W) for o in range(W))
+        assert taken == sum(int((x % W != r).sum()) for r, x in enumerate(ids))
+        assert asked.sum() < 0.7 * taken
+    else:
+        assert asked.sum() == pcap * W * (W - 1)              # every region full
+    for d in range(W):                       # every owner: run sums + Adam
+        pool, uq, cnt, ss = owners[d]
+        p_out = (C.c_void_p * W)(*[outbox[d][s_ * pcap * D:].data_ptr() for s_ in range(W)])     # region s of the owner's own buffer
+        _lib.check(L.srm2_reduce_adam_apply_pull_f32(pool.data_ptr(), uq.data_ptr(), arr(t_grads), p_out, err.data_ptr(), W, cap,
+                                                     n_recv[d:].data_ptr(), D, -1, cnt.data_ptr(), uq.numel(), sc, ss.data_ptr(), ss.numel(), st),
+                   'apply_pull')
+        assert np.array_equal(pool.cpu().numpy().view(np.uint32), state[d::W].view(np.uint32)), d
+    # a set status word: the update kernels leave the shard as it is
+    pool, uq, cnt, ss = owners[0]
+    before = pool.clone()
+    err.fill_(2)
+    p_out = (C.c_void_p * W)(*[outbox[0][s_ * pcap * D:].data_ptr() for s_ in range(W)])
+    _lib.check(L.srm2_reduce_adam_apply_pull_f32(pool.data_ptr(), uq.data_ptr(), arr(t_grads), p_out, err.data_ptr(), W, cap, n_recv.data_ptr(), D, -1,
+                                                 cnt.data_ptr(), uq.numel(), sc, ss.data_ptr(), ss.numel(), st), 'apply_pull')
+    assert torch.equal(pool.view(torch.int32), before.view(torch.int32))
+
+
 def test_engine_world1_pipelined_equals_step_by_step(oracle):
     """run_steps at world size 1 (index half of step s+1 on a side stream while the sum half of step s runs) against
     step() on a second engine and against the oracle."""
