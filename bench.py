@@ -340,6 +340,13 @@ def run_ours(a, world, rank, local_rank):
         extra_stage = float(np.mean([e0.elapsed_time(e1) for e0, e1 in ev_pairs[:m]]))
         win = [(x[0], x[1], x[2], extra_stage, x[4]) for x in win]
 
+    presum_on = bool(pull and eng._peer.get('presum') and getattr(eng, 'presum', True))
+    pushed_rows = 0
+    if presum_on:      # rows this rank stored into its peers' buffers of sums in the last step (one per request)
+        P = eng._peer
+        last_set = (K - 1) % P['slots']
+        cnts = P['req_n'][last_set * 16:last_set * 16 + world].tolist()
+        pushed_rows = int(sum(c for r_, c in enumerate(cnts) if r_ != rank))
     # ---- NVLink read ceiling of the pull path, measured here: every rank streams 256 MiB out of its neighbour's
     # gradient slots with the same 16-byte asynchronous copies the fused kernel uses, all ranks at once ----
     peer_read_gbs = None
@@ -441,7 +448,7 @@ def run_ours(a, world, rank, local_rank):
                        'stage_us': [min(stage_w) * 1e3, stage_ms * 1e3, max(stage_w) * 1e3]},
            'parity': parity,
            'roofline': {'bound': 'hbm', 'achieved': achieved, 'peak': peak, 'unit': 'GB/s', 'frac': achieved / peak, 'traffic': traffic,
-                        'kernel': 'srm2_segment_runsum_wide_kernel (fused run sums + Adam; multi-run rows finished in place; N > 1: gradient rows read from their source rank over NVLink)',
+                        'kernel': 'srm2_segment_runsum_wide_kernel (fused run sums + Adam; multi-run rows finished in place; N > 1: rows of other ranks arrive as sums prepared at their source)',
                         'peak_source': f'{peak_kind} (MEASURED_PEAKS.json hbm_gbs)' if peak_kind == 'measured' else 'fallback 6650 GB/s',
                         'stage_us': stage_ms * 1e3, 'algorithmic_bytes_per_launch': alg_bytes},
            'e2e': {'value': e_rows_all / (e_ms * 1e-3), 'unit': 'rows/s', 'h2d_bytes_per_step': h2d * world,
@@ -452,7 +459,7 @@ def run_ours(a, world, rank, local_rank):
     out['config']['pipeline'] = ('none: one call after another on one stream' if not pipelined else
                                  'ids known ahead: dedup, sort and run descriptors of later steps run on side streams while the run-sum + Adam '
                                  'kernel of step s streams the gradient rows')
-    if world > 1 and pull:
+    if world > 1 and pull and not presum_on:
         # the gradient rows of (world-1)/world of the lookups are read from peer memory by the same kernel
         nv_bytes = lookups_stage * (world - 1) / world * D * 4
         nv = nv_bytes / (stage_ms * 1e-3) / 1e9
@@ -460,8 +467,19 @@ def run_ours(a, world, rank, local_rank):
                                      'frac': nv / peer_read_gbs if peer_read_gbs else None,
                                      'peak_source': 'measured in this run: 256 MiB read from the next rank\'s gradient slots with 16-byte asynchronous '
                                                     'copies on every SM, all ranks at once, slowest rank (srm2_read_probe)'}
+    elif world > 1 and pull:
+        # sums prepared at the source: what crosses NVLink is one row per request, stored into the owner's memory by the
+        # prepared-sums stage (a kernel of its own beside the run-sum kernel of the step before); the timed kernel reads local memory
+        left = n * (world - 1) / world
+        out['roofline']['nvlink'] = {'rows_per_step_this_rank': pushed_rows, 'bytes_per_step_this_rank': pushed_rows * D * 4,
+                                     'lookups_leaving_this_rank_per_step': left, 'rows_per_lookup_leaving': pushed_rows / left if left else None,
+                                     'read_ceiling_GBs': peer_read_gbs,
+                                     'note': 'the leading lookups of a run that come from one rank are added up there (same order, from +0) and cross '
+                                             'as one row; the run-sum + Adam kernel of the roofline object reads local memory only'}
     if world > 1:
-        out['config']['exchange'] = ('pull: lookup names by peer stores, gradient rows read from their source rank by the fused reduce+Adam kernel (NVLink)'
+        out['config']['exchange'] = ('pull with sums prepared at the source: lookup names by peer stores; the leading lookups of a run that come from one '
+                                     'rank are added up there and stored into the owner\'s memory as one row (NVLink stores)' if presum_on else
+                                     'pull: lookup names by peer stores, gradient rows read from their source rank by the fused reduce+Adam kernel (NVLink)'
                                      if pull else 'fused routing kernel: peer stores over NVLink' if p2p else 'NCCL all-to-all')
     return out
 
