@@ -13,9 +13,9 @@ constexpr int kSMs = 148;
 // Grid of an index kernel (dedup, sort bookkeeping, segment boundaries, plans, requests): these kernels run beside the
 // bandwidth-bound kernel of an earlier step, whose CTAs hold every register of every SM, so each of their CTAs waits for
 // one of those to retire and then displaces the next.  A grid of a thousand small CTAs sweeps the whole machine for a
-// wave; two CTAs per SM with a grid-stride loop do the same work from a few slots.
+// wave; at most four CTAs per SM with a grid-stride loop do the same work from a few slots.
 inline unsigned index_grid(int64_t blocks) {
-  const int64_t cap = 2 * kSMs;
+  const int64_t cap = 4 * kSMs;
   return (unsigned)(blocks < 1 ? 1 : (blocks < cap ? blocks : cap));
 }
 
