@@ -340,6 +340,18 @@ def run_ours(a, world, rank, local_rank):
         extra_stage = float(np.mean([e0.elapsed_time(e1) for e0, e1 in ev_pairs[:m]]))
         win = [(x[0], x[1], x[2], extra_stage, x[4]) for x in win]
 
+    # ---- N = 1: the same kernel with the GPU to itself (one call after the other on one stream), outside the timed region:
+    # what the kernel reaches alone, beside what it reaches while it shares the GPU with the index stages of later steps ----
+    stage_alone_ms = None
+    if world == 1 and pipelined:
+        m = min(K, 10)
+        for k, (i_, g_) in enumerate(batches(a.warmup, m)):
+            L.srm2_stage_events(ev_pairs[k][0].cuda_event, ev_pairs[k][1].cuda_event)
+            eng.step(i_, g_, step_no + k)
+        L.srm2_stage_events(None, None)
+        barrier()
+        step_no += m
+        stage_alone_ms = float(np.mean([e0.elapsed_time(e1) for e0, e1 in ev_pairs[:m]]))
     presum_on = bool(pull and eng._peer.get('presum') and getattr(eng, 'presum', True))
     pushed_rows = 0
     if presum_on:      # rows this rank stored into its peers' buffers of sums in the last step (one per request)
@@ -450,7 +462,13 @@ def run_ours(a, world, rank, local_rank):
            'roofline': {'bound': 'hbm', 'achieved': achieved, 'peak': peak, 'unit': 'GB/s', 'frac': achieved / peak, 'traffic': traffic,
                         'kernel': 'srm2_segment_runsum_wide_kernel (fused run sums + Adam; multi-run rows finished in place; N > 1: rows of other ranks arrive as sums prepared at their source)',
                         'peak_source': f'{peak_kind} (MEASURED_PEAKS.json hbm_gbs)' if peak_kind == 'measured' else 'fallback 6650 GB/s',
-                        'stage_us': stage_ms * 1e3, 'algorithmic_bytes_per_launch': alg_bytes},
+                        'stage_us': stage_ms * 1e3, 'algorithmic_bytes_per_launch': alg_bytes,
+                        'alone': None if stage_alone_ms is None else
+                        {'stage_us': stage_alone_ms * 1e3, 'achieved': alg_bytes / (stage_alone_ms * 1e-3) / 1e9,
+                         'frac': alg_bytes / (stage_alone_ms * 1e-3) / 1e9 / peak,
+                         'note': 'the same kernel on the same inputs with the GPU to itself (steps issued one call after the other, '
+                                 'outside the timed region); frac above is measured inside the timed region, where the index '
+                                 'stages of later steps run beside it'}},
            'e2e': {'value': e_rows_all / (e_ms * 1e-3), 'unit': 'rows/s', 'h2d_bytes_per_step': h2d * world,
                    'd2h_bytes_per_step': 16 * world, 'steps': e2e_steps, 'pcie_h2d_GBs_per_gpu': h2d * e2e_steps / (e_ms * 1e-3) / 1e9,
                    'overlap': 'the H2D of step k+1 runs on a copy stream while step k computes; the count of step k is read one step late'},

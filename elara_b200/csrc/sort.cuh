@@ -38,28 +38,25 @@ srm2_sort_hist_kernel(const int64_t* __restrict__ key64, const uint32_t* __restr
   extern __shared__ uint32_t sh[];
   const int64_t n = eff_count(n_host, n_dev);
   const int bins = 1 << bits;
-  for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {     // a CTA takes every gridDim.x-th tile
-    for (int b = threadIdx.x; b < bins; b += kSortThreads) sh[b] = 0;
-    __syncthreads();
-    const int64_t base = (int64_t)tile * kSortTile;
+  for (int b = threadIdx.x; b < bins; b += kSortThreads) sh[b] = 0;
+  __syncthreads();
+  const int64_t base = (int64_t)blockIdx.x * kSortTile;
 #pragma unroll
-    for (int r = 0; r < kSortRounds; ++r) {
-      const int64_t i = base + r * kSortThreads + threadIdx.x;
-      if (i < n) {
-        const uint32_t k = key64 ? make_key(key64[i], cap, mod) : key32[i];
-        atomicAdd(&sh[(k >> shift) & (bins - 1)], 1u);
-      }
+  for (int r = 0; r < kSortRounds; ++r) {
+    const int64_t i = base + r * kSortThreads + threadIdx.x;
+    if (i < n) {
+      const uint32_t k = key64 ? make_key(key64[i], cap, mod) : key32[i];
+      atomicAdd(&sh[(k >> shift) & (bins - 1)], 1u);
     }
-    __syncthreads();
-    for (int b = threadIdx.x; b < bins; b += kSortThreads) {
-      const uint32_t c = sh[b];
-      if (dtot) {
-        hist[(int64_t)tile * bins + b] = c;
-        if (c) { atomicAdd(dtot + b, c); atomicAdd(dtot + (int64_t)(1 + tile / kSuperTile) * bins + b, c); }
-      }
-      else hist[(int64_t)b * tiles + tile] = c;
+  }
+  __syncthreads();
+  for (int b = threadIdx.x; b < bins; b += kSortThreads) {
+    const uint32_t c = sh[b];
+    if (dtot) {
+      hist[(int64_t)blockIdx.x * bins + b] = c;
+      if (c) { atomicAdd(dtot + b, c); atomicAdd(dtot + (int64_t)(1 + blockIdx.x / kSuperTile) * bins + b, c); }
     }
-    __syncthreads();
+    else hist[(int64_t)b * tiles + blockIdx.x] = c;
   }
 }
 
@@ -80,89 +77,86 @@ srm2_sort_scatter_kernel(const int64_t* __restrict__ key64, const uint32_t* __re
   const int bins = 1 << bits;
   uint32_t* goff = sh + kSortWarps * bins;         // global offset of (digit, this tile)
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {     // a CTA takes every gridDim.x-th tile
-    for (int b = threadIdx.x; b < bins * kSortWarps; b += kSortThreads) sh[b] = 0;
-    // ---- this warp's keys and positions, all loads issued before anything depends on them ----
-    const int64_t base_i = (int64_t)tile * kSortTile + (int64_t)warp * (32 * kSortRounds);
-    uint32_t key[kSortRounds], val[kSortRounds], rnk[kSortRounds];
+  for (int b = threadIdx.x; b < bins * kSortWarps; b += kSortThreads) sh[b] = 0;
+  // ---- this warp's keys and positions, all loads issued before anything depends on them ----
+  const int64_t base_i = (int64_t)blockIdx.x * kSortTile + (int64_t)warp * (32 * kSortRounds);
+  uint32_t key[kSortRounds], val[kSortRounds], rnk[kSortRounds];
 #pragma unroll
-    for (int r = 0; r < kSortRounds; ++r) {
-      const int64_t i = base_i + r * 32 + lane;
-      key[r] = 0; val[r] = (uint32_t)i;
-      if (i < n) {
-        key[r] = key64 ? make_key(key64[i], cap, mod) : key32[i];
-        if (val32) val[r] = val32[i];
-      }
+  for (int r = 0; r < kSortRounds; ++r) {
+    const int64_t i = base_i + r * 32 + lane;
+    key[r] = 0; val[r] = (uint32_t)i;
+    if (i < n) {
+      key[r] = key64 ? make_key(key64[i], cap, mod) : key32[i];
+      if (val32) val[r] = val32[i];
     }
-    // ---- global offsets of this tile's digits ----
-    if (dtot == nullptr) {
-      for (int b = threadIdx.x; b < bins; b += kSortThreads) goff[b] = hist[(int64_t)b * tiles + tile];
-    } else {
-      // thread t owns the consecutive digits [t*per, (t+1)*per): sum of the earlier tiles (coalesced over threads when
-      // per == 1, i.e. up to 256 digits; still line-friendly above), then a block scan of the digit totals
-      const int per = (bins + kSortThreads - 1) / kSortThreads;
-      uint32_t tsum = 0;
-      for (int q = 0; q < per; ++q) {
-        const int b = threadIdx.x * per + q;
-        if (b >= bins) break;
-        const uint32_t* col = hist + b;
-        uint32_t before = 0;
-        const int my_group = (int)tile / kSuperTile;
-        for (int gq = 0; gq < my_group; ++gq) before += __ldg(dtot + (int64_t)(1 + gq) * bins + b);
-        int t = my_group * kSuperTile;
-        for (; t + 8 <= (int)tile; t += 8) {
-          uint32_t v[8];
+  }
+  // ---- global offsets of this tile's digits ----
+  if (dtot == nullptr) {
+    for (int b = threadIdx.x; b < bins; b += kSortThreads) goff[b] = hist[(int64_t)b * tiles + blockIdx.x];
+  } else {
+    // thread t owns the consecutive digits [t*per, (t+1)*per): sum of the earlier tiles (coalesced over threads when
+    // per == 1, i.e. up to 256 digits; still line-friendly above), then a block scan of the digit totals
+    const int per = (bins + kSortThreads - 1) / kSortThreads;
+    uint32_t tsum = 0;
+    for (int q = 0; q < per; ++q) {
+      const int b = threadIdx.x * per + q;
+      if (b >= bins) break;
+      const uint32_t* col = hist + b;
+      uint32_t before = 0;
+      const int my_group = (int)blockIdx.x / kSuperTile;
+      for (int gq = 0; gq < my_group; ++gq) before += __ldg(dtot + (int64_t)(1 + gq) * bins + b);
+      int t = my_group * kSuperTile;
+      for (; t + 8 <= (int)blockIdx.x; t += 8) {
+        uint32_t v[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) v[e] = __ldg(col + (int64_t)(t + e) * bins);
+        for (int e = 0; e < 8; ++e) v[e] = __ldg(col + (int64_t)(t + e) * bins);
 #pragma unroll
-          for (int e = 0; e < 8; ++e) before += v[e];
-        }
-        for (; t < (int)tile; ++t) before += __ldg(col + (int64_t)t * bins);
-        goff[b] = before;
-        tsum += __ldg(dtot + b);
+        for (int e = 0; e < 8; ++e) before += v[e];
       }
-      uint32_t dbase = block_exclusive_scan<kSortThreads>(tsum, ws, nullptr);
-      for (int q = 0; q < per; ++q) {
-        const int b = threadIdx.x * per + q;
-        if (b >= bins) break;
-        goff[b] += dbase; dbase += __ldg(dtot + b);
-      }
+      for (; t < (int)blockIdx.x; ++t) before += __ldg(col + (int64_t)t * bins);
+      goff[b] = before;
+      tsum += __ldg(dtot + b);
     }
-    __syncthreads();
-    uint32_t* cnt = sh + warp * bins;
+    uint32_t dbase = block_exclusive_scan<kSortThreads>(tsum, ws, nullptr);
+    for (int q = 0; q < per; ++q) {
+      const int b = threadIdx.x * per + q;
+      if (b >= bins) break;
+      goff[b] += dbase; dbase += __ldg(dtot + b);
+    }
+  }
+  __syncthreads();
+  uint32_t* cnt = sh + warp * bins;
 #pragma unroll
-    for (int r = 0; r < kSortRounds; ++r) {
-      const int64_t i = base_i + r * 32 + lane;
-      const bool ok = i < n;
-      const unsigned act = __ballot_sync(0xffffffffu, ok);
-      if (ok) {
-        const uint32_t d = (key[r] >> shift) & (bins - 1);
-        const unsigned m = __match_any_sync(act, d);
-        const int leader = __ffs(m) - 1;
-        uint32_t old = 0;
-        if (lane == leader) { old = cnt[d]; cnt[d] = old + __popc(m); }
-        old = __shfl_sync(m, old, leader);
-        rnk[r] = old + __popc(m & ((1u << lane) - 1u));
-      }
+  for (int r = 0; r < kSortRounds; ++r) {
+    const int64_t i = base_i + r * 32 + lane;
+    const bool ok = i < n;
+    const unsigned act = __ballot_sync(0xffffffffu, ok);
+    if (ok) {
+      const uint32_t d = (key[r] >> shift) & (bins - 1);
+      const unsigned m = __match_any_sync(act, d);
+      const int leader = __ffs(m) - 1;
+      uint32_t old = 0;
+      if (lane == leader) { old = cnt[d]; cnt[d] = old + __popc(m); }
+      old = __shfl_sync(m, old, leader);
+      rnk[r] = old + __popc(m & ((1u << lane) - 1u));
     }
-    __syncthreads();
-    // exclusive scan of the warp counts across warps, per digit, on top of the tile's global offset
-    for (int b = threadIdx.x; b < bins; b += kSortThreads) {
-      uint32_t run = goff[b];
+  }
+  __syncthreads();
+  // exclusive scan of the warp counts across warps, per digit, on top of the tile's global offset
+  for (int b = threadIdx.x; b < bins; b += kSortThreads) {
+    uint32_t run = goff[b];
 #pragma unroll
-      for (int w = 0; w < kSortWarps; ++w) { const uint32_t c = sh[w * bins + b]; sh[w * bins + b] = run; run += c; }
-    }
-    __syncthreads();
+    for (int w = 0; w < kSortWarps; ++w) { const uint32_t c = sh[w * bins + b]; sh[w * bins + b] = run; run += c; }
+  }
+  __syncthreads();
 #pragma unroll
-    for (int r = 0; r < kSortRounds; ++r) {
-      const int64_t i = base_i + r * 32 + lane;
-      if (i < n) {
-        const uint32_t d = (key[r] >> shift) & (bins - 1);
-        const uint32_t dst = cnt[d] + rnk[r];
-        out_key[dst] = key[r]; out_val[dst] = val[r];
-      }
+  for (int r = 0; r < kSortRounds; ++r) {
+    const int64_t i = base_i + r * 32 + lane;
+    if (i < n) {
+      const uint32_t d = (key[r] >> shift) & (bins - 1);
+      const uint32_t dst = cnt[d] + rnk[r];
+      out_key[dst] = key[r]; out_val[dst] = val[r];
     }
-    __syncthreads();                                 // the counters are reused by the next tile
   }
 }
 
@@ -191,12 +185,12 @@ static int radix_sort_by_key(const int64_t* src, int64_t n, const int64_t* n_dev
   for (int p = 0; p < passes; ++p) {
     const int shiftp = p * bits;
     dt = separate_scan ? nullptr : sb.dtot + sort_dtot_words_pass(sb.tiles, bits) * p;
-    srm2_sort_hist_kernel<<<index_grid(sb.tiles), kSortThreads, sm_hist, st>>>(p == 0 ? src : nullptr, ki, n, n_dev, shiftp, bits, sb.hist, dt, sb.tiles, cap, mod);
+    srm2_sort_hist_kernel<<<sb.tiles, kSortThreads, sm_hist, st>>>(p == 0 ? src : nullptr, ki, n, n_dev, shiftp, bits, sb.hist, dt, sb.tiles, cap, mod);
     if (separate_scan) {
       srm2_scan_exclusive_u32_kernel<<<1, kScanThreads, 0, st>>>(sb.hist, sb.hist, entries, nullptr, entries, 0, nullptr);
       *launches += 1;
     }
-    srm2_sort_scatter_kernel<<<index_grid(sb.tiles), kSortThreads, sm_scat, st>>>(p == 0 ? src : nullptr, ki, vi, n, n_dev, shiftp, bits, sb.hist, dt, sb.tiles,
+    srm2_sort_scatter_kernel<<<sb.tiles, kSortThreads, sm_scat, st>>>(p == 0 ? src : nullptr, ki, vi, n, n_dev, shiftp, bits, sb.hist, dt, sb.tiles,
                                                                      ko, vo, cap, mod);
     *launches += 2;
     ki = ko; vi = vo;
