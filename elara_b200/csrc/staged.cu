@@ -24,7 +24,7 @@ struct Staged {
   cudaEvent_t ev(int stage, int64_t k) const { return static_cast<cudaEvent_t>(a.events[stage * kRing + (int)(k % kRing)]); }
   bool ok() const { return rc == SRM2_OK; }
   void trace(int64_t k, int stage, int end, cudaStream_t st) {
-    if (a.trace_events) cuda(cudaEventRecord(static_cast<cudaEvent_t>(a.trace_events[k * 10 + stage * 2 + end]), st));
+    if (a.trace_events) cuda(cudaEventRecord(static_cast<cudaEvent_t>(a.trace_events[k * 14 + stage * 2 + end]), st));
   }
   void check(int r) { if (rc == SRM2_OK && r != SRM2_OK) rc = r; }
   void cuda(cudaError_t e) { if (rc == SRM2_OK && note_cuda(e)) rc = SRM2_ERR_CUDA; }
@@ -90,6 +90,7 @@ struct Staged {
     const int64_t cap_u = a.cap_u < a.n ? a.cap_u : a.n;
     check(srm2_reduce_adam_index(a.u[q], src, a.inv[q], a.n, n_dev, a.D, -1, a.counts_out + 2 * k, cap_u, part, a.scr_s[q], (size_t)a.scr_s_bytes, st));
     if (presum && part == SRM2_INDEX_DESCRIPTORS) {
+      trace(k, 5, 0, st);
       // requests for sums prepared at the source: set k mod n_slots of every rank's request buffers (the sums of step
       // k - n_slots, their last reader, ended on every rank before anybody left the first barrier of this step's exchange)
       const int64_t set = k % a.n_slots;
@@ -97,6 +98,7 @@ struct Staged {
       ps.peer_req = a.peer_req + set * a.world; ps.peer_req_n = a.peer_req_n + set * a.world; ps.req_count = a.req_count + set * 32;
       ps.peer_tickets = a.peer_tickets_req; *a.ticket += 1; ps.ticket = (uint64_t)*a.ticket;
       check(srm2_presum_request(a.n, n_dev, a.D, cap_u, a.scr_s[q], (size_t)a.scr_s_bytes, &ps, st));
+      trace(k, 5, 1, st);
     }
     trace(k, part == SRM2_INDEX_SORT ? 2 : 3, 1, st);
     cuda(cudaEventRecord(ev(part == SRM2_INDEX_SORT ? 2 : 3, k), st));
@@ -112,10 +114,12 @@ struct Staged {
     const int64_t set = k % a.n_slots;
     cuda(cudaStreamWaitEvent(pr, ev(3, k), 0));                            // the requests are complete (barrier of the descriptors stage)
     if (k >= 2) cuda(cudaStreamWaitEvent(pr, ev(4, k - 2), 0));
+    trace(k, 6, 0, pr);
     srm2_presum ps = presum_base();
     ps.req = a.req[set]; ps.req_n = a.req_n[set]; ps.peer_out = a.peer_push + (k % 3) * a.world; ps.done = a.presum_done;
     ps.peer_tickets = a.peer_tickets_sum; *a.ticket += 1; ps.ticket = (uint64_t)*a.ticket;
     check(srm2_presum_rows_f32(a.slot[set], a.n_k[k], a.D, &ps, pr));
+    trace(k, 6, 1, pr);
     cuda(cudaEventRecord(ev(6, k), pr));
   }
   // stage 4

@@ -495,7 +495,7 @@ class ShardedSparseAdam:
                 keep.append(vp([e.cuda_event for pair in self._stage_events for e in pair]))
                 A.stage_events = C.cast(keep[-1], C.c_void_p)
             if trace:
-                tev = [torch.cuda.Event(enable_timing=True) for _ in range(K * 10)]
+                tev = [torch.cuda.Event(enable_timing=True) for _ in range(K * 14)]
                 t0ev = torch.cuda.Event(enable_timing=True)
                 for e in tev:
                     e.record(comp)
@@ -534,8 +534,9 @@ class ShardedSparseAdam:
             if trace:      # microseconds since the start: (begin, end) of exchange, dedup, sort, descriptors, sums per step
                 torch.cuda.synchronize(self.dev)
                 first = 0 if pull else 1
-                self.trace_result = [tuple((t0ev.elapsed_time(tev[k * 10 + 2 * q]) * 1e3, t0ev.elapsed_time(tev[k * 10 + 2 * q + 1]) * 1e3)
-                                           for q in range(first, 5)) for k in range(K)]
+                last = 7 if presum else 5          # ... then requests and prepared sums where they exist
+                self.trace_result = [tuple((t0ev.elapsed_time(tev[k * 14 + 2 * q]) * 1e3, t0ev.elapsed_time(tev[k * 14 + 2 * q + 1]) * 1e3)
+                                           for q in range(first, last)) for k in range(K)]
             self.last_local_lookups = nr
             self.last_local_lookups_total += nr * K
             return [counts_out[k] for k in range(K)]

@@ -563,8 +563,9 @@ typedef struct srm2_staged {
   void* const* streams;                          /* (host) [5] cudaStream_t; [7] at world > 1 */
   void* const* events;                           /* (host) [112] cudaEvent_t without timing: 16 per stage */
   void* const* stage_events;                     /* (host) [2K] or NULL: recorded around the sums of each step */
-  void* const* trace_events;                     /* (host) [K * 10] or NULL: cudaEvent_t with timing, (begin, end) of the five
-                                                    stages of every step, step-major (diagnostics) */
+  void* const* trace_events;                     /* (host) [K * 14] or NULL: cudaEvent_t with timing, (begin, end) of exchange,
+                                                    dedup, sort, descriptors (requests included), sums, requests, prepared
+                                                    sums of every step, step-major (diagnostics) */
   /* world > 1 (pull exchange); ignored at world 1 */
   int64_t world, rank, cap, n_recv_bufs, n_slots, timeout_ns;
   void* route_scr; int64_t route_scr_bytes; int64_t* counts; uint32_t* err; int64_t* n_recv;   /* two route scratch sets of
