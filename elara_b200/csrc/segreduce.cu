@@ -181,11 +181,11 @@ __device__ __forceinline__ void stage_lookup(const ReduceArgs& a, float4* slot, 
   else cp_async16(slot, grad_row<PEER>(a, name) + j4 * 4);
 }
 
-constexpr int kRunThreads = 256;
+constexpr int kRunThreads = 128;
 constexpr int kRunStageVecs = kRun + 3;                                  // gradient rows + w, m, v
 constexpr int kWarpChainMax = 96;         // rows with more partial vectors are added up by a whole CTA (below)
 constexpr int kLongCap = 16;              // such rows one CTA can take over; further ones are finished by their lane group
-constexpr int kRunSmemBytes = kRunStageVecs * kRunThreads * 16 + 128;   // 53,248 B of staging slots + the long-row list
+constexpr int kRunSmemBytes = kRunStageVecs * kRunThreads * 16 + 128;   // 26,624 B of staging slots + the long-row list
 
 // Sum of `n` consecutive partial vectors at p (this lane's 16 bytes of each), in order from +0: twelve slots as three
 // groups of four, the oldest group is added while the two younger ones are in flight.
@@ -274,7 +274,7 @@ __device__ __forceinline__ void finish_long_rows(const ReduceArgs& a, float4* st
 //  - a one-run item issues all its copies at once; longer items stream run after run through two half-run slot sets;
 //  - descriptors are fetched two items ahead and the first run's names one item ahead, so neither is waited for.
 template <bool FUSED, bool PEER>
-__global__ void __launch_bounds__(kRunThreads, 4)
+__global__ void __launch_bounds__(kRunThreads, 8)
 srm2_segment_runsum_wide_kernel(ReduceArgs a) {
   extern __shared__ __align__(128) float4 stage[];                 // [kRunStageVecs][kRunThreads]
   uint32_t* s_long = reinterpret_cast<uint32_t*>(stage + kRunStageVecs * kRunThreads);   // behind the staging slots, so
@@ -771,9 +771,10 @@ static int segment_pipeline(bool fused, int order, const float* grad, const int6
   const int64_t run_items_max = (n / kChunk + n / (kChunk + 1) + 2 + cap) * lpr;      // long chunks + one entry per unique row
   // Many short-lived CTAs: a CTA that has to add up a row of many partial vectors does so after its last item, so the
   // sooner CTAs end the sooner those chains start; in the split form SM room also frees up every few microseconds for the
-  // small kernels of the other streams (the next steps' index work).
-  const int64_t cta_cap = (int64_t)kSMs * 32;
-  const int grid_runs = (int)((run_items_max + 255) / 256 < cta_cap ? (run_items_max + 255) / 256 : cta_cap);
+  // small kernels of the other streams (the next steps' index work).  CTAs of 128 threads, eight to an SM, 64 per SM in all:
+  // the eight hold every register of the SM between them, so the finer the grain the sooner another kernel's CTA gets in.
+  const int64_t cta_cap = (int64_t)kSMs * 64;
+  const int grid_runs = (int)((run_items_max + kRunThreads - 1) / kRunThreads < cta_cap ? (run_items_max + kRunThreads - 1) / kRunThreads : cta_cap);
   const int rows_fit = (int)(kFinalSmemBytes / (D * 4));                 // partial vectors that fit the CTA's staging buffer
   const int short_rows = rows_fit / kFinalWarps, chunk_rows = rows_fit;
   const size_t sm_final = kFinalSmemBytes;
