@@ -68,3 +68,60 @@ def test_sharded_equals_single_process(tmp_path, oracle, world):
         assert np.array_equal(shard.view(np.uint32), st[r::world].view(np.uint32))
         touched += int((shard[:, 1] != 0).any(axis=1).sum())
     assert touched > 500
+
+
+@pytest.mark.parametrize('world', [2, 3, 8])
+def test_sums_prepared_at_the_source_are_the_owner_s_sums(oracle, world):
+    """The rule the multi-GPU exchange relies on, checked on the CPU with the oracle's arithmetic: in the order of the
+    segment-reduce (lookups of a row in ascending global position, runs of ten summed from +0, run sums added from +0) the
+    leading lookups of a run that come from one rank may be replaced by their own left-to-right sum from +0 — the row sums
+    keep their bits.  Replacing a group further back in a run would not (shown on the same data)."""
+    rng = np.random.default_rng(world)
+    R, D, n = 400, 8, 6000
+    p = np.arange(1, R + 1, dtype=np.float64) ** -1.1
+    ids = [rng.choice(R, size=n, p=p / p.sum()).astype(np.int64) for _ in range(world)]           # rank r holds lookups r*n .. (r+1)*n-1
+    grads = [(rng.standard_normal((n, D)) * 10.0 ** rng.integers(-4, 5, size=(n, 1))).astype(np.float32) for _ in range(world)]
+    all_ids, all_grads = np.concatenate(ids), np.concatenate(grads)
+    u, inv = oracle.unique_inverse(all_ids)
+    want = oracle.segment_reduce(all_grads, inv, len(u), chunk=oracle.SEGMENT_CHUNK)
+    src = np.repeat(np.arange(world), n)
+
+    def sum_from_zero(rows):
+        acc = np.zeros(D, np.float32)
+        for r in rows:
+            acc = (acc + all_grads[r]).astype(np.float32)
+        return acc
+
+    def reduce_with_groups(leading_only):
+        out = np.zeros((len(u), D), np.float32)
+        order = np.argsort(inv, kind='stable')
+        bounds = np.searchsorted(inv[order], np.arange(len(u) + 1))
+        replaced = 0
+        for j in range(len(u)):
+            pos = order[bounds[j]:bounds[j + 1]]
+            total = np.zeros(D, np.float32)
+            for s0 in range(0, len(pos), 10):
+                run = pos[s0:s0 + 10]
+                g = 0 if leading_only else next((q for q in range(1, len(run)) if src[run[q]] != src[run[q - 1]]), 0)
+                m = g + 1
+                while m < len(run) and src[run[m]] == src[run[g]]:
+                    m += 1
+                acc = np.zeros(D, np.float32)
+                for q in range(g):
+                    acc = (acc + all_grads[run[q]]).astype(np.float32)
+                if m - g >= 2:
+                    acc = (acc + sum_from_zero(run[g:m])).astype(np.float32)          # the group arrives as one row
+                    replaced += m - g
+                else:
+                    m = g
+                for q in range(m, len(run)):
+                    acc = (acc + all_grads[run[q]]).astype(np.float32)
+                total = (total + acc).astype(np.float32)
+            out[j] = total
+        return out, replaced
+
+    got, replaced = reduce_with_groups(leading_only=True)
+    assert replaced > 0.3 * len(all_ids)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    other, replaced2 = reduce_with_groups(leading_only=False)
+    assert replaced2 > 0 and not np.array_equal(other.view(np.uint32), want.view(np.uint32))
