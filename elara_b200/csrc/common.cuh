@@ -10,12 +10,14 @@ namespace srm2 {
 // The B200 has 148 SMs; grids of the streaming kernels are sized in multiples of this.
 constexpr int kSMs = 148;
 
-// Grid of an index kernel (dedup, sort bookkeeping, segment boundaries, plans, requests): these kernels run beside the
-// bandwidth-bound kernel of an earlier step, whose CTAs hold every register of every SM, so each of their CTAs waits for
-// one of those to retire and then displaces the next.  A grid of a thousand small CTAs sweeps the whole machine for a
-// wave; at most four CTAs per SM with a grid-stride loop do the same work from a few slots.
+// Grid of an index kernel (dedup, sort bookkeeping, segment boundaries, plans, requests, the exchange's kernels).  These
+// kernels run beside the bandwidth-bound kernel of an earlier step, whose CTAs hold every register of every SM between
+// them: a CTA of another kernel gets in when one of those retires, and for as long as it lives it takes that one's place.
+// SM time is what the pipelined step runs out of, and an index kernel is bound by the latency of a few dependent loads,
+// not by the number of its threads — so it gets a grid-stride loop on two CTAs per SM at most (the kernels that talk to
+// other GPUs: one), which costs it little time and spends a fraction of the SM time of a grid sized by its input.
 inline unsigned index_grid(int64_t blocks) {
-  const int64_t cap = 4 * kSMs;
+  const int64_t cap = 2 * kSMs;
   return (unsigned)(blocks < 1 ? 1 : (blocks < cap ? blocks : cap));
 }
 

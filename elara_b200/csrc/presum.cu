@@ -107,7 +107,10 @@ extern "C" int srm2_presum_rows_f32(const float* grad, int64_t n, int64_t D, con
   // the number of requests is on the device; at most n / 2 of them (each names two or more of this rank's n rows)
   const int64_t items_max = (n / 2 + 1) * lpr;
   int64_t grid = (items_max + kPresumThreads - 1) / kPresumThreads;
-  if (grid > (int64_t)kSMs * 6) grid = (int64_t)kSMs * 6;      // two waves of the three CTAs an SM holds
+  // One CTA per SM: the kernel runs beside the run-sum kernel of the step before, whose CTAs hold every register of the SMs
+  // between them; every CTA here takes the place of two and a half of those for as long as it lives, and what bounds this
+  // kernel is the latency of its dependent loads, not the number of its threads.
+  if (grid > (int64_t)kSMs) grid = (int64_t)kSMs;
   if (grid < 1) grid = 1;
   srm2_presum_rows_kernel<<<(unsigned)grid, kPresumThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       grad, n, lpr, shift, (int)D, (int)W, (int)ps->rank, (uint32_t)ps->cap, static_cast<const uint4*>(ps->req), ps->req_n, po, ps->err, pt,

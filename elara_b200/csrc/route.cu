@@ -523,7 +523,7 @@ extern "C" int srm2_route_dispatch_ids(const int64_t* ids, int64_t n, int64_t wo
   }
   SortBuffers sb;
   route_layout(n, world, static_cast<char*>(scratch), &sb);     // keyA / valA hold the owners and the permutation of srm2_route_plan
-  int grid = (int)((n + 255) / 256 < (int64_t)kSMs * 4 ? (n + 255) / 256 : (int64_t)kSMs * 4);
+  int grid = (int)((n + 255) / 256 < (int64_t)kSMs ? (n + 255) / 256 : (int64_t)kSMs);      // one CTA per SM: see index_grid
   if (grid < 1) grid = 1;
   uint32_t* done = sb.dtot + sort_dtot_words(sb.tiles, route_bits(world), 1);      // zeroed by the plan
   srm2_route_dispatch_ids_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(ids, sb.valA, sb.keyA, n, (int)world, (int)rank, cmat, pl, ps, cap,

@@ -987,7 +987,8 @@ extern "C" int srm2_presum_request(int64_t n, const int64_t* n_dev, int64_t D, i
   seg_layout(n, max_unique, D, static_cast<char*>(scratch), &s);
   const uint32_t* skey = (s.passes & 1) ? s.keyA : s.keyB;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  srm2_presum_request_kernel<<<index_grid((n + 255) / 256), 256, 0, st>>>(skey, s.seg_start, s.seg_end, s.names, s.row_desc, n, n_dev, max_unique,
+  const int64_t req_blocks = (n + 255) / 256 < (int64_t)kSMs ? (n + 255) / 256 : (int64_t)kSMs;      // one CTA per SM: see index_grid
+  srm2_presum_request_kernel<<<(unsigned)(req_blocks < 1 ? 1 : req_blocks), 256, 0, st>>>(skey, s.seg_start, s.seg_end, s.names, s.row_desc, n, n_dev, max_unique,
                                                                         (int)ps->rank, (int)W, (uint32_t)ps->cap, pr, ps->req_count, pn, pt,
                                                                         (unsigned long long)ps->ticket, ps->err, (long long)ps->timeout_ns);
   return launch_status(1);
