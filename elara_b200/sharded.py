@@ -259,7 +259,7 @@ class ShardedSparseAdam:
                 gbuf = None
             sig = symm.empty(48, dtype=torch.int64, device=self.dev)       # barrier tickets: exchange | requests | prepared sums
             ts = [rlid, payload, cmat, sig] + ([gbuf] if pull else [])
-            presum = bool(presum and pull and n_max < (1 << 23))
+            presum = bool(presum and pull and cap < (1 << 23))          # names keep one bit for "a prepared sum"
             if presum:
                 # per (source, owner) pair: a source's n_max lookups make at most n_max / 2 requests in all; the owners share
                 # them evenly on average (row id mod W), twice that is kept per owner; a full region costs bytes, not bits
