@@ -1,4 +1,5 @@
-// A window of optimizer steps enqueued as a pipeline of stages on five streams (see srm2_staged in the header).
+// A window of optimizer steps enqueued as a pipeline of stages on five streams, seven with more than one rank (see
+// srm2_staged in the header).
 // Pure host code: it makes the library's own calls and orders them with CUDA events.  Written in C++ because a step is
 // about twenty launches and an interpreted host loop needs longer to issue them than the GPU needs to run them.
 #include "common.cuh"

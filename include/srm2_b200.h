@@ -532,7 +532,7 @@ int srm2_reduce_adam_apply_pull_f32(float* pool, const int64_t* slots, const flo
                                     srm2_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------------
- * A window of K steps as a pipeline of stages on five streams, enqueued by one call (no counterpart in the reference;
+ * A window of K steps as a pipeline of stages on five streams (seven at world > 1), enqueued by one call (no counterpart in the reference;
  * the reference's driver is a Python loop).  It issues exactly the calls documented above, in this order per
  * iteration k — sums(k), descriptors(k+1), sort(k+2), dedup(k+3), exchange(k+4), plan(k+5) — with CUDA events between:
  *   plan (world > 1)      srm2_route_plan                                                  on streams[6]
@@ -548,7 +548,7 @@ int srm2_reduce_adam_apply_pull_f32(float* pool, const int64_t* slots, const flo
  * A host loop that makes these calls itself gives the same result; this entry point exists because at ~20 launches per
  * step the host, not the GPU, bounds such a loop.  All members are 8 bytes wide.  Pointers marked (host) are host
  * arrays; everything else is device memory.  Nothing is allocated or synchronised; the call returns when the window is
- * enqueued, streams[0..3] have been joined into streams[4].
+ * enqueued, every other stream has been joined into streams[4].
  */
 typedef struct srm2_staged {
   int64_t K, first_step, n, D, n_rows, cap_u;   /* n: lookups per step (world 1), capacity of a receive buffer (world > 1) */
