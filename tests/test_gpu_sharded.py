@@ -103,9 +103,9 @@ def test_pull_exchange_emulated_on_one_gpu(oracle, n, D, W):
         assert np.array_equal(pool.cpu().numpy().view(np.uint32), state[d::W].view(np.uint32)), d
 
 
-@pytest.mark.parametrize('n,D,W,pcap', [(3000, 16, 2, 3001), (40000, 128, 4, 20000), (90000, 64, 3, 40), (212992, 128, 8, 53248),
-                                        (50000, 24, 2, 30001)])
-def test_pull_exchange_with_sums_prepared_at_the_source(oracle, n, D, W, pcap):
+@pytest.mark.parametrize('n,D,W,pcap,one_owner', [(3000, 16, 2, 3001, False), (40000, 128, 4, 20000, False), (90000, 64, 3, 40, False),
+                                                  (212992, 128, 8, 53248, False), (50000, 24, 2, 30001, False), (6000, 32, 3, 6001, True)])
+def test_pull_exchange_with_sums_prepared_at_the_source(oracle, n, D, W, pcap, one_owner):
     """The pull exchange in which the leading lookups of a run that come from one rank are added up by that rank and read
     by the owner as one row (srm2_presum_request / srm2_presum_rows_f32 / srm2_reduce_adam_apply_pull_f32), all W ranks'
     buffers on one device, no barriers (the calls are made in the order the barriers would enforce).  The shards must
@@ -122,6 +122,8 @@ def test_pull_exchange_with_sums_prepared_at_the_source(oracle, n, D, W, pcap):
     p = np.arange(1, R + 1, dtype=np.float64) ** -1.1
     perm0 = rng.permutation(R)
     ids = [perm0[rng.choice(R, size=n, p=p / p.sum())].astype(np.int64) for _ in range(W)]
+    if one_owner:                            # every row belongs to rank 1: the other owners receive nothing and ask for nothing
+        ids = [x // W * W + 1 for x in ids]
     grads = [(rng.standard_normal((n, D)) * 10.0 ** rng.integers(-3, 4, size=(n, 1))).astype(np.float32) for _ in range(W)]
     for g in grads:
         g[rng.integers(0, n, 50)] = -0.0                         # signed zeros must come out as the one-by-one sum leaves them
