@@ -60,6 +60,29 @@ def test_division_random_pairs_over_the_guarded_exponents(dev):
     assert bad == 0, f'first mismatch a={first[0]:08x} b={first[1]:08x}'
 
 
+def test_division_brute_force_sweep(dev):
+    """Optional and long: every dividend significand against every divisor significand that ends in SRM2_DIV_SWEEP_SHIFT
+    zero bits (shift 3: an eighth of all divisors, 8.8e12 quotients, a few minutes on a B200; shift 0 would be all of
+    them).  Not needed for the argument — the midpoint enumeration above covers every divisor — but it is the same claim
+    checked the blunt way.  Skipped unless the variable is set."""
+    import os, time
+    shift = os.environ.get('SRM2_DIV_SWEEP_SHIFT')
+    if shift is None:
+        pytest.skip('set SRM2_DIV_SWEEP_SHIFT (0..8) to run the brute-force sweep')
+    shift = int(shift)
+    assert 0 <= shift <= 8
+    total = tested_all = 0
+    t0 = time.time()
+    step = 1 << 14                           # divisors per call: each call is a second or two of GPU time
+    for lo in range(0, 1 << (23 - shift), step):
+        tested, bad, first, _ = run(dev, DIV_ALL, lo, lo + step, 1, shift)
+        torch.cuda.synchronize(dev)
+        assert bad == 0, f'first mismatch a={first[0]:08x} b={first[1]:08x}'
+        tested_all += tested
+    print(f'division sweep: shift {shift}, {tested_all} quotients, 0 mismatches, {time.time() - t0:.0f} s')
+    assert tested_all == (1 << (23 - shift)) * (1 << 23)
+
+
 @pytest.mark.parametrize('mode', [0, 1])
 def test_packed_adam_step_equals_ieee_step(dev, mode):
     tested, bad, first, _ = run(dev, ADAM, 5 + mode, 5 + mode + (1 << 28), 0, mode)
