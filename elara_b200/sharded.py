@@ -424,7 +424,8 @@ class ShardedSparseAdam:
         pull = W > 1
         L = _lib.lib()
         K = len(batches)
-        n_max = max(i.numel() for i, _ in batches)
+        n_k = [i.numel() for i, _ in batches]
+        n_max = max(n_k)
         comp = torch.cuda.current_stream(self.dev)
         st = getattr(self, '_stage_streams', None)
         if st is None:
@@ -459,8 +460,7 @@ class ShardedSparseAdam:
         NB = 4                                                        # buffer sets = stages that hold one (dedup, sort, descriptors, sums)
         while len(f['u2']) < NB:
             f['u2'].append(torch.empty_like(f['u'])); f['inv2'].append(torch.empty_like(f['inv'])); f['scr_s2'].append(torch.empty_like(f['scr_s']))
-        counts_out = torch.zeros(K, 2, dtype=torch.int64, device=self.dev)
-        cnt_ptr = [counts_out[k].data_ptr() for k in range(K)]
+        counts_out = torch.empty(K, 2, dtype=torch.int64, device=self.dev)      # both words of every step are written by its dedup
         u_ptr = [t.data_ptr() for t in f['u2']]
         inv_ptr = [t.data_ptr() for t in f['inv2']]
         ss_ptr = [t.data_ptr() for t in f['scr_s2']]
@@ -486,13 +486,16 @@ class ShardedSparseAdam:
             A.lr, A.b1, A.b2, A.eps = self.hyper
             A.pool, A.counts_out = pool_ptr, counts_out.data_ptr()
             keep = [vp([i.data_ptr() for i, _ in batches]), vp([g.data_ptr() for _, g in batches]),
-                    (C.c_int64 * K)(*[i.numel() for i, _ in batches]), vp([xss, dss, sos, ixs, ms, pr.cuda_stream, pl.cuda_stream]), vp([e.cuda_event for e in ring])]
+                    (C.c_int64 * K)(*n_k), vp([xss, dss, sos, ixs, ms, pr.cuda_stream, pl.cuda_stream]), vp([e.cuda_event for e in ring])]
             A.ids, A.grads, A.n_k, A.streams, A.events = (C.cast(x, C.c_void_p) for x in keep)
             for q in range(4):
                 A.u[q], A.inv[q], A.scr_s[q] = u_ptr[q], inv_ptr[q], ss_ptr[q]
             A.scr_s_bytes, A.scr_u, A.scr_u_bytes = ss_len, su_ptr, su_len
             if self._stage_events:
-                keep.append(vp([e.cuda_event for pair in self._stage_events for e in pair]))
+                cached = getattr(self, '_stage_events_handles', None)       # the same list of events window after window: keep its handles
+                if cached is None or cached[0] is not self._stage_events or len(cached[1]) != 2 * len(self._stage_events):
+                    cached = self._stage_events_handles = (self._stage_events, vp([e.cuda_event for pair in self._stage_events for e in pair]))
+                keep.append(cached[1])
                 A.stage_events = C.cast(keep[-1], C.c_void_p)
             if trace:
                 tev = [torch.cuda.Event(enable_timing=True) for _ in range(K * 14)]
@@ -540,6 +543,7 @@ class ShardedSparseAdam:
             self.last_local_lookups = nr
             self.last_local_lookups_total += nr * K
             return [counts_out[k] for k in range(K)]
+        cnt_ptr = [counts_out.data_ptr() + 16 * k for k in range(K)]
         mkev = lambda: torch.cuda.Event(enable_timing=trace)
         ev_x, ev_d, ev_i, ev_done, ev_p = ([mkev() for _ in range(K)] for _ in range(5))
         ev_begin = {q: [mkev() for _ in range(K)] for q in 'xdis'} if trace else None
